@@ -1,0 +1,55 @@
+// Shared helpers of the kernel library: error reporting, dtype codes, conversions.
+//
+// Every exported function is `extern "C"`, takes raw device pointers, sizes and a stream, returns 0
+// on success and a non-zero code otherwise; `gi_last_error()` gives the message of the last failure
+// on the calling thread. Nothing here allocates device memory: callers own every buffer.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+namespace gi {
+
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+void set_error(const char* fmt, ...);
+
+inline int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("%s: %s", what, cudaGetErrorString(e));
+        return 1;
+    }
+    return 0;
+}
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+}  // namespace gi
+
+#define GI_REQUIRE(cond, ...)            \
+    do {                                 \
+        if (!(cond)) {                   \
+            gi::set_error(__VA_ARGS__);  \
+            return 2;                    \
+        }                                \
+    } while (0)

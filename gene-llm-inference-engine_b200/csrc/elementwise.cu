@@ -1,0 +1,229 @@
+// Memory-bound kernels of the step: embedding gather, RMSNorm, rotary position encoding fused with
+// the key/value page store, SwiGLU, and the page copy used for copy-on-write.
+//
+// Numerics follow the reference's scalar definitions: RMSNorm `w * (scale * x)` with
+// `scale = 1/sqrt(sum(x^2)/n + eps)` (src/kernels/kernels.cpp:72-83), rotation `a*c - b*s`,
+// `a*s + b*c` (src/kernels/kernels.cpp:164-180), SiLU `g * (1/(1+exp(-g)))`
+// (src/kernels/kernels.cpp:106-110). All arithmetic is 32-bit; only stores round.
+#include "common.cuh"
+
+#include <mutex>
+#include <string>
+
+namespace gi {
+
+static thread_local std::string g_error;
+
+void set_error(const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_error = buf;
+}
+
+// ---------------------------------------------------------------------------------- embedding
+template <typename TW>
+__global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
+                             float* __restrict__ out, int D, float scale) {
+    const int t = blockIdx.x;
+    const TW* row = table + static_cast<size_t>(tokens[t]) * D;
+    float* o = out + static_cast<size_t>(t) * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) o[d] = to_float(row[d]) * scale;
+}
+
+// ---------------------------------------------------------------------------------- RMSNorm
+// One block per output row. Each thread sums a fixed strided subset with fmaf, lanes are combined
+// by a fixed xor tree and warps in index order, so a row's result never depends on the batch.
+template <typename TOut>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                               const float* __restrict__ weight, TOut* __restrict__ out, int D, float eps) {
+    __shared__ float warp_part[32];
+    __shared__ float s_scale;
+    const int r = blockIdx.x;
+    const float* xr = x + static_cast<size_t>(rows ? rows[r] : r) * D;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) ss = fmaf(xr[d], xr[d], ss);
+    ss = warp_sum(ss);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    if (lane == 0) warp_part[warp] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.f;
+        for (int w = 0; w < nwarp; ++w) total += warp_part[w];
+        s_scale = 1.0f / sqrtf(total / static_cast<float>(D) + eps);
+    }
+    __syncthreads();
+    const float scale = s_scale;
+    TOut* o = out + static_cast<size_t>(r) * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) o[d] = from_float<TOut>(weight[d] * (scale * xr[d]));
+}
+
+// ---------------------------------------------------------------------------------- SwiGLU
+template <typename TOut>
+__global__ void swiglu_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int I, size_t total) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / I;
+    const int c = static_cast<int>(i % I);
+    const float g = gu[t * 2 * I + c];
+    const float u = gu[t * 2 * I + I + c];
+    out[i] = from_float<TOut>(g * (1.0f / (1.0f + expf(-g))) * u);
+}
+
+// ---------------------------------------------------------------------------------- RoPE + store
+// One block per token. Query heads are rotated and written to q_out; key heads are rotated and
+// written to the token's cache row; value heads are copied there. cos/sin are rows of a table
+// [max_position, rot_half] built on the host in double precision.
+template <typename TQ, typename TKV>
+__global__ void rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positions,
+                                  const int* __restrict__ row_req, const int* __restrict__ block_tables,
+                                  int table_stride, const float* __restrict__ cos_t,
+                                  const float* __restrict__ sin_t, int rot_half, int interleaved,
+                                  TQ* __restrict__ q_out, TKV* __restrict__ k_cache, TKV* __restrict__ v_cache,
+                                  int H, int Hkv, int hd, int page_size, int write_kv) {
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const float* row = qkv + static_cast<size_t>(t) * (H + 2 * Hkv) * hd;
+    const float* c = cos_t ? cos_t + static_cast<size_t>(pos) * rot_half : nullptr;
+    const float* s = sin_t ? sin_t + static_cast<size_t>(pos) * rot_half : nullptr;
+    const int rot_dim = c ? 2 * rot_half : 0;
+    size_t kv_base = 0;
+    if (write_kv) {
+        const int page = block_tables[static_cast<size_t>(row_req[t]) * table_stride + pos / page_size];
+        kv_base = (static_cast<size_t>(page) * Hkv * page_size + (pos % page_size)) * hd;
+    }
+    const int n_rot = (H + (write_kv ? Hkv : 0)) * hd;
+    for (int e = threadIdx.x; e < n_rot; e += blockDim.x) {
+        const int head = e / hd, d = e % hd;
+        const float* v = row + static_cast<size_t>(head) * hd;
+        float o;
+        if (d < rot_dim) {
+            if (interleaved) {
+                const int k = d >> 1;
+                o = (d & 1) ? v[d - 1] * s[k] + v[d] * c[k] : v[d] * c[k] - v[d + 1] * s[k];
+            } else if (d < rot_half) {
+                o = v[d] * c[d] - v[d + rot_half] * s[d];
+            } else {
+                const int k = d - rot_half;
+                o = v[k] * s[k] + v[d] * c[k];
+            }
+        } else {
+            o = v[d];
+        }
+        if (head < H) {
+            q_out[(static_cast<size_t>(t) * H + head) * hd + d] = from_float<TQ>(o);
+        } else {
+            const int g = head - H;
+            k_cache[kv_base + static_cast<size_t>(g) * page_size * hd + d] = from_float<TKV>(o);
+        }
+    }
+    if (write_kv) {
+        const float* vrow = row + static_cast<size_t>(H + Hkv) * hd;
+        for (int e = threadIdx.x; e < Hkv * hd; e += blockDim.x) {
+            const int g = e / hd, d = e % hd;
+            v_cache[kv_base + static_cast<size_t>(g) * page_size * hd + d] = from_float<TKV>(vrow[e]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------- page copy
+__global__ void copy_pages_kernel(char* base, size_t array_stride, size_t page_bytes,
+                                  const int* __restrict__ src, const int* __restrict__ dst) {
+    char* arr = base + blockIdx.y * array_stride;
+    const uint4* s = reinterpret_cast<const uint4*>(arr + static_cast<size_t>(src[blockIdx.x]) * page_bytes);
+    uint4* d = reinterpret_cast<uint4*>(arr + static_cast<size_t>(dst[blockIdx.x]) * page_bytes);
+    for (size_t i = threadIdx.x; i < page_bytes / 16; i += blockDim.x) d[i] = s[i];
+}
+
+}  // namespace gi
+
+using namespace gi;
+
+extern "C" {
+
+const char* gi_last_error() { return g_error.c_str(); }
+
+int gi_embed(const void* table, int table_dtype, const int* tokens, float* out, int T, int D, float scale,
+             void* stream) {
+    if (T == 0) return 0;
+    GI_REQUIRE(T > 0 && D > 0, "embed: T and D must be positive (T=%d, D=%d)", T, D);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (table_dtype == kF32) {
+        embed_kernel<float><<<T, 256, 0, st>>>(static_cast<const float*>(table), tokens, out, D, scale);
+    } else if (table_dtype == kBF16) {
+        embed_kernel<__nv_bfloat16><<<T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(table), tokens, out, D, scale);
+    } else {
+        GI_REQUIRE(false, "embed: unsupported table dtype code %d", table_dtype);
+    }
+    return check_launch("embed");
+}
+
+int gi_rmsnorm(const float* x, const int* rows, const float* weight, void* out, int out_dtype, int n_rows, int D,
+               float eps, void* stream) {
+    if (n_rows == 0) return 0;
+    GI_REQUIRE(n_rows > 0 && D > 0, "rmsnorm: sizes must be positive (rows=%d, D=%d)", n_rows, D);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (out_dtype == kF32) {
+        rmsnorm_kernel<float><<<n_rows, 256, 0, st>>>(x, rows, weight, static_cast<float*>(out), D, eps);
+    } else if (out_dtype == kBF16) {
+        rmsnorm_kernel<__nv_bfloat16><<<n_rows, 256, 0, st>>>(x, rows, weight, static_cast<__nv_bfloat16*>(out), D, eps);
+    } else {
+        GI_REQUIRE(false, "rmsnorm: unsupported output dtype code %d", out_dtype);
+    }
+    return check_launch("rmsnorm");
+}
+
+int gi_swiglu(const float* gate_up, void* out, int out_dtype, int T, int I, void* stream) {
+    if (T == 0) return 0;
+    GI_REQUIRE(T > 0 && I > 0, "swiglu: sizes must be positive (T=%d, I=%d)", T, I);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t total = static_cast<size_t>(T) * I;
+    const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+    if (out_dtype == kF32) {
+        swiglu_kernel<float><<<blocks, 256, 0, st>>>(gate_up, static_cast<float*>(out), I, total);
+    } else if (out_dtype == kBF16) {
+        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(gate_up, static_cast<__nv_bfloat16*>(out), I, total);
+    } else {
+        GI_REQUIRE(false, "swiglu: unsupported output dtype code %d", out_dtype);
+    }
+    return check_launch("swiglu");
+}
+
+// dtype: the type of q_out and of the cache (both f32 on the 32-bit path, both bf16 otherwise).
+int gi_rope_store(const float* qkv, const int* positions, const int* row_req, const int* block_tables,
+                  int table_stride, const float* cos_t, const float* sin_t, int rot_half, int interleaved,
+                  void* q_out, void* k_cache, void* v_cache, int dtype, int T, int H, int Hkv, int hd,
+                  int page_size, int write_kv, void* stream) {
+    if (T == 0) return 0;
+    GI_REQUIRE(T > 0 && H > 0 && Hkv > 0 && hd > 0 && page_size > 0, "rope_store: sizes must be positive");
+    GI_REQUIRE(2 * rot_half <= hd, "rope_store: rotary size %d exceeds the head size %d", 2 * rot_half, hd);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == kF32) {
+        rope_store_kernel<float, float><<<T, 256, 0, st>>>(
+            qkv, positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved,
+            static_cast<float*>(q_out), static_cast<float*>(k_cache), static_cast<float*>(v_cache), H, Hkv, hd,
+            page_size, write_kv);
+    } else if (dtype == kBF16) {
+        rope_store_kernel<__nv_bfloat16, __nv_bfloat16><<<T, 256, 0, st>>>(
+            qkv, positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved,
+            static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
+            static_cast<__nv_bfloat16*>(v_cache), H, Hkv, hd, page_size, write_kv);
+    } else {
+        GI_REQUIRE(false, "rope_store: unsupported dtype code %d", dtype);
+    }
+    return check_launch("rope_store");
+}
+
+int gi_copy_pages(void* base, long long array_stride_bytes, int n_arrays, long long page_bytes, const int* src,
+                  const int* dst, int n_copies, void* stream) {
+    if (n_copies == 0 || n_arrays == 0) return 0;
+    GI_REQUIRE(page_bytes % 16 == 0, "copy_pages: a page of %lld bytes is not a multiple of 16", page_bytes);
+    dim3 grid(n_copies, n_arrays);
+    copy_pages_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<char*>(base), static_cast<size_t>(array_stride_bytes), static_cast<size_t>(page_bytes), src, dst);
+    return check_launch("copy_pages");
+}
+
+}  // extern "C"

@@ -1,0 +1,276 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+A step takes any mix of prompt portions and single decoded tokens, cut anywhere. It runs only the
+tokens it is given, as one batch, against what earlier steps left in the cache, and returns the
+logits at the wanted places. Position of a token = the request's cached length + its index among
+the request's tokens of this step (src/model/transformer.cpp:483-518). A step is all or nothing:
+pages for every entry are reserved first, and if they run out everything is given back and
+``OutOfPages`` is raised with no state changed.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, OutOfPages, RequestCache
+from ..ops import kernels
+from ..parts import DecoderModel
+
+_STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request and the places among them whose logits are wanted."""
+    key: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)
+
+
+@dataclass
+class Segment:
+    """Where one request's tokens lie in the step's rows (host copy, for parts that need it)."""
+    key: Hashable
+    start: int          # first row
+    length: int         # number of rows
+    first_position: int
+    state_slot: int
+    fresh_state: bool
+
+
+class StepContext:
+    """What the parts see of a step: row arrays on the device, caches, state and scratch."""
+
+    def __init__(self, engine: "StepEngine", n_tokens: int, n_requests: int, n_logit_rows: int,
+                 segments: List[Segment], views: Dict[str, torch.Tensor]):
+        self._engine = engine
+        self.n_tokens = n_tokens
+        self.n_requests = n_requests
+        self.n_logit_rows = n_logit_rows
+        self.segments = segments
+        self.page_size = engine.page_size
+        self.compute_dtype = engine.model.dtype
+        self.tokens = views["tokens"]
+        self.positions = views["positions"]
+        self.row_req = views["row_req"]
+        self.logit_rows = views["logit_rows"]
+        self.state_slots = views["state_slots"]
+        self.seg_start = views["seg_start"]
+        self.seg_len = views["seg_len"]
+        self._tables = views["tables"]
+        self.all_single = all(s.length == 1 for s in segments)
+        self.max_context = max((s.first_position + s.length for s in segments), default=0)
+
+    def pages(self, layer: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(keys, values) of a layer, each [pages, Hkv, page_size, head_dim]."""
+        return self._engine.layer_pages[layer]
+
+    def block_tables(self, layer: int) -> torch.Tensor:
+        """Block tables [requests of this step, stride] of the group the layer belongs to."""
+        return self._tables[self._engine.cache.group_of_layer[layer]]
+
+    def state(self, layer: int) -> torch.Tensor:
+        """State of a layer for every slot: [slots, *shape]; row ``state_slot`` is a request's."""
+        return self._engine.layer_state[layer]
+
+    def scratch(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        return self._engine.scratch(name, shape, dtype)
+
+
+class StepEngine:
+    def __init__(self, model: DecoderModel, page_size: int = 16, n_pages: int = 256, max_requests: int = 8,
+                 max_step_tokens: int = 2048, max_logit_rows: Optional[int] = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("StepEngine needs a CUDA device: this engine has no CPU path")
+        self.model = model
+        self.device = model.device
+        self.page_size = page_size
+        self.n_pages = n_pages
+        self.max_requests = max_requests
+        self.max_step_tokens = max_step_tokens
+        self.max_logit_rows = max_logit_rows or max_step_tokens
+        needs = model.cache_needs()
+        state_needs = model.state_needs()
+        self.cache = CacheManager(needs, page_size, n_pages, model.max_position, max_requests,
+                                  state_layers=sorted(state_needs))
+        # device memory of the pages: per group [layers of the group, 2 (keys, values), pages, Hkv, page, hd]
+        self.group_pages: List[torch.Tensor] = []
+        self.layer_pages: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+        for group in self.cache.groups:
+            need = group.need
+            t = torch.empty((len(group.layers), 2, n_pages, need.num_kv_heads, page_size, need.head_dim),
+                            dtype=model.dtype, device=self.device)
+            t.fill_(float("nan"))       # never read before written; NaN makes a stale read visible
+            self.group_pages.append(t)
+            for i, layer in enumerate(group.layers):
+                self.layer_pages[layer] = (t[i, 0], t[i, 1])
+        self.layer_state: Dict[int, torch.Tensor] = {}
+        for layer, need in state_needs.items():
+            self.layer_state[layer] = torch.zeros((max_requests, *need.shape), dtype=_STATE_DTYPES[need.dtype],
+                                                  device=self.device)
+        self._scratch: Dict[Tuple, torch.Tensor] = {}
+        self._init_descriptor()
+
+    # ------------------------------------------------------------------ memory
+    def scratch(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """A reusable buffer; the same name, trailing shape and dtype give the same memory each step."""
+        key = (name, tuple(shape[1:]), dtype)
+        buf = self._scratch.get(key)
+        if buf is None or buf.shape[0] < shape[0]:
+            rows = max(shape[0], self.max_logit_rows if name in ("logits", "head_in") else self.max_step_tokens)
+            buf = torch.empty((rows, *shape[1:]), dtype=dtype, device=self.device)
+            self._scratch[key] = buf
+        return buf[:shape[0]]
+
+    def _init_descriptor(self) -> None:
+        """One int32 buffer holds everything the kernels read about a step's rows and requests; a
+        ring of pinned host mirrors is filled and copied with a single transfer per step."""
+        T, R = self.max_step_tokens, self.max_requests
+        stride = self.cache.max_pages_per_request
+        self._layout: Dict[str, Tuple[int, int]] = {}
+        off = 0
+        for name, n in (("tokens", T), ("positions", T), ("row_req", T), ("logit_rows", self.max_logit_rows),
+                        ("state_slots", R), ("seg_start", R), ("seg_len", R)):
+            self._layout[name] = (off, n)
+            off += n
+        self._table_stride = max(stride, 1)
+        self._table_off = []
+        for _ in self.cache.groups:
+            self._table_off.append(off)
+            off += R * self._table_stride
+        self._desc_size = off
+        self._desc_dev = torch.zeros(off, dtype=torch.int32, device=self.device)
+        self._ring = [torch.zeros(off, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._ring_np = [b.numpy() for b in self._ring]
+        self._ring_events: List[Optional[torch.cuda.Event]] = [None] * 4
+        self._ring_next = 0
+
+    # ------------------------------------------------------------------ requests
+    def open(self, key: Hashable) -> RequestCache:
+        return self.cache.open(key)
+
+    def close(self, key: Hashable) -> None:
+        self.cache.close(self.cache.requests[key])
+
+    def length(self, key: Hashable) -> int:
+        return self.cache.requests[key].length
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs one batch. Returns 32-bit logits [wanted, vocab] on the device, in the order of
+        the entries and of each entry's ``want`` (None when nothing is wanted). The returned
+        tensor is scratch memory that the next step overwrites."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return None
+        V = self.model.vocab_size
+        seen = set()
+        total = 0
+        n_want = 0
+        for e in entries:
+            if e.key in seen:
+                raise ValueError(f"request {e.key!r} appears twice in one step")
+            seen.add(e.key)
+            if e.key not in self.cache.requests:
+                raise KeyError(f"request {e.key!r} is not open")
+            n = len(e.tokens)
+            for tok in e.tokens:
+                if not (0 <= int(tok) < V):
+                    raise IndexError(f"token id {tok} is outside the vocabulary of {V}")
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise IndexError(f"wanted place {w} is outside the {n} tokens of request {e.key!r}")
+            rc = self.cache.requests[e.key]
+            if rc.length + n > self.model.max_position:
+                raise IndexError(f"request {e.key!r}: position {rc.length + n - 1} is beyond the context length "
+                                 f"{self.model.max_position}")
+            total += n
+            n_want += len(e.want)
+        if total > self.max_step_tokens:
+            raise ValueError(f"{total} tokens in one step exceed the limit {self.max_step_tokens}")
+        if len(entries) > self.max_requests:
+            raise ValueError(f"{len(entries)} requests in one step exceed the limit {self.max_requests}")
+        if n_want > self.max_logit_rows:
+            raise ValueError(f"{n_want} wanted rows exceed the limit {self.max_logit_rows}")
+
+        # ---- reserve pages for every entry, all or nothing
+        reserved: List[RequestCache] = []
+        copies = []
+        try:
+            for e in entries:
+                rc = self.cache.requests[e.key]
+                copies += self.cache.reserve(rc, len(e.tokens))
+                reserved.append(rc)
+        except OutOfPages:
+            for rc in reserved:
+                self.cache.rollback(rc)
+            raise
+        if copies:
+            self._copy_pages(copies)
+
+        # ---- describe the step
+        slot = self._ring_next
+        self._ring_next = (slot + 1) % len(self._ring)
+        if self._ring_events[slot] is not None:
+            self._ring_events[slot].synchronize()
+        host = self._ring_np[slot]
+        lay = self._layout
+        segments: List[Segment] = []
+        row = 0
+        k = 0
+        t_off, p_off, r_off, l_off = lay["tokens"][0], lay["positions"][0], lay["row_req"][0], lay["logit_rows"][0]
+        for r, e in enumerate(entries):
+            rc = self.cache.requests[e.key]
+            n = len(e.tokens)
+            host[t_off + row:t_off + row + n] = np.asarray(e.tokens, dtype=np.int32)
+            host[p_off + row:p_off + row + n] = np.arange(rc.length, rc.length + n, dtype=np.int32)
+            host[r_off + row:r_off + row + n] = r
+            for w in e.want:
+                host[l_off + k] = row + int(w)
+                k += 1
+            host[lay["state_slots"][0] + r] = rc.state_slot
+            host[lay["seg_start"][0] + r] = row
+            host[lay["seg_len"][0] + r] = n
+            for g in range(len(self.cache.groups)):
+                base = self._table_off[g] + r * self._table_stride
+                npg = rc.n_pages[g]
+                host[base:base + npg] = rc.tables[g][:npg]
+            segments.append(Segment(e.key, row, n, rc.length, rc.state_slot, rc.fresh_state))
+            row += n
+        self._desc_dev.copy_(self._ring[slot], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._ring_events[slot] = ev
+
+        dev = self._desc_dev
+        R = len(entries)
+        views = {
+            "tokens": dev[t_off:t_off + total], "positions": dev[p_off:p_off + total],
+            "row_req": dev[r_off:r_off + total], "logit_rows": dev[l_off:l_off + k],
+            "state_slots": dev[lay["state_slots"][0]:lay["state_slots"][0] + R],
+            "seg_start": dev[lay["seg_start"][0]:lay["seg_start"][0] + R],
+            "seg_len": dev[lay["seg_len"][0]:lay["seg_len"][0] + R],
+            "tables": [dev[o:o + R * self._table_stride].view(R, self._table_stride) for o in self._table_off],
+        }
+        for seg in segments:                       # state of a new request starts from zero
+            if seg.fresh_state:
+                for st in self.layer_state.values():
+                    st[seg.state_slot].zero_()
+        ctx = StepContext(self, total, R, k, segments, views)
+        logits = self.model.forward(ctx)
+        for e in entries:
+            self.cache.advance(self.cache.requests[e.key], len(e.tokens))
+        return logits
+
+    def _copy_pages(self, copies) -> None:
+        for g, pages in enumerate(self.group_pages):
+            mine = [c for c in copies if c.group == g]
+            if not mine:
+                continue
+            src = torch.tensor([c.src for c in mine], dtype=torch.int32, device=self.device)
+            dst = torch.tensor([c.dst for c in mine], dtype=torch.int32, device=self.device)
+            flat = pages.view(pages.shape[0] * 2, *pages.shape[2:])
+            kernels.copy_pages(flat, src, dst)

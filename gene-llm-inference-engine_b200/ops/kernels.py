@@ -1,0 +1,158 @@
+"""Python faces of the kernel entry points: tensors in, launches on the current stream.
+
+Each function checks device, dtype, contiguity and sizes of what it is given (a kernel never sees
+a pointer it could misread) and raises ``KernelError`` with the library's message when the library
+refuses a size. Nothing here computes on the host.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .library import KernelError, check, lib
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _CODES[dtype]
+    except KeyError:
+        raise KernelError(f"unsupported dtype {dtype} (float32 and bfloat16 only)") from None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev(t: torch.Tensor, name: str, dtype: Optional[torch.dtype] = None) -> int:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+def _opt(t: Optional[torch.Tensor], name: str, dtype: torch.dtype) -> int:
+    return 0 if t is None else _dev(t, name, dtype)
+
+
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t, :] = table[tokens[t], :] * scale, widened to 32-bit."""
+    T, D = out.shape
+    if table.shape[1] != D or tokens.numel() != T:
+        raise KernelError("embed: shapes of table, tokens and out do not agree")
+    check(lib().gi_embed(_dev(table, "table"), dtype_code(table.dtype), _dev(tokens, "tokens", torch.int32),
+                         _dev(out, "out", torch.float32), T, D, float(scale), _stream()), "embed")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r, :] = weight * (x[row_r, :] / sqrt(mean(x^2) + eps)); ``rows`` gathers rows of x."""
+    n, D = out.shape
+    if x.shape[1] != D or weight.numel() != D:
+        raise KernelError("rmsnorm: shapes of x, weight and out do not agree")
+    if rows is None and x.shape[0] < n:
+        raise KernelError("rmsnorm: x has fewer rows than out")
+    if rows is not None and rows.numel() != n:
+        raise KernelError("rmsnorm: rows and out do not agree")
+    check(lib().gi_rmsnorm(_dev(x, "x", torch.float32), _opt(rows, "rows", torch.int32),
+                           _dev(weight, "weight", torch.float32), _dev(out, "out"), dtype_code(out.dtype),
+                           n, D, float(eps), _stream()), "rmsnorm")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I):
+        raise KernelError("swiglu: gate_up must be [T, 2I] for out [T, I]")
+    check(lib().gi_swiglu(_dev(gate_up, "gate_up", torch.float32), _dev(out, "out"), dtype_code(out.dtype), T, I,
+                          _stream()), "swiglu")
+
+
+def rope_store(qkv: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor, block_tables: torch.Tensor,
+               cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], interleaved: bool,
+               q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+               num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, write_kv: bool = True) -> None:
+    """Rotates query and key heads of ``qkv`` [T, (H+2Hkv)*hd] by the rows of the cos/sin table at
+    each token's position, writes queries to ``q_out`` [T, H*hd] and keys/values into the token's
+    row of the paged cache [pages, Hkv, page_size, hd]."""
+    T = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError("rope_store: qkv width does not match the head counts")
+    if q_out.shape != (T, num_heads * head_dim):
+        raise KernelError("rope_store: q_out must be [T, H*hd]")
+    if k_cache.dtype != q_out.dtype or v_cache.dtype != q_out.dtype:
+        raise KernelError("rope_store: q_out and the cache must have one dtype")
+    if k_cache.shape[1:] != (num_kv_heads, page_size, head_dim) or v_cache.shape != k_cache.shape:
+        raise KernelError("rope_store: the cache must be [pages, Hkv, page_size, hd]")
+    rot_half = 0 if cos is None else cos.shape[1]
+    if cos is not None and (sin is None or sin.shape != cos.shape):
+        raise KernelError("rope_store: cos and sin tables must have one shape")
+    check(lib().gi_rope_store(
+        _dev(qkv, "qkv", torch.float32), _dev(positions, "positions", torch.int32),
+        _dev(row_req, "row_req", torch.int32), _dev(block_tables, "block_tables", torch.int32),
+        block_tables.shape[1], _opt(cos, "cos", torch.float32), _opt(sin, "sin", torch.float32), rot_half,
+        int(interleaved), _dev(q_out, "q_out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
+        dtype_code(q_out.dtype), T, num_heads, num_kv_heads, head_dim, page_size, int(write_kv), _stream()),
+        "rope_store")
+
+
+def copy_pages(cache: torch.Tensor, src: torch.Tensor, dst: torch.Tensor) -> None:
+    """cache is [arrays, pages, ...]; copies page src[i] to page dst[i] in every array."""
+    n_arrays = cache.shape[0]
+    page_bytes = cache[0, 0].numel() * cache.element_size()
+    array_stride = cache[0].numel() * cache.element_size()
+    check(lib().gi_copy_pages(_dev(cache, "cache"), array_stride, n_arrays, page_bytes,
+                              _dev(src, "src", torch.int32), _dev(dst, "dst", torch.int32), src.numel(),
+                              _stream()), "copy_pages")
+
+
+def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                      row_req: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor,
+                      num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, scale: float,
+                      window: Optional[int] = None) -> None:
+    """Causal attention of every row of ``q`` [T, H*hd] over its request's pages."""
+    T = q.shape[0]
+    if q.shape != (T, num_heads * head_dim) or out.shape != q.shape or out.dtype != q.dtype:
+        raise KernelError("attention: q and out must be [T, H*hd] of one dtype")
+    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise KernelError("attention: q and the cache must have one dtype")
+    if k_cache.shape[1:] != (num_kv_heads, page_size, head_dim) or v_cache.shape != k_cache.shape:
+        raise KernelError("attention: the cache must be [pages, Hkv, page_size, hd]")
+    check(lib().gi_attention_generic(
+        _dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), _dev(out, "out"), dtype_code(q.dtype),
+        _dev(row_req, "row_req", torch.int32), _dev(positions, "positions", torch.int32),
+        _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1], T, num_heads, num_kv_heads,
+        head_dim, page_size, float(scale), int(window or 0), _stream()), "attention")
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out[M,N] (+)= a[M,K] @ w[N,K]^T with 32-bit fused multiply-adds on the CUDA cores."""
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm: shapes do not agree (a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)})")
+    check(lib().gi_gemm_simt(_dev(a, "a"), dtype_code(a.dtype), _dev(w, "w"), dtype_code(w.dtype), _dev(out, "out"),
+                             dtype_code(out.dtype), int(accumulate), M, N, K, K, K, N, _stream()), "gemm")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    rows, V = logits.shape
+    check(lib().gi_argmax(_dev(logits, "logits", torch.float32), rows, V, _dev(out, "out", torch.int32), _stream()),
+          "argmax")
+
+
+def sample(logits: torch.Tensor, scratch: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> None:
+    rows, V = logits.shape
+    if scratch.numel() < rows * V:
+        raise KernelError("sample: scratch must hold rows x vocab floats")
+    check(lib().gi_sample(_dev(logits, "logits", torch.float32), _dev(scratch, "scratch", torch.float32), rows, V,
+                          _dev(temperature, "temperature", torch.float32), _dev(top_k, "top_k", torch.int32),
+                          _dev(top_p, "top_p", torch.float32), _dev(uniform, "uniform", torch.float32),
+                          _dev(out, "out", torch.int32), _stream()), "sample")

@@ -1,0 +1,34 @@
+"""A weight matrix with the matrix products the engine needs: ``out (+)= a @ weight^T``.
+
+The weight is [N, K] row-major, as checkpoints store it (``y = W x``). On the 32-bit path weight
+and activations are 32-bit and the product runs on the CUDA cores with fused multiply-adds. On the
+bfloat16 path the weight is bfloat16 and the product accumulates in 32-bit; the output may be
+32-bit (and may accumulate into the 32-bit residual stream) or bfloat16.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import kernels
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, compute_dtype: torch.dtype, device: torch.device):
+        if weight.dim() != 2:
+            raise ValueError("Linear: the weight must be a matrix")
+        self.out_features, self.in_features = weight.shape
+        self.compute_dtype = compute_dtype
+        self.weight = weight.to(device=device, dtype=compute_dtype).contiguous()
+
+    @classmethod
+    def sharing(cls, other: "Linear") -> "Linear":
+        """A second Linear over the same device tensor (a tied head)."""
+        new = cls.__new__(cls)
+        new.__dict__.update(other.__dict__)
+        return new
+
+    def forward(self, a: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
+        if a.dtype != self.compute_dtype:
+            raise kernels.KernelError(f"Linear: activations are {a.dtype}, the weight is {self.compute_dtype}")
+        kernels.gemm_simt(a, self.weight, out, accumulate)
+        return out

@@ -1,0 +1,66 @@
+"""The attention mixer: grouped-query causal attention over the paged cache."""
+from __future__ import annotations
+
+import torch
+
+from ..cache import CacheNeed
+from ..config import PartSpec
+from ..ops import kernels
+from ..ops.linear import Linear
+from .registry import POSITION_ENCODINGS, build_part, register_mixer
+
+
+@register_mixer("attention")
+class AttentionMixer:
+    """q, k, v = W_qkv xn; position encoding on q and k; k, v stored in the request's pages;
+    causal softmax(q k^T * scale) v per head with query head h reading key/value head
+    h // (H / Hkv); x += W_o out (src/model/transformer.cpp:389-434).
+
+    Params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale`` (multiplied
+    after the dot product), ``window`` (None = all keys) and ``position`` (a PartSpec).
+    Weights: ``w_qkv`` [(H+2Hkv)*hd, hidden] and ``w_o`` [hidden, H*hd]."""
+
+    def __init__(self, params, weights, build):
+        self.hidden_size = int(params["hidden_size"])
+        self.num_heads = int(params["num_heads"])
+        self.num_kv_heads = int(params["num_kv_heads"])
+        self.head_dim = int(params["head_dim"])
+        self.scale = float(params["scale"])
+        self.window = params.get("window")
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError("attention: num_heads must be a multiple of num_kv_heads")
+        pos_spec = params.get("position") or PartSpec("none", {})
+        self.position = build_part(POSITION_ENCODINGS, "position encoding", pos_spec, {}, build)
+        qkv_rows = (self.num_heads + 2 * self.num_kv_heads) * self.head_dim
+        if tuple(weights["w_qkv"].shape) != (qkv_rows, self.hidden_size):
+            raise ValueError(f"attention: w_qkv has shape {tuple(weights['w_qkv'].shape)}, expected "
+                             f"({qkv_rows}, {self.hidden_size})")
+        if tuple(weights["w_o"].shape) != (self.hidden_size, self.num_heads * self.head_dim):
+            raise ValueError(f"attention: w_o has shape {tuple(weights['w_o'].shape)}")
+        self.w_qkv = Linear(weights["w_qkv"], build.compute_dtype, build.device)
+        self.w_o = Linear(weights["w_o"], build.compute_dtype, build.device)
+        self.dtype = build.compute_dtype
+
+    def cache_need(self):
+        return CacheNeed(self.num_kv_heads, self.head_dim, self.window)
+
+    def state_need(self):
+        return None
+
+    def forward(self, ctx, run, xn: torch.Tensor, x: torch.Tensor) -> None:
+        """``xn``: normalised input [T, hidden] in the compute dtype; ``x``: the 32-bit residual
+        stream, to which the mixer's output is added. ``run`` names whose cache to use."""
+        T = xn.shape[0]
+        H, Hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        k_cache, v_cache = ctx.pages(run.cache_layer)
+        tables = ctx.block_tables(run.cache_layer)
+        qkv = ctx.scratch("qkv", (T, (H + 2 * Hkv) * hd), torch.float32)
+        self.w_qkv.forward(xn, qkv)
+        q = ctx.scratch("q", (T, H * hd), self.dtype)
+        kernels.rope_store(qkv, ctx.positions, ctx.row_req, tables, self.position.cos, self.position.sin,
+                           self.position.interleaved, q, k_cache, v_cache, H, Hkv, hd, ctx.page_size,
+                           write_kv=run.writes_cache)
+        att = ctx.scratch("att", (T, H * hd), self.dtype)
+        kernels.attention_generic(q, k_cache, v_cache, att, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
+                                  ctx.page_size, self.scale, self.window)
+        self.w_o.forward(att, x, accumulate=True)

@@ -1,0 +1,36 @@
+"""Feed-forward parts."""
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels
+from ..ops.linear import Linear
+from .registry import register_feed_forward
+
+
+@register_feed_forward("swiglu")
+class SwiGLUFeedForward:
+    """x += W_down (silu(W_gate xn) * (W_up xn)) (src/model/transformer.cpp:437-450).
+
+    Params: ``hidden_size``, ``intermediate_size``. Weights: ``w_gate_up`` [2I, hidden] (gate rows
+    first, then up rows) and ``w_down`` [hidden, I]."""
+
+    def __init__(self, params, weights, build):
+        self.hidden_size = int(params["hidden_size"])
+        self.intermediate_size = int(params["intermediate_size"])
+        I, D = self.intermediate_size, self.hidden_size
+        if tuple(weights["w_gate_up"].shape) != (2 * I, D):
+            raise ValueError(f"swiglu: w_gate_up has shape {tuple(weights['w_gate_up'].shape)}, expected ({2 * I}, {D})")
+        if tuple(weights["w_down"].shape) != (D, I):
+            raise ValueError(f"swiglu: w_down has shape {tuple(weights['w_down'].shape)}, expected ({D}, {I})")
+        self.w_gate_up = Linear(weights["w_gate_up"], build.compute_dtype, build.device)
+        self.w_down = Linear(weights["w_down"], build.compute_dtype, build.device)
+        self.dtype = build.compute_dtype
+
+    def forward(self, ctx, xn: torch.Tensor, x: torch.Tensor) -> None:
+        T = xn.shape[0]
+        gu = ctx.scratch("gate_up", (T, 2 * self.intermediate_size), torch.float32)
+        self.w_gate_up.forward(xn, gu)
+        h = ctx.scratch("ffn_hidden", (T, self.intermediate_size), self.dtype)
+        kernels.swiglu(gu, h)
+        self.w_down.forward(h, x, accumulate=True)

@@ -1,0 +1,43 @@
+"""The tiny configurations the tests run: two Llama shapes that differ in every size and option."""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+TINY_A = {   # grouped heads 4:2, tied head, plain RoPE, float32 weights
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_act": "silu",
+    "hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 2, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 16, "vocab_size": 256, "max_position_embeddings": 128,
+    "rope_theta": 10000.0, "rope_scaling": None, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+}
+
+TINY_B = {   # one key/value head for 3 query heads, untied head, llama3-scaled RoPE, sizes that are no power of two
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_act": "silu",
+    "hidden_size": 96, "intermediate_size": 160, "num_hidden_layers": 3, "num_attention_heads": 3,
+    "num_key_value_heads": 1, "head_dim": 32, "vocab_size": 384, "max_position_embeddings": 256,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 64},
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+}
+
+# How each tiny model's weights are drawn (weights.write_random_model arguments).
+WEIGHTS_A = {"seed": 11, "dtype": "float32", "std": 0.02, "norm_mean": 1.0, "norm_std": 0.01}
+WEIGHTS_B = {"seed": 23, "dtype": "bfloat16", "std": 0.02, "norm_mean": 1.0, "norm_std": 0.02}
+# Larger weights give peaked attention and distinct logits, so a wrong key, a wrong position or a
+# stale page changes the result visibly (with N(0, 0.02) every softmax is nearly uniform).
+SHARP_A = dict(WEIGHTS_A, seed=12, std=0.2, norm_std=0.1)
+SHARP_B = dict(WEIGHTS_B, seed=24, std=0.2, norm_std=0.1)
+
+
+def make_model_dir(config, weights, out_dir):
+    from geneinfer_b200.weights import write_random_model
+    return write_random_model(config, weights["seed"], out_dir, weights["dtype"], std=weights["std"],
+                              norm_mean=weights["norm_mean"], norm_std=weights["norm_std"])
+
+
+def random_tokens(n, vocab, seed):
+    import numpy as np
+    return [int(t) for t in np.random.default_rng(seed).integers(0, vocab, size=n)]
