@@ -120,7 +120,10 @@ class StepEngine:
         key = (name, tuple(shape[1:]), dtype)
         buf = self._scratch.get(key)
         if buf is None or buf.shape[0] < shape[0]:
-            rows = max(shape[0], self.max_logit_rows if name in ("logits", "head_in") else self.max_step_tokens)
+            if name in ("logits", "head_in"):      # wanted rows are usually few: grow on demand
+                rows = min(self.max_logit_rows, max(8, 1 << (shape[0] - 1).bit_length()))
+            else:
+                rows = max(shape[0], self.max_step_tokens)
             buf = torch.empty((rows, *shape[1:]), dtype=dtype, device=self.device)
             self._scratch[key] = buf
         return buf[:shape[0]]

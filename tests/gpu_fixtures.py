@@ -1,0 +1,63 @@
+"""Shared pieces of the GPU tests: model folders made in a temporary place, plain logits of the
+test requests, tolerances."""
+import functools
+import os
+import tempfile
+
+import numpy as np
+import torch
+
+import plain_model as pm
+import tiny_configs as tc
+
+# 32-bit: both sides compute in 32-bit, only summation orders differ.
+TOL_F32 = 2e-5
+# bfloat16 against the plain implementation that rounds to bfloat16 at the same places: what is
+# left are summation orders and single-ulp flips of stored activations.
+TOL_BF16 = 1.5e-2
+
+_TMP = tempfile.TemporaryDirectory(prefix="geneinfer_tests_")
+
+CASES = {
+    "a": (tc.TINY_A, tc.SHARP_A), "b": (tc.TINY_B, tc.SHARP_B),
+    "a_named": (tc.TINY_A, tc.WEIGHTS_A), "b_named": (tc.TINY_B, tc.WEIGHTS_B),
+}
+
+REQUEST_LENGTHS = {"a": [40, 75, 128, 100, 64, 33, 90], "b": [1, 5, 24, 64, 100, 200, 256],
+                   "a_named": [7, 16, 33], "b_named": [1, 5, 24, 64, 100]}
+
+
+@functools.lru_cache(maxsize=None)
+def model_dir(case: str) -> str:
+    config, weights = CASES[case]
+    return tc.make_model_dir(config, weights, os.path.join(_TMP.name, case))
+
+
+@functools.lru_cache(maxsize=None)
+def requests(case: str):
+    vocab = CASES[case][0]["vocab_size"]
+    return {f"r{i}": tc.random_tokens(n, vocab, 100 + i) for i, n in enumerate(REQUEST_LENGTHS[case])}
+
+
+@functools.lru_cache(maxsize=None)
+def plain_logits(case: str, dtype: str):
+    """Plain logits [T, vocab] of every test request; for bfloat16 the plain implementation rounds
+    weights and stored activations to bfloat16 where the engine does."""
+    w, cfg = pm.load_plain(model_dir(case))
+    rnd = pm.no_rounding
+    if dtype == "bfloat16":
+        w, rnd = pm.round_weights_bf16(w), pm.bf16_rounding
+    return {rid: pm.plain_forward(w, cfg, toks, rnd).numpy() for rid, toks in requests(case).items()}
+
+
+def tolerance(dtype: str) -> float:
+    return TOL_F32 if dtype == "float32" else TOL_BF16
+
+
+def make_engine(case: str, dtype: str, n_pages: int, max_requests: int = 4, page_size: int = 16,
+                max_step_tokens: int = 512):
+    from geneinfer_b200.engine.loading import load_model
+    from geneinfer_b200.engine.step import StepEngine
+    model = load_model(model_dir(case), dtype=dtype)
+    return StepEngine(model, page_size=page_size, n_pages=n_pages, max_requests=max_requests,
+                      max_step_tokens=max_step_tokens)

@@ -143,34 +143,51 @@ def plain_swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return gate * (1.0 / (1.0 + torch.exp(-gate))) * up
 
 
-def plain_layer(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, cfg: dict, cos, sin) -> torch.Tensor:
+def no_rounding(t: torch.Tensor) -> torch.Tensor:
+    return t
+
+
+def bf16_rounding(t: torch.Tensor) -> torch.Tensor:
+    """Rounds to bfloat16 (nearest even) and widens again."""
+    return t.to(torch.bfloat16).to(F32)
+
+
+def plain_layer(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, cfg: dict, cos, sin,
+                rnd=no_rounding) -> torch.Tensor:
     """One layer in the reference's order: norm, q/k/v, rope on q and k, attention, o, +, norm,
-    gate/up, silu*up, down, + (src/model/transformer.cpp:379-451)."""
+    gate/up, silu*up, down, + (src/model/transformer.cpp:379-451). ``rnd`` is applied where a
+    bfloat16 engine stores an activation in 16 bits (the operands of matrix products and what goes
+    into the cache); sums, norms, rotation and softmax stay 32-bit either way."""
     T = x.shape[0]
     H, Hkv, hd = cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
-    xb = plain_rmsnorm(x, w[prefix + "input_layernorm.weight"], cfg["eps"])
+    xb = rnd(plain_rmsnorm(x, w[prefix + "input_layernorm.weight"], cfg["eps"]))
     q = (xb @ w[prefix + "self_attn.q_proj.weight"].T).reshape(T, H, hd)
     k = (xb @ w[prefix + "self_attn.k_proj.weight"].T).reshape(T, Hkv, hd)
-    v = (xb @ w[prefix + "self_attn.v_proj.weight"].T).reshape(T, Hkv, hd)
-    q, k = plain_rope(q, cos, sin), plain_rope(k, cos, sin)
-    att = plain_attention(q, k, v, 1.0 / math.sqrt(np.float32(hd)), cfg.get("window"))
+    v = rnd((xb @ w[prefix + "self_attn.v_proj.weight"].T).reshape(T, Hkv, hd))
+    q, k = rnd(plain_rope(q, cos, sin)), rnd(plain_rope(k, cos, sin))
+    att = rnd(plain_attention(q, k, v, 1.0 / math.sqrt(np.float32(hd)), cfg.get("window")))
     x = x + att.reshape(T, H * hd) @ w[prefix + "self_attn.o_proj.weight"].T
-    xb = plain_rmsnorm(x, w[prefix + "post_attention_layernorm.weight"], cfg["eps"])
-    h = plain_swiglu(xb @ w[prefix + "mlp.gate_proj.weight"].T, xb @ w[prefix + "mlp.up_proj.weight"].T)
+    xb = rnd(plain_rmsnorm(x, w[prefix + "post_attention_layernorm.weight"], cfg["eps"]))
+    h = rnd(plain_swiglu(xb @ w[prefix + "mlp.gate_proj.weight"].T, xb @ w[prefix + "mlp.up_proj.weight"].T))
     return x + h @ w[prefix + "mlp.down_proj.weight"].T
 
 
-def plain_forward(w: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int]) -> torch.Tensor:
+def plain_forward(w: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int], rnd=no_rounding) -> torch.Tensor:
     """Logits [T, vocab] at every position of one whole sequence (final norm and head:
     src/model/transformer.cpp:453-474; the head is the embedding table when tied)."""
     T = len(tokens)
     cos, sin = plain_rope_table(range(T), cfg["head_dim"], cfg["theta"], cfg["scaling"])
     x = plain_embedding(w["model.embed_tokens.weight"], tokens)
     for l in range(cfg["layers"]):
-        x = plain_layer(x, w, f"model.layers.{l}.", cfg, cos, sin)
-    xn = plain_rmsnorm(x, w["model.norm.weight"], cfg["eps"])
+        x = plain_layer(x, w, f"model.layers.{l}.", cfg, cos, sin, rnd)
+    xn = rnd(plain_rmsnorm(x, w["model.norm.weight"], cfg["eps"]))
     head = w["model.embed_tokens.weight"] if cfg["tied"] else w["lm_head.weight"]
     return xn @ head.to(F32).T
+
+
+def round_weights_bf16(w: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    """What a bfloat16 engine makes of 32-bit stored weights: matrices rounded, norm weights kept."""
+    return {k: (v if v.dim() == 1 else bf16_rounding(v)) for k, v in w.items()}
 
 
 def load_plain(model_dir: str):

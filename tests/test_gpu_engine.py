@@ -1,0 +1,138 @@
+"""The engine against the plain implementation under every way of cutting the work, in 32-bit and
+in bfloat16: whole, tail decoded one by one, portions of changing size, mixed batches on so few
+pages that they are used again, long decoding, the first tokens; and through bin/trace_run."""
+import numpy as np
+import pytest
+
+import gpu_fixtures as gf
+import trace_tools as tt
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+CASES = ["a", "b"]
+
+
+def _play(case, dtype, steps, page_size=16):
+    reqs = gf.requests(case)
+    max_tokens = tt.max_tokens_of(steps, reqs)
+    engine = gf.make_engine(case, dtype, n_pages=max_tokens // page_size, page_size=page_size)
+    got = tt.run_in_process(engine, steps)
+    engine.cache.check_invariants()
+    assert not engine.cache.requests, "requests left open"
+    assert all(g.pool.free_count == g.pool.n_pages for g in engine.cache.groups), "pages were lost"
+    return got
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", CASES + ["a_named", "b_named"])
+def test_whole(case, dtype):
+    got = _play(case, dtype, tt.trace_whole(gf.requests(case)))
+    tt.compare(got, gf.plain_logits(case, dtype), gf.tolerance(dtype), f"whole {case} {dtype}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", CASES)
+def test_tail_decoded_one_by_one(case, dtype):
+    got = _play(case, dtype, tt.trace_tail_decode(gf.requests(case), tail=32))
+    tt.compare(got, gf.plain_logits(case, dtype), gf.tolerance(dtype), f"tail {case} {dtype}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", CASES)
+def test_portions_of_changing_size(case, dtype):
+    got = _play(case, dtype, tt.trace_portions(gf.requests(case)))
+    tt.compare(got, gf.plain_logits(case, dtype), gf.tolerance(dtype), f"portions {case} {dtype}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("seed", [1, 2])
+def test_mixed_batches_reusing_pages(case, dtype, seed):
+    reqs = gf.requests(case)
+    steps = tt.trace_mixed(reqs, seed=seed)
+    assert max(len(s["entries"]) for s in steps) >= 3
+    total = sum(tt.round_up(len(t)) for t in reqs.values())
+    assert tt.max_tokens_of(steps, reqs) < total, "the pool must be too small to hold all requests at once"
+    got = _play(case, dtype, steps)
+    tt.compare(got, gf.plain_logits(case, dtype), gf.tolerance(dtype), f"mixed {case} {dtype} seed {seed}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_cuts_agree_bitwise_in_32bit_and_closely_in_bf16(dtype):
+    """The same position computed whole, decoded and in portions: identical in 32-bit (every output
+    is one fixed chain of operations), within rounding in bfloat16."""
+    case = "b"
+    a = _play(case, dtype, tt.trace_whole(gf.requests(case)))
+    b = _play(case, dtype, tt.trace_portions(gf.requests(case)))
+    c = _play(case, dtype, tt.trace_mixed(gf.requests(case), seed=5))
+    for other in (b, c):
+        for key, row in other.items():
+            if dtype == "float32":
+                assert np.array_equal(row, a[key]), f"{key}: cuts differ in 32-bit"
+            else:
+                assert tt.rel_err(row, a[key]) < gf.TOL_BF16
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_and_first_tokens(dtype):
+    """A request decoded token by token from its very first token to the end of the context."""
+    case = "b"
+    toks = gf.requests(case)["r6"]              # 256 tokens = the whole context
+    steps = [{"step": i, "entries": [{"id": "r6", "tokens": [t], "want": [0]}], "end": ["r6"] if i == len(toks) - 1 else []}
+             for i, t in enumerate(toks)]
+    got = _play(case, dtype, steps)
+    assert len(got) == len(toks)
+    tt.compare(got, gf.plain_logits(case, dtype), gf.tolerance(dtype), f"long decode {dtype}")
+
+
+@pytest.mark.parametrize("page_size", [8, 64])
+def test_other_page_sizes(page_size):
+    case, dtype = "a", "float32"
+    reqs = gf.requests(case)
+    steps = tt.trace_mixed(reqs, seed=3)
+    max_tokens = tt.max_tokens_of(steps, reqs, unit=max(64, page_size))
+    engine = gf.make_engine(case, dtype, n_pages=max_tokens // page_size, page_size=page_size)
+    got = tt.run_in_process(engine, steps)
+    tt.compare(got, gf.plain_logits(case, dtype), gf.TOL_F32, f"page size {page_size}")
+
+
+def test_step_refuses_bad_input_and_leaves_state_unchanged():
+    from geneinfer_b200.cache import OutOfPages
+    from geneinfer_b200.engine.step import StepEntry
+    engine = gf.make_engine("a", "float32", n_pages=4)
+    engine.open("x")
+    engine.open("y")
+    with pytest.raises(IndexError):
+        engine.step([StepEntry("x", [256], [0])])                 # token outside the vocabulary
+    with pytest.raises(IndexError):
+        engine.step([StepEntry("x", [1, 2], [2])])                # wanted place outside the tokens
+    with pytest.raises(KeyError):
+        engine.step([StepEntry("nobody", [1], [0])])
+    with pytest.raises(ValueError):
+        engine.step([StepEntry("x", [1], [0]), StepEntry("x", [2], [0])])
+    with pytest.raises(IndexError):
+        engine.step([StepEntry("x", [1] * 129, [])])              # beyond the context length
+    engine.step([StepEntry("x", [1] * 40, [39])])                 # 3 of 4 pages
+    free = engine.cache.free_pages()
+    with pytest.raises(OutOfPages):
+        engine.step([StepEntry("x", [2], [0]), StepEntry("y", [3] * 20, [0])])   # y needs 2 pages, 1 is free
+    assert engine.cache.free_pages() == free and engine.length("x") == 40 and engine.length("y") == 0
+    engine.cache.check_invariants()
+    out = engine.step([StepEntry("x", [2], [0]), StepEntry("y", [3] * 16, [15])])
+    assert out.shape == (2, 256)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", CASES)
+def test_trace_run_tool(case, dtype, tmp_path):
+    """bin/trace_run as a child process: all four ways of cutting in one trace."""
+    reqs = gf.requests(case)
+    steps = []
+    for part in (tt.trace_whole(reqs), tt.trace_tail_decode(reqs), tt.trace_portions(reqs),
+                 tt.trace_mixed(reqs, seed=9)):
+        base = len(steps)
+        steps += [dict(s, step=base + s["step"]) for s in part]
+    vocab = gf.CASES[case][0]["vocab_size"]
+    got = tt.run_trace_tool(gf.model_dir(case), dtype, steps, tt.max_tokens_of(steps, reqs), str(tmp_path / "out"), vocab)
+    tt.compare(got, gf.plain_logits(case, dtype), gf.tolerance(dtype), f"trace_run {case} {dtype}")

@@ -1,0 +1,283 @@
+"""Each kernel alone against a plain 32-bit (or 64-bit) computation of the same operation, at sizes
+other than the engine's: widths and vocabularies that are no power of two, head sizes in steps of
+16, odd head counts and groups, page edges, a far key among hundreds, a window's edge."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model as pm
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def K():
+    from geneinfer_b200.ops import kernels
+    return kernels
+
+
+def dt(name):
+    return torch.float32 if name == "float32" else torch.bfloat16
+
+
+def close(got, want, dtype, what, f32_tol=2e-6, bf16_tol=1e-2):
+    got, want = got.float().cpu(), want.float().cpu()
+    assert torch.isfinite(got).all(), f"{what}: not finite"
+    tol = f32_tol if dtype == "float32" else bf16_tol
+    err = float((got - want).abs().max() / max(1.0, float(want.abs().max())))
+    assert err < tol, f"{what}: error {err:.3e} >= {tol:.1e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,D,V", [(1, 48, 37), (19, 200, 1000), (130, 2048 + 16, 511)])
+def test_embed(dtype, T, D, V):
+    g = torch.Generator().manual_seed(1)
+    table = torch.randn(V, D, generator=g).to(dt(dtype)).to(DEV)
+    tokens = torch.randint(0, V, (T,), generator=g, dtype=torch.int32).to(DEV)
+    out = torch.full((T, D), float("nan"), device=DEV)
+    K().embed(table, tokens, out, 1.0)
+    assert torch.equal(out.cpu(), table.float().cpu()[tokens.cpu().long()])
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,D,eps", [(1, 16, 1e-5), (7, 96, 1e-6), (33, 1000, 0.05), (5, 4096 + 48, 1e-5)])
+def test_rmsnorm(out_dtype, T, D, eps):
+    g = torch.Generator().manual_seed(2)
+    x = (torch.randn(T, D, generator=g) * 3).to(DEV)
+    w = (1 + 0.1 * torch.randn(D, generator=g)).to(DEV)
+    out = torch.full((T, D), float("nan"), dtype=dt(out_dtype), device=DEV)
+    K().rmsnorm(x, w, out, eps)
+    want = pm.plain_rmsnorm(x.cpu(), w.cpu(), eps)
+    close(out, want, out_dtype, "rmsnorm")
+    rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32, device=DEV)
+    out2 = torch.full((3, D), float("nan"), dtype=dt(out_dtype), device=DEV)
+    K().rmsnorm(x, w, out2, eps, rows)
+    assert torch.equal(out2.cpu(), out.cpu()[rows.cpu().long()]), "gathered rows differ from the same rows in place"
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,I", [(1, 16), (9, 160), (64, 1000)])
+def test_swiglu(out_dtype, T, I):
+    g = torch.Generator().manual_seed(3)
+    gu = (torch.randn(T, 2 * I, generator=g) * 4).to(DEV)
+    out = torch.full((T, I), float("nan"), dtype=dt(out_dtype), device=DEV)
+    K().swiglu(gu, out)
+    close(out, pm.plain_swiglu(gu.cpu()[:, :I], gu.cpu()[:, I:]), out_dtype, "swiglu")
+
+
+@pytest.mark.parametrize("a_dtype,w_dtype,c_dtype", [("float32", "float32", "float32"), ("bfloat16", "bfloat16", "float32"),
+                                                     ("bfloat16", "bfloat16", "bfloat16"), ("float32", "bfloat16", "float32")])
+@pytest.mark.parametrize("M,N,K_", [(1, 1, 1), (1, 384, 96), (7, 100, 33), (65, 129, 257), (200, 64, 1000)])
+def test_gemm_simt(a_dtype, w_dtype, c_dtype, M, N, K_):
+    g = torch.Generator().manual_seed(4)
+    a = torch.randn(M, K_, generator=g).to(dt(a_dtype)).to(DEV)
+    w = torch.randn(N, K_, generator=g).to(dt(w_dtype)).to(DEV)
+    want = a.float().cpu().double() @ w.float().cpu().double().T
+    out = torch.full((M, N), float("nan"), dtype=dt(c_dtype), device=DEV)
+    K().gemm_simt(a, w, out)
+    close(out, want, c_dtype, "gemm", f32_tol=1e-5)
+    if c_dtype == "float32":
+        base = torch.randn(M, N, generator=g).to(DEV)
+        acc = base.clone()
+        K().gemm_simt(a, w, acc, accumulate=True)
+        close(acc, want + base.cpu().double(), "float32", "gemm accumulate", f32_tol=1e-5)
+        if M > 1:   # a row's result does not depend on the rows around it
+            one = torch.empty((1, N), device=DEV)
+            K().gemm_simt(a[M - 1:M].contiguous(), w, one)
+            assert torch.equal(one[0], out[M - 1]), "a row alone differs from the row in the batch"
+
+
+def _paged(dtype, n_pages, Hkv, ps, hd):
+    kc = torch.full((n_pages, Hkv, ps, hd), float("nan"), dtype=dt(dtype), device=DEV)
+    return kc, kc.clone()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,Hkv,hd,ps,interleaved,rot", [(4, 2, 16, 16, False, 16), (3, 1, 32, 8, False, 32),
+                                                          (6, 3, 48, 4, True, 48), (2, 2, 64, 16, False, 32)])
+def test_rope_store(dtype, H, Hkv, hd, ps, interleaved, rot):
+    g = torch.Generator().manual_seed(5)
+    lens = [5, 1, 2 * ps + 3]                         # three requests; rows: a portion, one token, a portion over a page edge
+    first = [ps - 2, 3 * ps - 1, 0]                   # the first portion crosses a page edge, the single token ends a page
+    T = sum(lens)
+    qkv = torch.randn(T, (H + 2 * Hkv) * hd, generator=g).to(DEV)
+    max_pos = 4 * ps
+    freq = 1.0 / (10000.0 ** (np.arange(rot // 2, dtype=np.float64) * 2 / rot))
+    ang = np.arange(max_pos, dtype=np.float64)[:, None] * freq[None]
+    cos = torch.from_numpy(np.cos(ang).astype(np.float32)).to(DEV)
+    sin = torch.from_numpy(np.sin(ang).astype(np.float32)).to(DEV)
+    n_pages = 16
+    perm = torch.randperm(n_pages, generator=g).int()
+    tables = torch.full((3, 4), -1, dtype=torch.int32)
+    k_used = 0
+    for r in range(3):
+        for i in range((first[r] + lens[r] + ps - 1) // ps):
+            tables[r, i] = perm[k_used]
+            k_used += 1
+    positions = torch.cat([torch.arange(first[r], first[r] + lens[r]) for r in range(3)]).int()
+    row_req = torch.cat([torch.full((lens[r],), r) for r in range(3)]).int()
+    kc, vc = _paged(dtype, n_pages, Hkv, ps, hd)
+    q_out = torch.full((T, H * hd), float("nan"), dtype=dt(dtype), device=DEV)
+    K().rope_store(qkv, positions.to(DEV), row_req.to(DEV), tables.to(DEV), cos, sin, interleaved, q_out, kc, vc,
+                   H, Hkv, hd, ps)
+    x = qkv.cpu().reshape(T, H + 2 * Hkv, hd)
+
+    def rotate(v, p):      # [heads, hd]
+        out = v.clone()
+        c, s = cos.cpu()[p], sin.cpu()[p]
+        half = rot // 2
+        if interleaved:
+            a, b = v[:, 0:rot:2], v[:, 1:rot:2]
+            out[:, 0:rot:2], out[:, 1:rot:2] = a * c - b * s, a * s + b * c
+        else:
+            a, b = v[:, :half], v[:, half:rot]
+            out[:, :half], out[:, half:rot] = a * c - b * s, a * s + b * c
+        return out
+
+    written = torch.zeros(n_pages, ps, dtype=torch.bool)
+    for t in range(T):
+        p, r = int(positions[t]), int(row_req[t])
+        close(q_out[t].reshape(H, hd), rotate(x[t, :H], p), dtype, f"q row {t}")
+        page, off = int(tables[r, p // ps]), p % ps
+        close(kc[page, :, off], rotate(x[t, H:H + Hkv], p), dtype, f"k row {t}")
+        close(vc[page, :, off], x[t, H + Hkv:], dtype, f"v row {t}")
+        written[page, off] = True
+    untouched = ~written
+    assert torch.isnan(kc.float().cpu().permute(0, 2, 1, 3)[untouched]).all() and \
+        torch.isnan(vc.float().cpu().permute(0, 2, 1, 3)[untouched]).all(), \
+        "rows of other positions were written"
+
+
+def _attention_case(dtype, H, Hkv, hd, ps, ctx_lens, q_lens, window, seed, spike=None):
+    """Requests with ``ctx_lens`` cached positions of which the last ``q_lens`` are this step's
+    queries. Pages are scattered and unused pages hold NaN. ``spike`` = (request, key position):
+    that key is made to match every query of the request strongly."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(ctx_lens)
+    n_pages = sum((c + ps - 1) // ps for c in ctx_lens) + 3
+    perm = torch.randperm(n_pages, generator=g).int()
+    stride = max((c + ps - 1) // ps for c in ctx_lens)
+    tables = torch.full((R, stride), -1, dtype=torch.int32)
+    kc, vc = _paged(dtype, n_pages, Hkv, ps, hd)
+    ks, vs, qs, positions, row_req = [], [], [], [], []
+    used = 0
+    for r in range(R):
+        k = torch.randn(ctx_lens[r], Hkv, hd, generator=g)
+        v = torch.randn(ctx_lens[r], Hkv, hd, generator=g)
+        q = torch.randn(ctx_lens[r], H, hd, generator=g)        # a query for every position; only the last q_lens run
+        if spike and spike[0] == r:
+            direction = torch.randn(hd, generator=g)
+            direction /= direction.norm()
+            k[spike[1]] = 12.0 * direction
+            q[:] = q * 0.3 + 12.0 * direction
+            v[spike[1]] = 5.0
+        k, v, q = (t.to(dt(dtype)).float() for t in (k, v, q))
+        for i in range((ctx_lens[r] + ps - 1) // ps):
+            page = int(perm[used]); used += 1
+            tables[r, i] = page
+            n = min(ps, ctx_lens[r] - i * ps)
+            kc[page, :, :n] = k[i * ps:i * ps + n].transpose(0, 1).to(dt(dtype)).to(DEV)
+            vc[page, :, :n] = v[i * ps:i * ps + n].transpose(0, 1).to(dt(dtype)).to(DEV)
+        ks.append(k); vs.append(v)
+        lo = ctx_lens[r] - q_lens[r]
+        qs.append(q[lo:])
+        positions += list(range(lo, ctx_lens[r]))
+        row_req += [r] * q_lens[r]
+    q_all = torch.cat(qs).reshape(-1, H * hd).to(dt(dtype)).to(DEV)
+    out = torch.full_like(q_all, float("nan"))
+    scale = 1.0 / math.sqrt(hd)
+    K().attention_generic(q_all, kc, vc, out, torch.tensor(row_req, dtype=torch.int32, device=DEV),
+                          torch.tensor(positions, dtype=torch.int32, device=DEV), tables.to(DEV), H, Hkv, hd, ps, scale,
+                          window)
+    want = []
+    for r in range(R):
+        full_q = torch.zeros(ctx_lens[r], H, hd)
+        full_q[ctx_lens[r] - q_lens[r]:] = qs[r]
+        o = pm.plain_attention(full_q, ks[r], vs[r], scale, window)
+        want.append(o[ctx_lens[r] - q_lens[r]:])
+    return out.reshape(-1, H, hd), torch.cat(want)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,Hkv,hd,ps", [(4, 2, 16, 16), (3, 1, 32, 8), (6, 3, 48, 16), (8, 2, 128, 32), (2, 1, 256, 16),
+                                          (5, 5, 80, 4)])
+def test_attention_mixed_rows(dtype, H, Hkv, hd, ps):
+    # a whole prompt, a single decoded token deep in a context, a portion over page edges, position 0 alone
+    got, want = _attention_case(dtype, H, Hkv, hd, ps, ctx_lens=[37, 130, 3 * ps + 1, 1], q_lens=[37, 1, ps + 2, 1],
+                                window=None, seed=6)
+    close(got, want, dtype, "attention", f32_tol=5e-6, bf16_tol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("far", [0, 15, 16, 17, 255, 256, 511])
+def test_attention_far_key_stands_out(dtype, far):
+    """One key among 600 dominates the softmax: an engine that drops it, or reads a neighbour
+    instead, returns something else entirely."""
+    got, want = _attention_case(dtype, 4, 2, 64, 16, ctx_lens=[600], q_lens=[3], window=None, seed=7, spike=(0, far))
+    assert float(want.abs().mean()) > 2.0           # the spiked value dominates the output
+    close(got, want, dtype, f"far key {far}", f32_tol=5e-6, bf16_tol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [1, 5, 16, 33])
+def test_attention_window_edge(dtype, window):
+    """The key just outside the window is the strong one for the last query and just inside for
+    the one before: both sides of the edge are checked."""
+    ctx = 100
+    got, want = _attention_case(dtype, 4, 2, 32, 16, ctx_lens=[ctx], q_lens=[window + 2], window=window, seed=8,
+                                spike=(0, ctx - 1 - window))
+    close(got, want, dtype, f"window {window}", f32_tol=5e-6, bf16_tol=1e-2)
+    assert float(want[-1].abs().mean()) < 2.0 and float(want[-2].abs().mean()) > 2.0
+
+
+def test_attention_refuses_unsupported_head_size():
+    from geneinfer_b200.ops import KernelError
+    with pytest.raises(KernelError, match="head size"):
+        _attention_case("float32", 2, 1, 24, 16, [4], [4], None, 1)
+    with pytest.raises(KernelError, match="head size"):
+        _attention_case("float32", 2, 1, 512, 16, [4], [4], None, 1)
+
+
+@pytest.mark.parametrize("rows,V", [(1, 1), (3, 1000), (5, 128256), (2, 50257)])
+def test_argmax(rows, V):
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn(rows, V, generator=g)
+    if V > 10:
+        logits[0, 7] = logits[0, V - 3] = 50.0       # a tie: the lower index wins
+    out = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+    K().argmax(logits.to(DEV), out)
+    want = [int(np.argmax(logits[r].numpy())) for r in range(rows)]
+    assert out.cpu().tolist() == want
+
+
+@pytest.mark.parametrize("V", [5, 384, 1000, 50257])
+@pytest.mark.parametrize("temperature,top_k,top_p", [(0.8, 0, 1.0), (1.0, 5, 1.0), (0.7, 0, 0.9), (1.3, 50, 0.5),
+                                                     (1.0, 1, 1.0), (1.0, 0, 1e-6), (2.0, 3, 0.99)])
+def test_sample_matches_plain_sampler(V, temperature, top_k, top_p):
+    g = torch.Generator().manual_seed(10)
+    rows = 24
+    logits = (torch.randn(rows, V, generator=g) * 2.5)
+    logits[3] = torch.round(logits[3])                # many equal probabilities: index order decides
+    logits[4] = 0.0                                   # all equal
+    us = torch.rand(rows, generator=g)
+    us[0], us[1] = 0.0, float(np.float32(1.0) - np.float32(2.0 ** -24))
+    out = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(rows * V, device=DEV)
+    K().sample(logits.to(DEV), scratch, torch.full((rows,), temperature, device=DEV),
+               torch.full((rows,), top_k, dtype=torch.int32, device=DEV), torch.full((rows,), top_p, device=DEV),
+               us.to(DEV), out)
+    got = out.cpu().tolist()
+    sampler = pm.PlainSampler(temperature, top_k, top_p)
+    bad = []
+    for r in range(rows):
+        want = sampler.sample(logits[r].numpy(), float(us[r]))
+        if got[r] != want:
+            # a draw that falls within rounding of a boundary of the cumulative sum may land on either side
+            lo = pm.PlainSampler(temperature, top_k, top_p).sample(logits[r].numpy(), max(0.0, float(us[r]) - 1e-6))
+            hi = pm.PlainSampler(temperature, top_k, top_p).sample(logits[r].numpy(), min(0.99999994, float(us[r]) + 1e-6))
+            if got[r] not in (lo, hi):
+                bad.append((r, got[r], want))
+    assert not bad, f"rows (row, got, want): {bad}"
