@@ -1,0 +1,318 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at the Llama-3.2-1B shape with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 and context 8192, timed on
+the device over exactly K decode steps (one step = one token for every request of the batch);
+``e2e`` is the same through the Python entry point (``Engine.step``: token ids from the host in,
+sampled ids back to the host, every step). ``prefill`` is one 2,048-token prompt in one step;
+``roofline`` relates the decode step's bytes (every weight once plus the cache of the live
+requests) to the measured copy bandwidth; ``points`` holds decode at batch 1 and 64.
+This engine runs on one GPU: for --gpus > 1 it prints one line saying so and exits with 2.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: the Llama-3.2-1B shape.
+LLAMA_1B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_act": "silu",
+    "hidden_size": 2048, "intermediate_size": 8192, "num_hidden_layers": 16, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 64, "vocab_size": 128256, "max_position_embeddings": 131072,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+}
+CONTEXT = 8192
+PAGE = 16
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                p = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            out.update({k: float(v) for k, v in p.items() if k in out and isinstance(v, (int, float))})
+            out["source"] = "measured"
+            return out
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def model_folder(config, seed=1):
+    """The random-weights model folder (made once per box under the temporary directory)."""
+    from geneinfer_b200.weights import write_random_model
+    tag = f"geneinfer_bench_{config['num_hidden_layers']}x{config['hidden_size']}_{seed}_{os.getuid()}"
+    path = os.path.join(tempfile.gettempdir(), tag)
+    if not (os.path.isfile(os.path.join(path, "model.safetensors")) and os.path.isfile(os.path.join(path, "done"))):
+        t0 = time.time()
+        print(f"[bench] writing random bf16 weights to {path}", file=sys.stderr, flush=True)
+        write_random_model(config, seed, path, "bfloat16", std=0.02, norm_mean=1.0, norm_std=0.02)
+        open(os.path.join(path, "done"), "w").close()
+        print(f"[bench] wrote them in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+    return path
+
+
+def step_bytes(model, cfg, batch, context):
+    """Bytes a decode step has to read: every weight it uses once, and the cache of the live requests."""
+    elt = 2
+    kv_per_token = 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * elt * cfg["num_hidden_layers"]
+    return model.weight_bytes() + batch * context * kv_per_token
+
+
+def prefill_flops(cfg, T):
+    D, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    A = cfg["num_attention_heads"] * cfg["head_dim"]
+    K = cfg["num_key_value_heads"] * cfg["head_dim"]
+    gemm = 2 * T * (D * (A + 2 * K) + A * D + 2 * D * I + I * D) * L
+    attention = 2 * T * T * cfg["head_dim"] * cfg["num_attention_heads"] * L      # causal: half of 2 products
+    head = 2 * D * cfg["vocab_size"]
+    return gemm + attention + head
+
+
+def fill_cache(engine, keys, length):
+    """Gives each request ``length`` cached positions of random keys and values (setup, untimed):
+    decoding reads them exactly as it would read real ones."""
+    for t in engine.group_pages:
+        t.normal_(0.0, 1.0)
+    for key in keys:
+        rc = engine.open(key)
+        engine.cache.reserve(rc, length)
+        engine.cache.advance(rc, length)
+
+
+def time_decode_device(engine, batch, context, steps, warmup, vocab):
+    """K decode steps of the step function with greedy sampling on the device, timed with CUDA events."""
+    import torch
+    from geneinfer_b200.engine.step import StepEntry
+    from geneinfer_b200.ops import kernels
+    keys = [f"b{i}" for i in range(batch)]
+    fill_cache(engine, keys, context - steps - warmup)
+    ids = torch.zeros(batch, dtype=torch.int32, device=engine.device)
+    g = torch.Generator().manual_seed(3)
+    toks = torch.randint(0, vocab, (steps + warmup, batch), generator=g).tolist()
+
+    def one(i):
+        logits = engine.step([StepEntry(k, [toks[i][j]], [0]) for j, k in enumerate(keys)])
+        kernels.argmax(logits, ids)
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = kernels.launch_count()
+    start.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    launches = kernels.launch_count() - launches0
+    for k in keys:
+        engine.close(k)
+    return ms / steps, launches
+
+
+def time_decode_e2e(llm, batch, context, steps, warmup, vocab):
+    """The same decode steps through Engine.step(): host token ids in, sampled ids out, every step."""
+    import torch
+    from geneinfer_b200 import SamplingParams
+    import numpy as np
+    rng = np.random.default_rng(5)
+    sched = llm.scheduler
+    prefill = context - steps - warmup - 1
+    for t in llm.steps.group_pages:
+        t.normal_(0.0, 1.0)
+    rids = []
+    for i in range(batch):
+        prompt = [int(t) for t in rng.integers(0, vocab, prefill + 1)]
+        rids.append(llm.submit(prompt, 0, SamplingParams(0.0)))
+    sched._admit()
+    for job in sched.running:                     # setup, untimed: the prompt's cache is filled with random values
+        llm.steps.cache.reserve(job.cache, prefill)
+        llm.steps.cache.advance(job.cache, prefill)
+        job.fed = prefill
+    for _ in range(warmup):
+        llm.step()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record()
+    for _ in range(steps):
+        llm.step()
+    end.record()
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    assert all(len(llm.result(r).generated_tokens) == warmup + steps for r in rids)
+    h2d = llm.steps._desc_size * 4
+    d2h = batch * 4
+    for job in list(sched.running):
+        sched._finish(job)
+    return wall_ms / steps, h2d, d2h
+
+
+def time_prefill(engine, tokens, warmup, vocab):
+    import torch
+    from geneinfer_b200.engine.step import StepEntry
+    g = torch.Generator().manual_seed(7)
+    times = []
+    for i in range(warmup + 3):
+        prompt = torch.randint(0, vocab, (tokens,), generator=g).tolist()
+        engine.open("p")
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.step([StepEntry("p", prompt, [tokens - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(start.elapsed_time(end))
+        engine.close("p")
+    return sorted(times)[len(times) // 2]
+
+
+def run_ours(args):
+    import torch
+    from geneinfer_b200 import Engine
+    cfg = dict(LLAMA_1B)
+    layers_full = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    pk = peaks()
+    folder = model_folder(cfg)
+    vocab = cfg["vocab_size"]
+    batch = 8
+    pages_per_request = CONTEXT // PAGE
+
+    def make(b):
+        return Engine(folder, dtype="bfloat16", max_seq_len=CONTEXT, page_size=PAGE, kv_pages=b * pages_per_request,
+                      max_running=b, step_tokens=PREFILL_TOKENS, prefix_cache=False)
+
+    llm = make(batch)
+    model = llm.model
+    clocks = ClockSampler()
+    clocks.start()
+    ms_step, launches = time_decode_device(llm.steps, batch, CONTEXT, args.steps, args.warmup, vocab)
+    clock_record = clocks.stop()
+    ms_e2e, h2d, d2h = time_decode_e2e(llm, batch, CONTEXT, args.steps, args.warmup, vocab)
+    ms_prefill = time_prefill(llm.steps, PREFILL_TOKENS, max(1, args.warmup), vocab)
+    bytes_step = step_bytes(model, cfg, batch, CONTEXT)
+    achieved = bytes_step / (ms_step * 1e-3) / 1e9
+    flops = prefill_flops(cfg, PREFILL_TOKENS)
+    del llm
+    torch.cuda.empty_cache()
+
+    points = {}
+    for b in (1, 64):
+        e = make(b)
+        ms_b, _ = time_decode_device(e.steps, b, CONTEXT, max(4, args.steps // 2), args.warmup, vocab)
+        points[f"decode_b{b}"] = round(b / (ms_b * 1e-3), 1)
+        del e
+        torch.cuda.empty_cache()
+
+    value = batch / (ms_step * 1e-3)
+    line = {
+        "metric": "decode tok/s at batch 8, context 8192 (Llama-3.2-1B shape, random bf16 weights)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights N(0,0.02), random token ids, random cache contents",
+        "impl": "ours",
+        "config": {
+            "model": "Llama-3.2-1B shape", "global_batch": batch, "seq_len": CONTEXT, "parallelism": "single GPU",
+            "layers": cfg["num_hidden_layers"], "layers_of_named_config": layers_full, "hidden": cfg["hidden_size"],
+            "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "intermediate": cfg["intermediate_size"], "vocab": vocab, "tied_head": True, "page_size": PAGE,
+            "rope": "theta 500000, llama3 32/1/4/8192", "rms_norm_eps": cfg["rms_norm_eps"],
+            "l2": "step inputs (weights + cache) are larger than L2", "peaks": pk["source"],
+        },
+        "e2e": {"value": round(batch / (ms_e2e * 1e-3), 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": round(ms_e2e, 4)},
+        "gpu_launches": launches,
+        "prefill": {"value": round(PREFILL_TOKENS / (ms_prefill * 1e-3), 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(ms_prefill, 3), "frac": round(flops / (ms_prefill * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clock_record,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def run_reference(args):
+    # The reference is a CMake project without setup.py or pyproject.toml:
+    # `pip install --no-index --target baseline/_ref <reference>` answers "not installable".
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "pip cannot install the reference: it is a CMake C++ project with neither setup.py nor pyproject.toml"}),
+          flush=True)
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0 = all)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(3, args.warmup)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

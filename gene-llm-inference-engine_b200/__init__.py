@@ -6,7 +6,8 @@ step function -> scheduler -> sampled tokens, with hand-written CUDA kernels on 
 from . import architectures  # noqa: F401  (fills the architecture registry)
 from . import cache, config, weights
 
-__all__ = ["cache", "config", "weights", "load_model", "StepEngine", "StepEntry"]
+__all__ = ["cache", "config", "weights", "load_model", "StepEngine", "StepEntry", "Engine", "Scheduler",
+           "SchedulerConfig", "GenerationRequest", "RequestResult", "SamplingParams", "RandomStream"]
 
 
 def __getattr__(name):
@@ -18,7 +19,13 @@ def __getattr__(name):
     if name in ("StepEngine", "StepEntry"):
         from .engine import step as _step
         return getattr(_step, name)
-    if name in ("Generator", "GenerationRequest", "SamplingParams", "generate"):
-        from .engine import generate as _gen
-        return getattr(_gen, name)
+    if name == "Engine":
+        from .engine.generate import Engine
+        return Engine
+    if name in ("Scheduler", "SchedulerConfig", "GenerationRequest", "RequestResult"):
+        from .engine import scheduler as _sched
+        return getattr(_sched, name)
+    if name in ("SamplingParams", "RandomStream"):
+        from .sampling import params as _params
+        return getattr(_params, name)
     raise AttributeError(name)

@@ -23,7 +23,17 @@ def dtype_code(dtype: torch.dtype) -> int:
         raise KernelError(f"unsupported dtype {dtype} (float32 and bfloat16 only)") from None
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far by this process (each wrapper call launches one)."""
+    return _launches
+
+
 def _stream() -> int:
+    global _launches
+    _launches += 1
     return torch.cuda.current_stream().cuda_stream
 
 

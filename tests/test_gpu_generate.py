@@ -1,0 +1,113 @@
+"""Generation through the Python entry point and the command line against the plain implementation:
+greedy and temperature sampling with fixed seeds, several requests at once, few pages."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import gpu_fixtures as gf
+import plain_model as pm
+import tiny_configs as tc
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _plain_continue(case, dtype, prompt, n_new, sampler, stop_ids=()):
+    w, cfg = pm.load_plain(gf.model_dir(case))
+    if dtype == "bfloat16":
+        w = pm.round_weights_bf16(w)
+    rnd = pm.bf16_rounding if dtype == "bfloat16" else pm.no_rounding
+    tokens, out, gaps = list(prompt), [], []
+    for _ in range(n_new):
+        logits = pm.plain_forward(w, cfg, tokens, rnd)[-1].numpy()
+        top2 = np.sort(logits)[-2:]
+        gaps.append(float(top2[1] - top2[0]))
+        nxt = sampler.sample(logits)
+        out.append(nxt)
+        tokens.append(nxt)
+        if nxt in stop_ids:
+            break
+    return out, gaps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_of_tiny_a(dtype):
+    """BASELINE's first configuration: 3 requests of 7/16/33 random ids, 16 greedy tokens each."""
+    from geneinfer_b200 import Engine
+    engine = Engine(gf.model_dir("a"), dtype=dtype, max_running=3, kv_pages=12, step_tokens=24)
+    prompts = [tc.random_tokens(n, 256, 40 + n) for n in (7, 16, 33)]
+    got = engine.generate(prompts, max_new_tokens=16, temperature=0.0)
+    for p, g in zip(prompts, got):
+        want, gaps = _plain_continue("a", dtype, p, 16, pm.PlainSampler(0.0))
+        assert len(g) == 16
+        if g != want:       # only a near-tie of the two best logits may differ, and only from there on
+            i = next(k for k in range(16) if g[k] != want[k])
+            assert gaps[i] < (1e-4 if dtype == "float32" else 5e-2), f"token {i}: {g} != {want}"
+    assert engine.stats.steps > 16 and not engine.steps.cache.requests
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_sampling_of_tiny_b(dtype):
+    """BASELINE's second configuration: 5 requests of 1/5/24/64/100 ids, temperature 0.8, fixed seeds."""
+    from geneinfer_b200 import Engine
+    engine = Engine(gf.model_dir("b"), dtype=dtype, max_running=4, kv_pages=20, step_tokens=48, prefill_chunk=32)
+    prompts = [tc.random_tokens(n, 384, 60 + n) for n in (1, 5, 24, 64, 100)]
+    got = engine.generate(prompts, max_new_tokens=12, temperature=0.8, seed=77)
+    agree = 0
+    for i, (p, g) in enumerate(zip(prompts, got)):
+        want, _ = _plain_continue("b", dtype, p, 12, pm.PlainSampler(0.8, 0, 1.0, seed=77 + i))
+        assert len(g) == 12
+        agree += g == want
+        if dtype == "float32":
+            assert g == want, f"request {i}: {g} != {want}"
+    assert agree >= (5 if dtype == "float32" else 3)     # bfloat16: a draw next to a boundary may fall either way
+    assert engine.stats.preemptions >= 0 and engine.steps.cache.free_pages() + engine.cached_blocks() == 20
+
+
+def test_top_k_top_p_and_stop_ids_through_the_engine():
+    from geneinfer_b200 import Engine, SamplingParams
+    engine = Engine(gf.model_dir("b"), dtype="float32", max_running=2, kv_pages=16)
+    prompt = tc.random_tokens(9, 384, 5)
+    want, _ = _plain_continue("b", "float32", prompt, 10, pm.PlainSampler(1.1, 20, 0.8, seed=3))
+    rid = engine.submit(prompt, len(prompt) + 9, SamplingParams(1.1, 20, 0.8, 3))
+    stop = want[4]
+    rid2 = engine.submit(prompt, 0, SamplingParams(1.1, 20, 0.8, 3), stop_ids=[stop])
+    engine.run_until_idle()
+    assert engine.result(rid).generated_tokens == want
+    first = want.index(stop)
+    assert engine.result(rid2).generated_tokens == want[:first + 1] and engine.result(rid2).stopped_by_end_token
+    assert engine.result(rid2).cached_tokens == 0 and engine.cached_blocks() >= 0
+
+
+def test_prefix_cache_gives_the_same_tokens():
+    from geneinfer_b200 import Engine
+    common = tc.random_tokens(40, 256, 9)
+    prompts = [common + tc.random_tokens(5, 256, 90 + i) for i in range(3)]
+    with_cache = Engine(gf.model_dir("a"), dtype="float32", max_running=1, kv_pages=24, prefix_cache=True)
+    without = Engine(gf.model_dir("a"), dtype="float32", max_running=1, kv_pages=24, prefix_cache=False)
+    assert with_cache.generate(prompts, 8) == without.generate(prompts, 8)
+    assert with_cache.stats.prefix_tokens == 2 * 32 and without.stats.prefix_tokens == 0
+    assert with_cache.cached_blocks() > 0
+    with_cache.clear_prefix_cache()
+    assert with_cache.steps.cache.free_pages() == 24
+
+
+def test_command_line(tmp_path):
+    prompt = tc.random_tokens(7, 256, 47)
+    want, _ = _plain_continue("a", "float32", prompt, 6, pm.PlainSampler(0.0))
+    dump = tmp_path / "tokens.txt"
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "gi_generate"), "--model", gf.model_dir("a"), "--prompt-ids",
+           " ".join(map(str, prompt)), "--steps", str(len(prompt) + 5), "--temperature", "0", "--weights", "f32",
+           "--dump-tokens", str(dump)]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr
+    lines = dump.read_text().splitlines()
+    assert [int(t) for t in lines[0].split()] == prompt and [int(t) for t in lines[1].split()] == want
+    assert p.stdout.strip().endswith(" ".join(map(str, want))) and "[stats]" in p.stderr
+    bad = subprocess.run(cmd[:4] + ["--prompt", "hello"], capture_output=True, text=True)
+    assert bad.returncode == 2 and "tokenizer" in bad.stderr
+    missing = subprocess.run(cmd[:2] + ["--model", str(tmp_path / "nothing"), "--prompt-ids", "1"], capture_output=True, text=True)
+    assert missing.returncode == 1 and "config.json" in missing.stderr
