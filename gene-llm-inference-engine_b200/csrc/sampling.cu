@@ -340,3 +340,65 @@ extern "C" int gi_sample(const float* logits, float* probs_scratch, int rows, in
         logits, probs_scratch, V, temperature, top_k, top_p, uniform, out);
     return check_launch("sample");
 }
+
+// ------------------------------------------------------------------------------------------------
+// The allocation-free variant of gi_sample (declared and explained in no_alloc.h).
+#include "no_alloc.h"
+
+#include <mutex>
+
+namespace gi {
+
+// The work area of gi_sample_no_alloc. In host code this name is only a handle for the runtime's
+// symbol table, not a device address: the address is looked up once per device below.
+static __device__ __align__(256) float g_sample_work_area[GI_SAMPLE_NO_ALLOC_MAX_FLOATS];
+
+constexpr int kMaxDevices = 64;
+static float* g_work_area_address[kMaxDevices] = {};
+static std::mutex g_work_area_mutex;
+
+// Device address of the work area on the current device; looked up on the first call per device.
+static int work_area_for_current_device(float** out) {
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) {
+        set_error("sample_no_alloc: cudaGetDevice failed: %s", cudaGetErrorString(e));
+        return 1;
+    }
+    if (device < 0 || device >= kMaxDevices) {
+        set_error("sample_no_alloc: device index %d is outside the supported range 0..%d", device, kMaxDevices - 1);
+        return 2;
+    }
+    std::lock_guard<std::mutex> lock(g_work_area_mutex);
+    if (g_work_area_address[device] == nullptr) {
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_sample_work_area);
+        if (e != cudaSuccess || ptr == nullptr) {
+            set_error("sample_no_alloc: cudaGetSymbolAddress failed on device %d: %s", device, cudaGetErrorString(e));
+            return 1;
+        }
+        g_work_area_address[device] = ptr;
+    }
+    *out = g_work_area_address[device];
+    return 0;
+}
+
+}  // namespace gi
+
+extern "C" int gi_sample_no_alloc(const float* logits, int rows, int vocab, const float* temperature,
+                                  const int* top_k, const float* top_p, const float* uniform, int* out,
+                                  void* stream) {
+    if (rows == 0) return 0;
+    GI_REQUIRE(rows > 0 && vocab > 0, "sample_no_alloc: sizes must be positive (rows=%d, vocab=%d)", rows, vocab);
+    const long long need = static_cast<long long>(rows) * vocab;
+    GI_REQUIRE(need <= GI_SAMPLE_NO_ALLOC_MAX_FLOATS,
+               "sample_no_alloc: %d rows x %d vocabulary = %lld floats exceed the built-in work area of %d floats; "
+               "sample fewer rows per call or use gi_sample with a scratch buffer of your own",
+               rows, vocab, need, GI_SAMPLE_NO_ALLOC_MAX_FLOATS);
+    float* work = nullptr;
+    const int rc = work_area_for_current_device(&work);
+    if (rc != 0) return rc;
+    sample_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        logits, work, vocab, temperature, top_k, top_p, uniform, out);
+    return check_launch("sample_no_alloc");
+}
