@@ -1,0 +1,447 @@
+// bfloat16 matrix product on the 5th-generation tensor cores: C (+)= A[M,K] * W[N,K]^T, 32-bit
+// accumulation in tensor memory.
+//
+// One CTA computes a 128 x BLOCK_Q tile. Both operands are K-major, so each is fetched by TMA as
+// [rows, 64] boxes with the 128-byte swizzle that tcgen05.mma reads directly. Three roles:
+//   warp 0      producer: one lane issues the TMA loads of a pipeline of kStages stages;
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (4 x K=16 per stage) and
+//               commits each stage back to the producer, and the finished tile to the epilogue;
+//   warps 2..5  epilogue: tcgen05.ld of the accumulators (one lane = one row of the tile), then
+//               store / accumulate into C in 32-bit, or round to bfloat16.
+// The 128-row operand "P" and the BLOCK_Q-row operand "Q" can be either matrix: for many tokens P
+// is the activations (C[p, q]); for few tokens the weights take the 128-row side and the tokens
+// become the narrow side (C[q, p]), so that a decode step streams every weight once at full tile
+// efficiency. The split over K (few tokens, narrow weight matrices) writes partial tiles to a
+// workspace; the CTA that arrives last adds them in split order, so results do not depend on
+// the order of arrival.
+//
+// Every wait on an mbarrier is bounded: when a limit is hit the kernel records a code in the
+// status word, stops issuing work, drains its own copies with bounded waits, frees its tensor
+// memory and returns; the host reads the status word with gi_gemm_tc_status().
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace gi {
+
+constexpr int kBlockP = 128;
+constexpr int kBlockK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kThreads = 192;
+constexpr unsigned long long kWaitCycles = 4000000000ull;   // about two seconds
+
+enum TcError : int { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3, kErrDrain = 4 };
+
+// ------------------------------------------------------------------------------------------ PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit is hit or another role has already given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart; version 1 (bit 46), layout type 2 = SWIZZLE_128B (bits 61..63).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;                     // leading byte offset: unused with swizzle
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;             // stride byte offset between 8-row groups
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+template <int BLOCK_Q>
+struct TcConfig {
+    static constexpr int kStageBytesP = kBlockP * kBlockK * 2;
+    static constexpr int kStageBytesQ = BLOCK_Q * kBlockK * 2;
+    static constexpr int kStageBytes = kStageBytesP + kStageBytesQ;
+    static constexpr int kStages = (BLOCK_Q >= 256) ? 4 : (BLOCK_Q >= 128) ? 6 : 8;
+    static constexpr int kTmemCols = BLOCK_Q < 32 ? 32 : BLOCK_Q;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
+    // instruction descriptor: D f32 (bits 4..5 = 1), A and B bf16 (bits 7..9, 10..12 = 1), both
+    // K-major, N >> 3 at bits 17..22, M >> 4 at bits 24..28
+    static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BLOCK_Q >> 3) << 17) |
+                                       (static_cast<uint32_t>(kBlockP >> 4) << 24);
+};
+
+struct TcParams {
+    void* C;
+    int c_bf16;              // 0: C is float, 1: C is bfloat16
+    int accumulate;          // C += product (float C only)
+    int rows_p, rows_q, K;
+    long long stride_p, stride_q;   // C[p * stride_p + q * stride_q]
+    int k_blocks_per_split;
+    int splits;
+    float* workspace;        // [tile][split][BLOCK_Q][128] partial tiles when splits > 1
+    unsigned* counters;      // one per tile, zero between launches
+    int* status;
+};
+
+template <int BLOCK_Q>
+__device__ __forceinline__ void store_row_chunk(const TcParams& p, int row_p, int q0, const float* v) {
+    // v[j] belongs to (row_p, q0 + j), j < 16
+    if (row_p >= p.rows_p) return;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int q = q0 + j;
+        if (q >= p.rows_q) break;
+        const long long idx = static_cast<long long>(row_p) * p.stride_p + static_cast<long long>(q) * p.stride_q;
+        if (p.c_bf16) {
+            static_cast<__nv_bfloat16*>(p.C)[idx] = __float2bfloat16_rn(v[j]);
+        } else {
+            float* c = static_cast<float*>(p.C) + idx;
+            *c = p.accumulate ? *c + v[j] : v[j];
+        }
+    }
+}
+
+template <int BLOCK_Q>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const TcParams p) {
+    using Cfg = TcConfig<BLOCK_Q>;
+    constexpr int kStages = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+    // bars[0..kStages) full, [kStages..2kStages) empty, [2kStages] accumulator ready
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* last_flag = const_cast<int*>(abort_flag) + 1;
+    int* epi_abort = last_flag + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_p = blockIdx.x, tile_q = blockIdx.y, split = blockIdx.z;
+    const int total_kb = (p.K + kBlockK - 1) / kBlockK;
+    const int kb_begin = split * p.k_blocks_per_split;
+    const int kb_end = min(total_kb, kb_begin + p.k_blocks_per_split);
+    const int n_kb = max(0, kb_end - kb_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);
+            mbar_init(smem_u32(&bars[kStages + s]), 1);
+        }
+        mbar_init(smem_u32(&bars[2 * kStages]), 1);
+        *abort_flag = 0;
+        *last_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % kStages;
+                const uint32_t parity = ((i / kStages) & 1) ^ 1;
+                if (!mbar_wait(smem_u32(&bars[kStages + s]), parity, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, kErrProducerWait); }
+                    break;
+                }
+                const uint32_t full = smem_u32(&bars[s]);
+                mbar_expect_tx(full, Cfg::kStageBytes);
+                uint8_t* stage = smem + s * Cfg::kStageBytes;
+                const int k0 = (kb_begin + i) * kBlockK;
+                tma_load_2d(smem_u32(stage), &map_p, k0, tile_p * kBlockP, full);
+                tma_load_2d(smem_u32(stage + Cfg::kStageBytesP), &map_q, k0, tile_q * BLOCK_Q, full);
+                issued = i + 1;
+            }
+            if (*abort_flag) {
+                // drain: every copy this lane issued must have landed before the CTA may exit
+                const int first = max(0, issued - kStages);
+                for (int i = first; i < issued; ++i) {
+                    const unsigned long long t0 = clock64();
+                    while (!mbar_try_wait(smem_u32(&bars[i % kStages]), (i / kStages) & 1)) {
+                        if (clock64() - t0 > kWaitCycles) { atomicCAS(p.status, 0, kErrDrain); break; }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % kStages;
+                if (!mbar_wait(smem_u32(&bars[s]), (i / kStages) & 1, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, kErrMmaWait); }
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes);
+                const uint64_t desc_p = umma_desc(a_addr);
+                const uint64_t desc_q = umma_desc(a_addr + Cfg::kStageBytesP);
+#pragma unroll
+                for (int k = 0; k < kBlockK / 16; ++k) {
+                    // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in the address field
+                    umma_bf16(tmem_base, desc_p + 2 * k, desc_q + 2 * k, Cfg::kIdesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&bars[kStages + s]));      // frees the stage once the MMAs have read it
+            }
+            if (ok) umma_commit(smem_u32(&bars[2 * kStages]));  // accumulator complete
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..5)
+        const int lane_group = warp & 3;                        // the TMEM lanes this warp may read
+        const int row_in_tile = lane_group * 32 + lane;
+        const int row_p = tile_p * kBlockP + row_in_tile;
+        bool have = n_kb > 0;
+        if (have && !mbar_wait(smem_u32(&bars[2 * kStages]), 0, abort_flag)) {
+            if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, kErrEpilogueWait); }
+            have = false;
+        }
+        tc_fence_after();
+        // one decision for all 128 epilogue threads (they meet at named barriers below)
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) *epi_abort = *abort_flag;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool aborted = *epi_abort != 0;
+        if (!aborted) {
+            constexpr int kChunks = (BLOCK_Q + 15) / 16;
+            if (p.splits == 1) {
+#pragma unroll 1
+                for (int c = 0; c < kChunks; ++c) {
+                    uint32_t r[16];
+                    float v[16];
+                    if (have) {
+                        tmem_ld_x16(tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + c * 16, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                    }
+                    store_row_chunk<BLOCK_Q>(p, row_p, tile_q * BLOCK_Q + c * 16, v);
+                }
+            } else {
+                // partial tile -> workspace [tile][split][q][128 rows]; the last CTA of the tile sums all splits
+                const int tile_id = tile_q * gridDim.x + tile_p;
+                float* ws_tile = p.workspace + static_cast<size_t>(tile_id) * p.splits * BLOCK_Q * kBlockP;
+                float* mine = ws_tile + static_cast<size_t>(split) * BLOCK_Q * kBlockP;
+#pragma unroll 1
+                for (int c = 0; c < kChunks; ++c) {
+                    uint32_t r[16];
+                    if (have) {
+                        tmem_ld_x16(tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + c * 16, r);
+                        tmem_ld_wait();
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        mine[(c * 16 + j) * kBlockP + row_in_tile] = have ? __uint_as_float(r[j]) : 0.f;
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    const unsigned arrived = atomicAdd(&p.counters[tile_id], 1u);
+                    *last_flag = (arrived == static_cast<unsigned>(p.splits - 1)) ? 1 : 0;
+                    if (*last_flag) p.counters[tile_id] = 0;        // ready for the next launch
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*last_flag) {
+                    __threadfence();
+#pragma unroll 1
+                    for (int c = 0; c < kChunks; ++c) {
+                        float v[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                        for (int s = 0; s < p.splits; ++s) {
+                            const float* part = ws_tile + static_cast<size_t>(s) * BLOCK_Q * kBlockP;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] += __ldcg(&part[(c * 16 + j) * kBlockP + row_in_tile]);
+                        }
+                        store_row_chunk<BLOCK_Q>(p, row_p, tile_q * BLOCK_Q + c * 16, v);
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) == cudaSuccess &&
+            status == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+        }
+    }
+    return fn;
+}
+
+// A [rows, K] row-major bf16 matrix viewed as boxes of [box_rows, 64] with 128-byte swizzle; reads
+// beyond rows or K give zeros.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("gemm_tc: cuTensorMapEncodeTiled is not available from the driver"); return 1; }
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("gemm_tc: cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r)); return 1; }
+    return 0;
+}
+
+template <int BLOCK_Q>
+static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParams& p, dim3 grid, cudaStream_t st) {
+    using Cfg = TcConfig<BLOCK_Q>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BLOCK_Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) { set_error("gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::kSmemBytes, cudaGetErrorString(e)); return 1; }
+        configured = true;
+    }
+    gemm_tc_kernel<BLOCK_Q><<<grid, kThreads, Cfg::kSmemBytes, st>>>(mp, mq, p);
+    return check_launch("gemm_tc");
+}
+
+}  // namespace gi
+
+using namespace gi;
+
+// C[M,N] (+)= A[M,K] * W[N,K]^T, A and W bfloat16 row-major with row strides lda, ldw (elements),
+// C float (optionally accumulated into) or bfloat16 with row stride ldc.
+//   swap = 0: tokens on the 128-row side (tile 128 x block_q over [M, N]);
+//   swap = 1: weights on the 128-row side, block_q >= tokens on the narrow side.
+//   splits > 1 (swap only): K is cut into `splits` ranges; workspace must hold
+//   tiles * splits * 128 * block_q floats and counters one zeroed word per tile.
+extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int accumulate, int M, int N, int K,
+                          long long lda, long long ldw, long long ldc, int swap, int block_q, int splits,
+                          void* workspace, long long workspace_floats, void* counters, int n_counters, void* status,
+                          void* stream) {
+    if (M == 0 || N == 0) return 0;
+    GI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: sizes must be positive (M=%d, N=%d, K=%d)", M, N, K);
+    GI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
+               "gemm_tc: K=%d and the row strides (%lld, %lld) must be multiples of 8 (16-byte rows for TMA)", K, lda, ldw);
+    GI_REQUIRE((reinterpret_cast<uintptr_t>(A) % 16 == 0) && (reinterpret_cast<uintptr_t>(W) % 16 == 0),
+               "gemm_tc: operands must be 16-byte aligned");
+    GI_REQUIRE(c_dtype == kF32 || c_dtype == kBF16, "gemm_tc: unsupported output dtype code %d", c_dtype);
+    GI_REQUIRE(!(accumulate && c_dtype != kF32), "gemm_tc: accumulation needs a 32-bit output");
+    GI_REQUIRE(block_q == 16 || block_q == 32 || block_q == 64 || block_q == 128 || block_q == 256,
+               "gemm_tc: block_q=%d is not one of 16, 32, 64, 128, 256", block_q);
+    GI_REQUIRE(splits >= 1, "gemm_tc: splits must be >= 1");
+    GI_REQUIRE(status != nullptr, "gemm_tc: a status word is required");
+
+    TcParams p;
+    p.C = C;
+    p.c_bf16 = c_dtype == kBF16;
+    p.accumulate = accumulate;
+    p.K = K;
+    p.splits = splits;
+    p.workspace = static_cast<float*>(workspace);
+    p.counters = static_cast<unsigned*>(counters);
+    p.status = static_cast<int*>(status);
+    const int total_kb = (K + kBlockK - 1) / kBlockK;
+    p.k_blocks_per_split = (total_kb + splits - 1) / splits;
+
+    CUtensorMap mp, mq;
+    if (swap) {
+        p.rows_p = N; p.rows_q = M; p.stride_p = 1; p.stride_q = ldc;
+        if (make_map(&mp, W, N, K, ldw, kBlockP) || make_map(&mq, A, M, K, lda, block_q)) return 1;
+    } else {
+        p.rows_p = M; p.rows_q = N; p.stride_p = ldc; p.stride_q = 1;
+        if (make_map(&mp, A, M, K, lda, kBlockP) || make_map(&mq, W, N, K, ldw, block_q)) return 1;
+    }
+    dim3 grid((p.rows_p + kBlockP - 1) / kBlockP, (p.rows_q + block_q - 1) / block_q, splits);
+    GI_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid too large");
+    if (splits > 1) {
+        const long long tiles = static_cast<long long>(grid.x) * grid.y;
+        GI_REQUIRE(workspace != nullptr && counters != nullptr, "gemm_tc: a split over K needs a workspace and counters");
+        GI_REQUIRE(tiles * splits * kBlockP * block_q <= workspace_floats,
+                   "gemm_tc: the workspace of %lld floats is too small for %lld tiles x %d splits", workspace_floats, tiles, splits);
+        GI_REQUIRE(tiles <= n_counters, "gemm_tc: %lld tiles need more than the %d counters given", tiles, n_counters);
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (block_q) {
+        case 16: return launch_tc<16>(mp, mq, p, grid, st);
+        case 32: return launch_tc<32>(mp, mq, p, grid, st);
+        case 64: return launch_tc<64>(mp, mq, p, grid, st);
+        case 128: return launch_tc<128>(mp, mq, p, grid, st);
+        default: return launch_tc<256>(mp, mq, p, grid, st);
+    }
+}
+
+// Reads the status word (synchronises the stream): 0 = no bounded wait ever gave up.
+extern "C" int gi_gemm_tc_status(const void* status, void* stream, int* out) {
+    cudaError_t e = cudaMemcpyAsync(out, status, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) { set_error("gemm_tc_status: %s", cudaGetErrorString(e)); return 1; }
+    return 0;
+}

@@ -151,6 +151,68 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: b
                              dtype_code(out.dtype), int(accumulate), M, N, K, K, K, N, _stream()), "gemm")
 
 
+class _TensorCoreState:
+    """Per-device buffers of the tensor-core matrix product: the workspace and tile counters of the
+    split over K, and the status word in which a kernel records a wait that gave up."""
+
+    WORKSPACE_FLOATS = 8 * 1024 * 1024
+    COUNTERS = 4096
+
+    def __init__(self, device: torch.device):
+        self.workspace = torch.empty(self.WORKSPACE_FLOATS, dtype=torch.float32, device=device)
+        self.counters = torch.zeros(self.COUNTERS, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+
+_tc_states = {}
+
+
+def _tc_state(device: torch.device) -> _TensorCoreState:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _tc_states:
+        _tc_states[key] = _TensorCoreState(device)
+    return _tc_states[key]
+
+
+def gemm_tc_plan(M: int, N: int, K: int):
+    """(swap, block_q, splits) for a product of these sizes. Few tokens put the weights on the
+    128-row side and split K until the grid fills the GPU; the choice depends on the sizes only."""
+    if M <= 128:
+        block_q = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+        tiles = (N + 127) // 128
+        k_blocks = (K + 63) // 64
+        splits = 1
+        while tiles * splits < 120 and k_blocks // (splits * 2) >= 4 and splits < 16:
+            splits *= 2
+        return True, block_q, splits
+    return False, (256 if N >= 256 else 128 if N > 64 else 64), 1
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, plan=None) -> None:
+    """out[M,N] (+)= a[M,K] @ w[N,K]^T on the tensor cores: bfloat16 operands, 32-bit accumulation,
+    output 32-bit (optionally accumulated into) or bfloat16. K must be a multiple of 8."""
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm: shapes do not agree (a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)})")
+    swap, block_q, splits = plan or gemm_tc_plan(M, N, K)
+    st = _tc_state(a.device)
+    check(lib().gi_gemm_tc(_dev(a, "a", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"),
+                           dtype_code(out.dtype), int(accumulate), M, N, K, K, K, N, int(swap), block_q, splits,
+                           st.workspace.data_ptr(), st.workspace.numel(), st.counters.data_ptr(), st.counters.numel(),
+                           st.status.data_ptr(), _stream()), "gemm_tc")
+
+
+def gemm_tc_status(device: torch.device) -> int:
+    """0 when no bounded wait of a tensor-core kernel ever gave up on this device (synchronises)."""
+    import ctypes
+    st = _tc_state(device)
+    out = ctypes.c_int(0)
+    check(lib().gi_gemm_tc_status(st.status.data_ptr(), torch.cuda.current_stream().cuda_stream, ctypes.byref(out)),
+          "gemm_tc_status")
+    return out.value
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     rows, V = logits.shape
     check(lib().gi_argmax(_dev(logits, "logits", torch.float32), rows, V, _dev(out, "out", torch.int32), _stream()),

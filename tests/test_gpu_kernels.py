@@ -281,3 +281,46 @@ def test_sample_matches_plain_sampler(V, temperature, top_k, top_p):
             if got[r] not in (lo, hi):
                 bad.append((r, got[r], want))
     assert not bad, f"rows (row, got, want): {bad}"
+
+
+@pytest.mark.parametrize("M,N,K_,plan", [
+    (128, 256, 64, (False, 256, 1)), (128, 256, 512, (False, 256, 1)), (300, 520, 200, (False, 256, 1)),
+    (129, 100, 96, (False, 128, 1)), (256, 64, 128, (False, 64, 1)),
+    (1, 128, 64, (True, 16, 1)), (7, 384, 96, (True, 16, 1)), (16, 128, 1024, (True, 16, 4)), (8, 2048, 2048, (True, 16, 8)),
+    (33, 200, 160, (True, 64, 1)), (64, 300, 1536, (True, 64, 3)), (100, 256, 512, (True, 128, 2)), (20, 130, 264, (True, 32, 2)),
+])
+@pytest.mark.parametrize("c_dtype", ["float32", "bfloat16"])
+def test_gemm_tensor_cores(M, N, K_, plan, c_dtype):
+    """The tcgen05 product in both orientations, with and without the split over K, at sizes that
+    are no multiple of the tile in any dimension; rows of zeros beyond M, N and K must not leak."""
+    g = torch.Generator().manual_seed(11)
+    a = torch.randn(M, K_, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(N, K_, generator=g).to(torch.bfloat16).to(DEV)
+    want = a.float().cpu().double() @ w.float().cpu().double().T
+    guard = torch.full((M + 2, N), -1024.0, dtype=dt(c_dtype), device=DEV)
+    out = guard[1:M + 1]
+    out.fill_(float("nan"))
+    K().gemm_tc(a, w, out, plan=plan)
+    assert K().gemm_tc_status(torch.device(DEV)) == 0
+    close(out, want, c_dtype, "gemm_tc", f32_tol=2e-6 * max(1, K_ / 64), bf16_tol=1e-2)
+    assert float(guard[0].float().min()) == -1024.0 == float(guard[-1].float().max()), "wrote outside the output"
+    if c_dtype == "float32":
+        base = torch.randn(M, N, generator=g).to(DEV)
+        acc = base.clone()
+        K().gemm_tc(a, w, acc, accumulate=True, plan=plan)
+        close(acc, want + base.cpu().double(), "float32", "gemm_tc accumulate", f32_tol=2e-6 * max(1, K_ / 64))
+        again = torch.empty_like(out)
+        K().gemm_tc(a, w, again, plan=plan)
+        assert torch.equal(again, out), "two runs differ"
+    auto = torch.empty((M, N), dtype=dt(c_dtype), device=DEV)
+    K().gemm_tc(a, w, auto)                            # the plan the engine would pick
+    close(auto, want, c_dtype, "gemm_tc auto plan", f32_tol=2e-6 * max(1, K_ / 64), bf16_tol=1e-2)
+    assert K().gemm_tc_status(torch.device(DEV)) == 0
+
+
+def test_gemm_tensor_cores_refuses_what_tma_cannot_address():
+    from geneinfer_b200.ops import KernelError
+    a = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)       # K = 100 is no multiple of 8
+    w = torch.zeros(8, 100, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError, match="multiples of 8"):
+        K().gemm_tc(a, w, torch.empty(4, 8, device=DEV))
