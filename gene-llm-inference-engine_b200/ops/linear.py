@@ -2,8 +2,9 @@
 
 The weight is [N, K] row-major, as checkpoints store it (``y = W x``). On the 32-bit path weight
 and activations are 32-bit and the product runs on the CUDA cores with fused multiply-adds. On the
-bfloat16 path the weight is bfloat16 and the product accumulates in 32-bit; the output may be
-32-bit (and may accumulate into the 32-bit residual stream) or bfloat16.
+bfloat16 path the weight is bfloat16 and the product runs on the tensor cores (tcgen05) with 32-bit
+accumulation; the output may be 32-bit (and may accumulate into the 32-bit residual stream) or
+bfloat16. A width that TMA cannot address (not a multiple of 8) falls back to the CUDA cores.
 """
 from __future__ import annotations
 
@@ -30,5 +31,8 @@ class Linear:
     def forward(self, a: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
         if a.dtype != self.compute_dtype:
             raise kernels.KernelError(f"Linear: activations are {a.dtype}, the weight is {self.compute_dtype}")
-        kernels.gemm_simt(a, self.weight, out, accumulate)
+        if self.compute_dtype is torch.bfloat16 and self.in_features % 8 == 0:
+            kernels.gemm_tc(a, self.weight, out, accumulate)        # tensor cores (TMA needs 16-byte rows)
+        else:
+            kernels.gemm_simt(a, self.weight, out, accumulate)
         return out
