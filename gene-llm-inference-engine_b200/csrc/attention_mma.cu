@@ -1,0 +1,505 @@
+// Paged causal attention in bfloat16 on the tensor cores (mma.sync m16n8k16, 32-bit accumulators
+// and 32-bit online softmax), in two kernels that share their warp-level code:
+//
+//   attention_decode   single decoded tokens deep in a context. The context is cut into chunks of
+//                      kChunkKeys positions (a fixed length, so a row's arithmetic does not depend on
+//                      the batch); one CTA takes one chunk of one (request, key/value head), its four
+//                      warps a quarter each, with the query heads that share the key/value head packed
+//                      as rows of the 16-row tile. Partial (max, sum, output) per chunk go to a
+//                      workspace and attention_combine merges them in chunk order.
+//   attention_prefill  portions of prompts. One CTA takes 64 query rows = (tokens x heads of one
+//                      key/value group) and walks the keys in tiles of 64 through a two-stage
+//                      cp.async pipeline; the four warps own 16 rows each.
+//
+// Keys and values come from pages [pages, Hkv, page_size, head_dim] through the request's block
+// table. Rows of a tile that lie outside every query's range are zero-filled on load, so stale or
+// unwritten page contents (tests fill them with NaN) can never reach a result.
+// Head sizes 16, 32, 64 and 128 are built; other sizes use the general kernel.
+#include "common.cuh"
+
+namespace gi {
+
+constexpr int kAttThreads = 128;
+constexpr int kTileKeys = 64;
+constexpr int kChunkKeys = 256;          // decode: keys per CTA (4 warps x 64)
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;       // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Tiles are stored as rows of HD bfloat16 with their 16-byte chunks permuted so that the eight
+// rows an ldmatrix reads fall into eight different bank groups.
+template <int HD>
+__device__ __forceinline__ int swizzled_chunk(int row, int chunk) {
+    constexpr int cpr = HD / 8;                       // 16-byte chunks per row
+    if (cpr >= 8) return chunk ^ (row & 7);
+    if (cpr == 4) return chunk ^ ((row >> 1) & 3);
+    return chunk ^ ((row >> 2) & 1);                  // cpr == 2
+}
+template <int HD>
+__device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk) {
+    return base + static_cast<uint32_t>((row * (HD / 8) + swizzled_chunk<HD>(row, chunk)) * 16);
+}
+
+// Loads keys [key0, key0 + n_rows) of one key/value head into a tile; rows outside [lo, hi] (the
+// union of what the tile's queries may read) are zero-filled and their pages are not touched.
+template <int HD>
+__device__ __forceinline__ void load_tile_async(uint32_t tile, const __nv_bfloat16* __restrict__ cache,
+                                                const int* __restrict__ table, int g, int Hkv, int page_size,
+                                                int key0, int n_rows, int lo, int hi, int tid, int n_threads) {
+    constexpr int cpr = HD / 8;
+    for (int i = tid; i < n_rows * cpr; i += n_threads) {
+        const int row = i / cpr, chunk = i % cpr;
+        const int key = key0 + row;
+        const bool valid = key >= lo && key <= hi;
+        const __nv_bfloat16* src = cache;
+        if (valid) {
+            const int page = table[key / page_size];
+            src = cache + ((static_cast<size_t>(page) * Hkv + g) * page_size + (key % page_size)) * HD + chunk * 8;
+        }
+        cp_async16(tile_addr<HD>(tile, row, chunk), src, valid);
+    }
+}
+
+// One warp: S = Q K^T for 16 query rows x 64 keys, online softmax update, O += P V.
+// q_frag: A fragments of the 16 x HD query tile. Row limits (lo, pos) are those of the two rows
+// this lane holds (lane/4 and lane/4 + 8). o: HD/8 n-tiles x 4 accumulators. m, l: per row.
+template <int HD>
+__device__ __forceinline__ void warp_tile_step(const uint32_t (*q_frag)[4], uint32_t k_tile, uint32_t v_tile, int key0,
+                                               const int* row_lo, const int* row_pos, float scale_log2,
+                                               float (*o)[4], float* m, float* l, int lane) {
+    constexpr int kK = HD / 16;                 // k-steps of Q K^T
+    constexpr int kN = kTileKeys / 8;           // n-tiles of S
+    float s[kN][4];
+#pragma unroll
+    for (int j = 0; j < kN; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+    for (int j = 0; j < kN; ++j) {
+#pragma unroll
+        for (int kk = 0; kk < kK; ++kk) {
+            uint32_t b0, b1;
+            // B fragment of K^T: keys j*8 + lane%8 (rows), head dims kk*16 + {0, 8} (two 8x8 matrices)
+            ldmatrix_x2(tile_addr<HD>(k_tile, j * 8 + (lane & 7), kk * 2 + ((lane >> 3) & 1)), b0, b1);
+            mma_bf16(s[j], q_frag[kk], b0, b1);
+        }
+    }
+    // scale, mask, row maxima
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < kN; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+            const bool ok = key >= row_lo[r] && key <= row_pos[r];
+            s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
+            mx[r] = fmaxf(mx[r], s[j][e]);
+        }
+    }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m[r], mx[r]);
+        corr[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - m_new);
+        m[r] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < kN; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const float p = (m[r] == -INFINITY) ? 0.f : exp2f(s[j][e] - m[r]);     // masked scores give 0
+            s[j][e] = p;
+            sum[r] += p;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+        l[r] = l[r] * corr[r] + sum[r];
+    }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+    // O += P V: P as A fragments (16 keys per k-step), V^T through transposed ldmatrix
+#pragma unroll
+    for (int t = 0; t < kTileKeys / 16; ++t) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * t][0], s[2 * t][1]);
+        a[1] = pack_bf16(s[2 * t][2], s[2 * t][3]);
+        a[2] = pack_bf16(s[2 * t + 1][0], s[2 * t + 1][1]);
+        a[3] = pack_bf16(s[2 * t + 1][2], s[2 * t + 1][3]);
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            uint32_t b0, b1;
+            // keys t*16 + {0..7, 8..15} (rows of V), head dims n*8..n*8+7, transposed on load
+            ldmatrix_x2_trans(tile_addr<HD>(v_tile, t * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, n), b0, b1);
+            mma_bf16(o[n], a, b0, b1);
+        }
+    }
+}
+
+// Loads the A fragments of a 16-row query tile stored (swizzled) in shared memory.
+template <int HD>
+__device__ __forceinline__ void load_q_frags(uint32_t q_tile, int row0, uint32_t (*q_frag)[4], int lane) {
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+        const int row = row0 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        ldmatrix_x4(tile_addr<HD>(q_tile, row, kk * 2 + (lane >> 4)), q_frag[kk][0], q_frag[kk][1], q_frag[kk][2], q_frag[kk][3]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ decode
+// grid (chunks, Hkv, decode requests). rows: one per query head of the group (G <= 16).
+// part_o [row_index][H][chunks][HD], part_ml [row_index][H][chunks][2] with row_index = blockIdx.z.
+template <int HD>
+__global__ void __launch_bounds__(kAttThreads)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                        const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ rows,
+                        const int* __restrict__ row_req, const int* __restrict__ positions,
+                        const int* __restrict__ block_tables, int table_stride, int H, int Hkv, int page_size,
+                        float scale_log2, int window, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        int max_chunks) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int G = H / Hkv;
+    const int chunk = blockIdx.x, g = blockIdx.y, idx = blockIdx.z;
+    const int t = rows[idx];
+    const int pos = positions[t];
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int c0 = chunk * kChunkKeys;
+    float* my_o = part_o + ((static_cast<size_t>(idx) * H + g * G) * max_chunks + chunk) * HD;
+    float* my_ml = part_ml + ((static_cast<size_t>(idx) * H + g * G) * max_chunks + chunk) * 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (c0 > pos || c0 + kChunkKeys <= lo) {
+        // nothing of this chunk is visible: an empty partial (m = -inf, l = 0)
+        if (threadIdx.x < G) {
+            my_ml[static_cast<size_t>(threadIdx.x) * max_chunks * 2] = -INFINITY;
+            my_ml[static_cast<size_t>(threadIdx.x) * max_chunks * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    const int* table = block_tables + static_cast<size_t>(row_req[t]) * table_stride;
+
+    // shared memory: Q tile [16][HD], then per warp a K tile and a V tile [64][HD]
+    constexpr int kTileBytes = kTileKeys * HD * 2;
+    const uint32_t q_tile = smem_addr(smem);
+    const uint32_t k_tile = q_tile + 16 * HD * 2 + warp * 2 * kTileBytes;
+    const uint32_t v_tile = k_tile + kTileBytes;
+    const int key0 = c0 + warp * kTileKeys;
+
+    // every warp loads its own keys and values; all warps share the query tile
+    load_tile_async<HD>(k_tile, k_cache, table, g, Hkv, page_size, key0, kTileKeys, lo, pos, lane, 32);
+    load_tile_async<HD>(v_tile, v_cache, table, g, Hkv, page_size, key0, kTileKeys, lo, pos, lane, 32);
+    cp_async_commit();
+    {
+        constexpr int cpr = HD / 8;
+        const uint4* src = reinterpret_cast<const uint4*>(q + (static_cast<size_t>(t) * H + g * G) * HD);
+        for (int i = threadIdx.x; i < 16 * cpr; i += kAttThreads) {
+            const int row = i / cpr, c = i % cpr;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row < G) v = src[row * cpr + c];
+            *reinterpret_cast<uint4*>(smem + (row * cpr + swizzled_chunk<HD>(row, c)) * 16) = v;
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    uint32_t q_frag[HD / 16][4];
+    load_q_frags<HD>(q_tile, 0, q_frag, lane);
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int r0 = lane >> 2;
+    int row_lo[2], row_pos[2];
+    row_lo[0] = lo; row_pos[0] = (r0 < G) ? pos : -1;            // rows beyond the group see nothing
+    row_lo[1] = lo; row_pos[1] = (r0 + 8 < G) ? pos : -1;
+    if (key0 <= pos && key0 + kTileKeys > lo)
+        warp_tile_step<HD>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane);
+    __syncthreads();                                               // tiles are read; reuse the memory
+
+    // merge the four warps in warp order through shared memory: [warp][16 rows][HD + 2]
+    float* red = reinterpret_cast<float*>(smem);
+    constexpr int kRow = HD + 2;
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        const int d = n * 8 + (lane & 3) * 2;
+        float* a = red + (warp * 16 + r0) * kRow + d;
+        float* b = red + (warp * 16 + r0 + 8) * kRow + d;
+        a[0] = o[n][0]; a[1] = o[n][1]; b[0] = o[n][2]; b[1] = o[n][3];
+    }
+    if ((lane & 3) == 0) {
+        red[(warp * 16 + r0) * kRow + HD] = m[0];
+        red[(warp * 16 + r0) * kRow + HD + 1] = l[0];
+        red[(warp * 16 + r0 + 8) * kRow + HD] = m[1];
+        red[(warp * 16 + r0 + 8) * kRow + HD + 1] = l[1];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * HD; i += kAttThreads) {
+        const int row = i / HD, d = i % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, red[(w * 16 + row) * kRow + HD]);
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = red[(w * 16 + row) * kRow + HD];
+            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+            acc += red[(w * 16 + row) * kRow + d] * f;
+            L += red[(w * 16 + row) * kRow + HD + 1] * f;
+        }
+        my_o[static_cast<size_t>(row) * max_chunks * HD + d] = acc;
+        if (d == 0) {
+            my_ml[static_cast<size_t>(row) * max_chunks * 2] = M;
+            my_ml[static_cast<size_t>(row) * max_chunks * 2 + 1] = L;
+        }
+    }
+}
+
+// grid (H, decode requests); one thread per head dim. Chunks are merged in increasing order.
+__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         const int* __restrict__ rows, const int* __restrict__ positions,
+                                         __nv_bfloat16* __restrict__ out, int H, int HD, int max_chunks, int window) {
+    const int h = blockIdx.x, idx = blockIdx.y;
+    const int t = rows[idx];
+    const int pos = positions[t];
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first = lo / kChunkKeys, last = pos / kChunkKeys;
+    const float* ml = part_ml + (static_cast<size_t>(idx) * H + h) * max_chunks * 2;
+    const float* po = part_o + (static_cast<size_t>(idx) * H + h) * max_chunks * HD;
+    float M = -INFINITY;
+    for (int c = first; c <= last; ++c) M = fmaxf(M, ml[c * 2]);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float acc = 0.f, L = 0.f;
+        for (int c = first; c <= last; ++c) {
+            const float mc = ml[c * 2];
+            const float f = (mc == -INFINITY) ? 0.f : exp2f(mc - M);
+            acc += po[static_cast<size_t>(c) * HD + d] * f;
+            L += ml[c * 2 + 1] * f;
+        }
+        out[(static_cast<size_t>(t) * H + h) * HD + d] = __float2bfloat16_rn(acc / L);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ prefill
+// Work item w = (first row of the tile in the step, number of tokens, request); grid (work, Hkv).
+// A tile holds tokens_per_tile = 64 / G tokens; tile row r = token r / G, head r % G of the group.
+template <int HD>
+__global__ void __launch_bounds__(kAttThreads)
+attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                         const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
+                         const int* __restrict__ work, const int* __restrict__ positions,
+                         const int* __restrict__ block_tables, int table_stride, int H, int Hkv, int page_size,
+                         float scale_log2, int window) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int G = H / Hkv;
+    const int g = blockIdx.y;
+    const int t0 = work[blockIdx.x * 3], n_tok = work[blockIdx.x * 3 + 1], req = work[blockIdx.x * 3 + 2];
+    const int n_rows = n_tok * G;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* table = block_tables + static_cast<size_t>(req) * table_stride;
+    const int pos_first = positions[t0], pos_last = pos_first + n_tok - 1;      // consecutive positions
+    const int lo_first = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+
+    constexpr int kTileBytes = kTileKeys * HD * 2;
+    constexpr int cpr = HD / 8;
+    const uint32_t q_tile = smem_addr(smem);
+    const uint32_t kv_base = q_tile + 64 * HD * 2;          // stage s: K at kv_base + s*2*kTileBytes, V after it
+
+    // the query tile: row r <- q[t0 + r / G][g * G + r % G]
+    for (int i = threadIdx.x; i < 64 * cpr; i += kAttThreads) {
+        const int row = i / cpr, c = i % cpr;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < n_rows) {
+            const int tok = row / G, hh = row % G;
+            v = *reinterpret_cast<const uint4*>(q + (static_cast<size_t>(t0 + tok) * H + g * G + hh) * HD + c * 8);
+        }
+        *reinterpret_cast<uint4*>(smem + (row * cpr + swizzled_chunk<HD>(row, c)) * 16) = v;
+    }
+
+    const int first_tile = lo_first / kTileKeys, last_tile = pos_last / kTileKeys;
+    const int n_tiles = last_tile - first_tile + 1;
+    auto issue = [&](int i) {
+        const uint32_t kt = kv_base + (i & 1) * 2 * kTileBytes;
+        const int key0 = (first_tile + i) * kTileKeys;
+        load_tile_async<HD>(kt, k_cache, table, g, Hkv, page_size, key0, kTileKeys, lo_first, pos_last, threadIdx.x, kAttThreads);
+        load_tile_async<HD>(kt + kTileBytes, v_cache, table, g, Hkv, page_size, key0, kTileKeys, lo_first, pos_last, threadIdx.x, kAttThreads);
+        cp_async_commit();
+    };
+    issue(0);
+    __syncthreads();                                    // the query tile is complete
+
+    uint32_t q_frag[HD / 16][4];
+    load_q_frags<HD>(q_tile, warp * 16, q_frag, lane);
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    int row_lo[2], row_pos[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + (lane >> 2) + r * 8;
+        if (row < n_rows) {
+            row_pos[r] = pos_first + row / G;
+            row_lo[r] = (window > 0 && row_pos[r] - window + 1 > 0) ? row_pos[r] - window + 1 : 0;
+        } else {
+            row_pos[r] = -1; row_lo[r] = 0;
+        }
+    }
+    // what this warp's rows can see at most (uniform across the warp)
+    const int warp_row_first = warp * 16, warp_row_last = min(n_rows - 1, warp * 16 + 15);
+    const int warp_pos_max = (warp_row_first < n_rows) ? pos_first + warp_row_last / G : -1;
+    const int warp_pos_min = pos_first + warp_row_first / G;
+    const int warp_lo_min = (window > 0 && warp_pos_min - window + 1 > 0) ? warp_pos_min - window + 1 : 0;
+
+    for (int i = 0; i < n_tiles; ++i) {
+        if (i + 1 < n_tiles) { issue(i + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        __syncthreads();
+        const uint32_t kt = kv_base + (i & 1) * 2 * kTileBytes;
+        const int key0 = (first_tile + i) * kTileKeys;
+        if (key0 <= warp_pos_max && key0 + kTileKeys > warp_lo_min)
+            warp_tile_step<HD>(q_frag, kt, kt + kTileBytes, key0, row_lo, row_pos, scale_log2, o, m, l, lane);
+        __syncthreads();                                // the stage may be overwritten by the next issue
+    }
+
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + (lane >> 2) + r * 8;
+        if (row >= n_rows) continue;
+        const int tok = row / G, hh = row % G;
+        const float inv = 1.0f / l[r];
+        __nv_bfloat16* dst = out + (static_cast<size_t>(t0 + tok) * H + g * G + hh) * HD + (lane & 3) * 2;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) = __floats2bfloat162_rn(o[n][2 * r] * inv, o[n][2 * r + 1] * inv);
+        }
+    }
+}
+
+template <int HD>
+static int launch_decode(const void* q, const void* kc, const void* vc, void* out, const int* rows, int n_rows,
+                         const int* row_req, const int* positions, const int* tables, int table_stride, int H, int Hkv,
+                         int page_size, float scale, int window, float* part_o, float* part_ml, int max_chunks,
+                         int n_chunks, cudaStream_t st) {
+    constexpr int smem = 16 * HD * 2 + 4 * 2 * kTileKeys * HD * 2;
+    constexpr int red = 4 * 16 * (HD + 2) * 4;
+    constexpr int bytes = smem > red ? smem : red;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) { set_error("attention_decode: %s", cudaGetErrorString(e)); return 1; }
+        configured = true;
+    }
+    dim3 grid(n_chunks, Hkv, n_rows);
+    attention_decode_kernel<HD><<<grid, kAttThreads, bytes, st>>>(
+        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc),
+        rows, row_req, positions, tables, table_stride, H, Hkv, page_size, scale * kLog2e, window, part_o, part_ml, max_chunks);
+    if (check_launch("attention_decode")) return 1;
+    dim3 grid2(H, n_rows);
+    attention_combine_kernel<<<grid2, HD < 32 ? 32 : HD, 0, st>>>(part_o, part_ml, rows, positions,
+                                                                   static_cast<__nv_bfloat16*>(out), H, HD, max_chunks, window);
+    return check_launch("attention_combine");
+}
+
+template <int HD>
+static int launch_prefill(const void* q, const void* kc, const void* vc, void* out, const int* work, int n_work,
+                          const int* positions, const int* tables, int table_stride, int H, int Hkv, int page_size,
+                          float scale, int window, cudaStream_t st) {
+    constexpr int bytes = 64 * HD * 2 + 2 * 2 * kTileKeys * HD * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) { set_error("attention_prefill: %s", cudaGetErrorString(e)); return 1; }
+        configured = true;
+    }
+    dim3 grid(n_work, Hkv);
+    attention_prefill_kernel<HD><<<grid, kAttThreads, bytes, st>>>(
+        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc),
+        static_cast<__nv_bfloat16*>(out), work, positions, tables, table_stride, H, Hkv, page_size, scale * kLog2e, window);
+    return check_launch("attention_prefill");
+}
+
+}  // namespace gi
+
+using namespace gi;
+
+extern "C" int gi_attention_fast_supported(int head_dim, int H, int Hkv) {
+    return (head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128) && Hkv > 0 && H % Hkv == 0 && H / Hkv <= 16;
+}
+
+extern "C" int gi_attention_chunk_keys() { return kChunkKeys; }
+
+// Single decoded tokens: rows[i] is the step row of the i-th one. part_o holds
+// n_rows * H * max_chunks * hd floats and part_ml n_rows * H * max_chunks * 2; n_chunks covers the
+// longest context among the rows.
+extern "C" int gi_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* rows,
+                                   int n_rows, const int* row_req, const int* positions, const int* block_tables,
+                                   int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window,
+                                   float* part_o, float* part_ml, int max_chunks, int n_chunks, void* stream) {
+    if (n_rows == 0) return 0;
+    GI_REQUIRE(gi_attention_fast_supported(hd, H, Hkv), "attention_decode: head size %d with %d/%d heads is not built", hd, H, Hkv);
+    GI_REQUIRE(n_chunks >= 1 && n_chunks <= max_chunks, "attention_decode: %d chunks exceed the workspace's %d", n_chunks, max_chunks);
+    GI_REQUIRE(n_rows <= 65535 && Hkv <= 65535, "attention_decode: grid too large");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define GI_DECODE(HD) return launch_decode<HD>(q, k_cache, v_cache, out, rows, n_rows, row_req, positions, block_tables, \
+                                               table_stride, H, Hkv, page_size, scale, window, part_o, part_ml, max_chunks, n_chunks, st)
+    switch (hd) {
+        case 16: GI_DECODE(16);
+        case 32: GI_DECODE(32);
+        case 64: GI_DECODE(64);
+        default: GI_DECODE(128);
+    }
+#undef GI_DECODE
+}
+
+// Prompt portions: work[3*i..] = (first step row of the tile, tokens in the tile, request index).
+extern "C" int gi_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work,
+                                    int n_work, const int* positions, const int* block_tables, int table_stride, int H,
+                                    int Hkv, int hd, int page_size, float scale, int window, void* stream) {
+    if (n_work == 0) return 0;
+    GI_REQUIRE(gi_attention_fast_supported(hd, H, Hkv), "attention_prefill: head size %d with %d/%d heads is not built", hd, H, Hkv);
+    GI_REQUIRE(Hkv <= 65535, "attention_prefill: grid too large");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define GI_PREFILL(HD) return launch_prefill<HD>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, \
+                                                 H, Hkv, page_size, scale, window, st)
+    switch (hd) {
+        case 16: GI_PREFILL(16);
+        case 32: GI_PREFILL(32);
+        case 64: GI_PREFILL(64);
+        default: GI_PREFILL(128);
+    }
+#undef GI_PREFILL
+}

@@ -52,6 +52,7 @@ class StepContext:
         self.n_logit_rows = n_logit_rows
         self.segments = segments
         self.page_size = engine.page_size
+        self.max_requests = engine.max_requests
         self.compute_dtype = engine.model.dtype
         self.tokens = views["tokens"]
         self.positions = views["positions"]
@@ -61,6 +62,7 @@ class StepContext:
         self.seg_start = views["seg_start"]
         self.seg_len = views["seg_len"]
         self._tables = views["tables"]
+        self._cache: Dict = {}
         self.all_single = all(s.length == 1 for s in segments)
         self.max_context = max((s.first_position + s.length for s in segments), default=0)
 
@@ -76,8 +78,28 @@ class StepContext:
         """State of a layer for every slot: [slots, *shape]; row ``state_slot`` is a request's."""
         return self._engine.layer_state[layer]
 
-    def scratch(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
-        return self._engine.scratch(name, shape, dtype)
+    def scratch(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype, capacity: Optional[int] = None) -> torch.Tensor:
+        return self._engine.scratch(name, shape, dtype, capacity)
+
+    def attention_work(self, tokens_per_tile: int):
+        """How this step's rows are shared between the two attention kernels: (rows of requests
+        that bring a single token [n] on the device, tiles of longer portions [m, 3] = (first
+        row, tokens, request), longest context among the single tokens). Built once per step."""
+        key = ("attention_work", tokens_per_tile)
+        if key not in self._cache:
+            single = [s.start for s in self.segments if s.length == 1]
+            tiles = []
+            for r, s in enumerate(self.segments):
+                if s.length > 1:
+                    for t in range(0, s.length, tokens_per_tile):
+                        tiles.append((s.start + t, min(tokens_per_tile, s.length - t), r))
+            longest = max((s.first_position + 1 for s in self.segments if s.length == 1), default=0)
+            flat = single + [v for tile in tiles for v in tile]
+            dev = self._engine.upload_ints(flat)
+            rows = dev[:len(single)]
+            work = dev[len(single):].view(len(tiles), 3)
+            self._cache[key] = (rows, work, longest)
+        return self._cache[key]
 
 
 class StepEngine:
@@ -115,13 +137,16 @@ class StepEngine:
         self._init_descriptor()
 
     # ------------------------------------------------------------------ memory
-    def scratch(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
-        """A reusable buffer; the same name, trailing shape and dtype give the same memory each step."""
+    def scratch(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype, capacity: Optional[int] = None) -> torch.Tensor:
+        """A reusable buffer; the same name, trailing shape and dtype give the same memory each step.
+        ``capacity`` is the most rows the buffer will ever need (default: the step's token limit)."""
         key = (name, tuple(shape[1:]), dtype)
         buf = self._scratch.get(key)
         if buf is None or buf.shape[0] < shape[0]:
             if name in ("logits", "head_in"):      # wanted rows are usually few: grow on demand
                 rows = min(self.max_logit_rows, max(8, 1 << (shape[0] - 1).bit_length()))
+            elif capacity is not None:
+                rows = max(shape[0], capacity)
             else:
                 rows = max(shape[0], self.max_step_tokens)
             buf = torch.empty((rows, *shape[1:]), dtype=dtype, device=self.device)
@@ -150,6 +175,31 @@ class StepEngine:
         self._ring_np = [b.numpy() for b in self._ring]
         self._ring_events: List[Optional[torch.cuda.Event]] = [None] * 4
         self._ring_next = 0
+        cap = 4 * (T + R)
+        self._aux_host = [torch.zeros(cap, dtype=torch.int32).pin_memory() for _ in range(8)]
+        self._aux_dev = [torch.zeros(cap, dtype=torch.int32, device=self.device) for _ in range(8)]
+        self._aux_events: List[Optional[torch.cuda.Event]] = [None] * 8
+        self._aux_next = 0
+
+    def upload_ints(self, values) -> torch.Tensor:
+        """Small integer lists that a part derives from the step (work lists): one pinned staging
+        buffer per call slot, copied asynchronously; the device view is valid until the next step."""
+        n = len(values)
+        slot = self._aux_next
+        self._aux_next = (slot + 1) % len(self._aux_host)
+        if self._aux_events[slot] is not None:
+            self._aux_events[slot].synchronize()
+        if n > self._aux_host[slot].numel():
+            self._aux_host[slot] = torch.zeros(2 * n, dtype=torch.int32).pin_memory()
+            self._aux_dev[slot] = torch.zeros(2 * n, dtype=torch.int32, device=self.device)
+        host, dev = self._aux_host[slot], self._aux_dev[slot]
+        if n:
+            host[:n] = torch.tensor(values, dtype=torch.int32)
+            dev[:n].copy_(host[:n], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._aux_events[slot] = ev
+        return dev[:n]
 
     # ------------------------------------------------------------------ requests
     def open(self, key: Hashable) -> RequestCache:

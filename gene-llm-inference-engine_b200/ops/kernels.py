@@ -141,6 +141,60 @@ def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         head_dim, page_size, float(scale), int(window or 0), _stream()), "attention")
 
 
+def attention_fast_supported(head_dim: int, num_heads: int, num_kv_heads: int) -> bool:
+    """Whether the tensor-core attention kernels are built for this head size and grouping."""
+    return bool(lib().gi_attention_fast_supported(head_dim, num_heads, num_kv_heads))
+
+
+def attention_chunk_keys() -> int:
+    """Positions per chunk of the decode kernel's split over the context (a fixed length)."""
+    return int(lib().gi_attention_chunk_keys())
+
+
+def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                     rows: torch.Tensor, row_req: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor,
+                     num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, scale: float,
+                     window: Optional[int], part_o: torch.Tensor, part_ml: torch.Tensor, max_chunks: int,
+                     n_chunks: int) -> None:
+    """Attention of single decoded tokens (bfloat16): ``rows`` lists their step rows; the context is
+    split into fixed chunks whose partial results go through ``part_o`` / ``part_ml``."""
+    n = rows.numel()
+    if part_o.numel() < n * num_heads * max_chunks * head_dim or part_ml.numel() < n * num_heads * max_chunks * 2:
+        raise KernelError("attention_decode: the workspace is too small")
+    if k_cache.shape[1:] != (num_kv_heads, page_size, head_dim) or v_cache.shape != k_cache.shape:
+        raise KernelError("attention: the cache must be [pages, Hkv, page_size, hd]")
+    if q.shape[1] != num_heads * head_dim or out.shape != q.shape:
+        raise KernelError("attention: q and out must be [T, H*hd]")
+    check(lib().gi_attention_decode(
+        _dev(q, "q", torch.bfloat16), _dev(k_cache, "k_cache", torch.bfloat16), _dev(v_cache, "v_cache", torch.bfloat16),
+        _dev(out, "out", torch.bfloat16), _dev(rows, "rows", torch.int32), n, _dev(row_req, "row_req", torch.int32),
+        _dev(positions, "positions", torch.int32), _dev(block_tables, "block_tables", torch.int32),
+        block_tables.shape[1], num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
+        _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), max_chunks, n_chunks,
+        _stream()), "attention_decode")
+    global _launches
+    _launches += 1            # the combine kernel
+
+
+def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                      work: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor, num_heads: int,
+                      num_kv_heads: int, head_dim: int, page_size: int, scale: float, window: Optional[int]) -> None:
+    """Attention of prompt portions (bfloat16): ``work`` [n, 3] = (first step row of a tile, tokens
+    in it (at most 64 // group size), request index)."""
+    if work.dim() != 2 or work.shape[1] != 3:
+        raise KernelError("attention_prefill: work must be [n, 3]")
+    if k_cache.shape[1:] != (num_kv_heads, page_size, head_dim) or v_cache.shape != k_cache.shape:
+        raise KernelError("attention: the cache must be [pages, Hkv, page_size, hd]")
+    if q.shape[1] != num_heads * head_dim or out.shape != q.shape:
+        raise KernelError("attention: q and out must be [T, H*hd]")
+    check(lib().gi_attention_prefill(
+        _dev(q, "q", torch.bfloat16), _dev(k_cache, "k_cache", torch.bfloat16), _dev(v_cache, "v_cache", torch.bfloat16),
+        _dev(out, "out", torch.bfloat16), _dev(work, "work", torch.int32), work.shape[0],
+        _dev(positions, "positions", torch.int32), _dev(block_tables, "block_tables", torch.int32),
+        block_tables.shape[1], num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
+        _stream()), "attention_prefill")
+
+
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """out[M,N] (+)= a[M,K] @ w[N,K]^T with 32-bit fused multiply-adds on the CUDA cores."""
     M, K = a.shape

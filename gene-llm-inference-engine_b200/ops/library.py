@@ -32,6 +32,12 @@ _SIGNATURES = {
     "gi_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                    c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p],
     "gi_gemm_tc_status": [c_void_p, c_void_p, c_void_p],
+    "gi_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                            c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "gi_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                             c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "gi_attention_fast_supported": [c_int, c_int, c_int],
+    "gi_attention_chunk_keys": [],
     "gi_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p],
     "gi_sample": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
 }

@@ -40,6 +40,12 @@ class AttentionMixer:
         self.w_qkv = Linear(weights["w_qkv"], build.compute_dtype, build.device)
         self.w_o = Linear(weights["w_o"], build.compute_dtype, build.device)
         self.dtype = build.compute_dtype
+        # bfloat16 with a head size the tensor-core kernels are built for; else the general kernel
+        self.fast = self.dtype is torch.bfloat16 and kernels.attention_fast_supported(
+            self.head_dim, self.num_heads, self.num_kv_heads)
+        if self.fast:
+            self.chunk_keys = kernels.attention_chunk_keys()
+            self.max_chunks = (build.max_position + self.chunk_keys - 1) // self.chunk_keys
 
     def cache_need(self):
         return CacheNeed(self.num_kv_heads, self.head_dim, self.window)
@@ -61,6 +67,21 @@ class AttentionMixer:
                            self.position.interleaved, q, k_cache, v_cache, H, Hkv, hd, ctx.page_size,
                            write_kv=run.writes_cache)
         att = ctx.scratch("att", (T, H * hd), self.dtype)
-        kernels.attention_generic(q, k_cache, v_cache, att, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
-                                  ctx.page_size, self.scale, self.window)
+        if self.fast:
+            # tensor-core kernels: single decoded tokens split their context over many CTAs,
+            # portions of prompts run tile by tile
+            rows, work, longest = ctx.attention_work(64 // (H // Hkv))
+            if rows.numel():
+                n = rows.numel()
+                part_o = ctx.scratch("att_part_o", (n, H * self.max_chunks * hd), torch.float32, capacity=ctx.max_requests)
+                part_ml = ctx.scratch("att_part_ml", (n, H * self.max_chunks * 2), torch.float32, capacity=ctx.max_requests)
+                n_chunks = (longest + self.chunk_keys - 1) // self.chunk_keys
+                kernels.attention_decode(q, k_cache, v_cache, att, rows, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
+                                         ctx.page_size, self.scale, self.window, part_o, part_ml, self.max_chunks, n_chunks)
+            if work.shape[0]:
+                kernels.attention_prefill(q, k_cache, v_cache, att, work, ctx.positions, tables, H, Hkv, hd,
+                                          ctx.page_size, self.scale, self.window)
+        else:
+            kernels.attention_generic(q, k_cache, v_cache, att, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
+                                      ctx.page_size, self.scale, self.window)
         self.w_o.forward(att, x, accumulate=True)

@@ -12,9 +12,15 @@ import tiny_configs as tc
 
 # 32-bit: both sides compute in 32-bit, only summation orders differ.
 TOL_F32 = 2e-5
-# bfloat16 against the plain implementation that rounds to bfloat16 at the same places: what is
-# left are summation orders and single-ulp flips of stored activations.
-TOL_BF16 = 1.5e-2
+# bfloat16: the plain implementation rounds to bfloat16 where the engine does, but two bfloat16
+# computations that round in a slightly different order (the running maximum of an online softmax,
+# the order of a sum) differ by a fraction of the model's own bfloat16 noise, which depends on
+# how much the weights amplify it. The tolerance is therefore tied to that noise, measured per
+# model as the distance between the rounding and the exact plain implementation: an engine must
+# stay within three quarters of it (measured on B200: 0.27 to 0.51 of it, the largest share on the
+# model whose logits are smallest). A wrong key, position or page in the sharp models moves logits
+# by about their own size, an order of magnitude more than this.
+BF16_NOISE_SHARE = 0.75
 
 _TMP = tempfile.TemporaryDirectory(prefix="geneinfer_tests_")
 
@@ -50,8 +56,15 @@ def plain_logits(case: str, dtype: str):
     return {rid: pm.plain_forward(w, cfg, toks, rnd).numpy() for rid, toks in requests(case).items()}
 
 
-def tolerance(dtype: str) -> float:
-    return TOL_F32 if dtype == "float32" else TOL_BF16
+@functools.lru_cache(maxsize=None)
+def bf16_noise(case: str) -> float:
+    """max|a-b| / max(1, max|b|) between the bfloat16-rounding and the exact plain implementation."""
+    exact, rounded = plain_logits(case, "float32"), plain_logits(case, "bfloat16")
+    return max(float(np.abs(rounded[r] - exact[r]).max() / max(1.0, np.abs(exact[r]).max())) for r in exact)
+
+
+def tolerance(dtype: str, case: str) -> float:
+    return TOL_F32 if dtype == "float32" else BF16_NOISE_SHARE * bf16_noise(case)
 
 
 def make_engine(case: str, dtype: str, n_pages: int, max_requests: int = 4, page_size: int = 16,

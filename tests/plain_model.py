@@ -118,11 +118,13 @@ def plain_rope(v: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
 
 
 def plain_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
-                    window: Optional[int] = None) -> torch.Tensor:
+                    window: Optional[int] = None, rnd=None) -> torch.Tensor:
     """Causal grouped-query attention of a whole sequence (src/model/transformer.cpp:228-255):
     for the query at position P and head h, kv head g = h // (H / Hkv), scores
     s_j = (q . k_j) * scale for j <= P only, softmax with the sum in double
-    (src/kernels/kernels.cpp:87-104), out = sum_j p_j v_j. q: [T, H, hd]; k, v: [T, Hkv, hd]."""
+    (src/kernels/kernels.cpp:87-104), out = sum_j p_j v_j. q: [T, H, hd]; k, v: [T, Hkv, hd].
+    ``rnd`` (bfloat16 engines): the unnormalised weights exp(s - max) are rounded as the operand of
+    the product with v, while their sum stays 32-bit: out = (rnd(e) @ v) / sum(e)."""
     T, H, hd = q.shape
     Hkv = k.shape[1]
     mul = H // Hkv
@@ -133,8 +135,11 @@ def plain_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: fl
             lo = 0 if window is None else max(0, P - window + 1)
             s = (k[lo:P + 1, g] @ q[P, h]) * np.float32(scale)
             e = torch.exp(s - s.max())
-            p = e / e.double().sum().to(F32)
-            out[P, h] = p @ v[lo:P + 1, g]
+            if rnd is None:
+                p = e / e.double().sum().to(F32)
+                out[P, h] = p @ v[lo:P + 1, g]
+            else:
+                out[P, h] = (rnd(e) @ v[lo:P + 1, g]) / e.double().sum().to(F32)
     return out
 
 
@@ -165,7 +170,8 @@ def plain_layer(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, cfg: d
     k = (xb @ w[prefix + "self_attn.k_proj.weight"].T).reshape(T, Hkv, hd)
     v = rnd((xb @ w[prefix + "self_attn.v_proj.weight"].T).reshape(T, Hkv, hd))
     q, k = rnd(plain_rope(q, cos, sin)), rnd(plain_rope(k, cos, sin))
-    att = rnd(plain_attention(q, k, v, 1.0 / math.sqrt(np.float32(hd)), cfg.get("window")))
+    att = rnd(plain_attention(q, k, v, 1.0 / math.sqrt(np.float32(hd)), cfg.get("window"),
+                              None if rnd is no_rounding else rnd))
     x = x + att.reshape(T, H * hd) @ w[prefix + "self_attn.o_proj.weight"].T
     xb = rnd(plain_rmsnorm(x, w[prefix + "post_attention_layernorm.weight"], cfg["eps"]))
     h = rnd(plain_swiglu(xb @ w[prefix + "mlp.gate_proj.weight"].T, xb @ w[prefix + "mlp.up_proj.weight"].T))

@@ -151,7 +151,33 @@ def test_rope_store(dtype, H, Hkv, hd, ps, interleaved, rot):
         "rows of other positions were written"
 
 
-def _attention_case(dtype, H, Hkv, hd, ps, ctx_lens, q_lens, window, seed, spike=None):
+def _run_fast_attention(q_all, kc, vc, out, row_req, positions, tables, q_lens, ctx_lens, H, Hkv, hd, ps, scale, window):
+    """The tensor-core kernels: single tokens through the decode kernel, portions through prefill."""
+    kern = K()
+    G = H // Hkv
+    per_tile = 64 // G
+    decode_rows, work, row = [], [], 0
+    for r, n in enumerate(q_lens):
+        if n == 1:
+            decode_rows.append(row)
+        else:
+            for t in range(0, n, per_tile):
+                work.append([row + t, min(per_tile, n - t), r])
+        row += n
+    if decode_rows:
+        chunk = kern.attention_chunk_keys()
+        max_chunks = (max(ctx_lens) + chunk - 1) // chunk + 2
+        n_chunks = (max(ctx_lens[r] for r, n in enumerate(q_lens) if n == 1) + chunk - 1) // chunk
+        part_o = torch.full((len(decode_rows) * H * max_chunks * hd,), float("nan"), device=DEV)
+        part_ml = torch.full((len(decode_rows) * H * max_chunks * 2,), float("nan"), device=DEV)
+        kern.attention_decode(q_all, kc, vc, out, torch.tensor(decode_rows, dtype=torch.int32, device=DEV), row_req,
+                              positions, tables, H, Hkv, hd, ps, scale, window, part_o, part_ml, max_chunks, n_chunks)
+    if work:
+        kern.attention_prefill(q_all, kc, vc, out, torch.tensor(work, dtype=torch.int32, device=DEV), positions, tables,
+                               H, Hkv, hd, ps, scale, window)
+
+
+def _attention_case(dtype, H, Hkv, hd, ps, ctx_lens, q_lens, window, seed, spike=None, fast=False):
     """Requests with ``ctx_lens`` cached positions of which the last ``q_lens`` are this step's
     queries. Pages are scattered and unused pages hold NaN. ``spike`` = (request, key position):
     that key is made to match every query of the request strongly."""
@@ -189,9 +215,12 @@ def _attention_case(dtype, H, Hkv, hd, ps, ctx_lens, q_lens, window, seed, spike
     q_all = torch.cat(qs).reshape(-1, H * hd).to(dt(dtype)).to(DEV)
     out = torch.full_like(q_all, float("nan"))
     scale = 1.0 / math.sqrt(hd)
-    K().attention_generic(q_all, kc, vc, out, torch.tensor(row_req, dtype=torch.int32, device=DEV),
-                          torch.tensor(positions, dtype=torch.int32, device=DEV), tables.to(DEV), H, Hkv, hd, ps, scale,
-                          window)
+    rr = torch.tensor(row_req, dtype=torch.int32, device=DEV)
+    pp = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    if fast:
+        _run_fast_attention(q_all, kc, vc, out, rr, pp, tables.to(DEV), q_lens, ctx_lens, H, Hkv, hd, ps, scale, window)
+    else:
+        K().attention_generic(q_all, kc, vc, out, rr, pp, tables.to(DEV), H, Hkv, hd, ps, scale, window)
     want = []
     for r in range(R):
         full_q = torch.zeros(ctx_lens[r], H, hd)
@@ -324,3 +353,36 @@ def test_gemm_tensor_cores_refuses_what_tma_cannot_address():
     w = torch.zeros(8, 100, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(KernelError, match="multiples of 8"):
         K().gemm_tc(a, w, torch.empty(4, 8, device=DEV))
+
+
+@pytest.mark.parametrize("H,Hkv,hd,ps", [(4, 2, 16, 16), (3, 1, 32, 8), (8, 2, 64, 16), (32, 8, 64, 16), (8, 2, 128, 32), (5, 5, 64, 4),
+                                          (16, 1, 32, 16)])
+def test_attention_tensor_cores_mixed_rows(H, Hkv, hd, ps):
+    """The mma kernels on a whole prompt, single tokens deep in long contexts (several chunks, a
+    chunk edge, a tile edge), a portion over page edges, and position 0 alone."""
+    got, want = _attention_case("bfloat16", H, Hkv, hd, ps, ctx_lens=[150, 700, 3 * ps + 1, 1, 256, 257, 64, 65],
+                                q_lens=[150, 1, ps + 2, 1, 1, 1, 1, 1], window=None, seed=6, fast=True)
+    close(got, want, "bfloat16", "attention (tensor cores)", bf16_tol=1e-2)
+
+
+@pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 255, 256, 511, 597])
+@pytest.mark.parametrize("q_len", [1, 3])
+def test_attention_tensor_cores_far_key(far, q_len):
+    got, want = _attention_case("bfloat16", 8, 2, 64, 16, ctx_lens=[600], q_lens=[q_len], window=None, seed=7,
+                                spike=(0, far), fast=True)
+    assert float(want.abs().mean()) > 2.0
+    close(got, want, "bfloat16", f"far key {far}", bf16_tol=1e-2)
+
+
+@pytest.mark.parametrize("window", [1, 5, 16, 33, 300])
+def test_attention_tensor_cores_window_edge(window):
+    ctx = 700
+    for q_len in (window + 2, 1):      # a portion straddling the edge; and a single token whose edge key is just outside
+        got, want = _attention_case("bfloat16", 4, 2, 32, 16, ctx_lens=[ctx], q_lens=[q_len], window=window, seed=8,
+                                    spike=(0, ctx - 1 - window), fast=True)
+        close(got, want, "bfloat16", f"window {window} q_len {q_len}", bf16_tol=1e-2)
+        assert float(want[-1].abs().mean()) < 2.0
+    got, want = _attention_case("bfloat16", 4, 2, 32, 16, ctx_lens=[ctx], q_lens=[1], window=window, seed=8,
+                                spike=(0, ctx - window), fast=True)          # just inside
+    close(got, want, "bfloat16", f"window {window} inside", bf16_tol=1e-2)
+    assert float(want[-1].abs().mean()) > 2.0

@@ -51,6 +51,9 @@ class _Ctx:
 
     def __init__(self, dtype, lens, Hkv, hd, page_size=8):
         self.page_size = page_size
+        self.max_requests = len(lens)
+        self._lens = list(lens)
+        self._starts = [sum(lens[:i]) for i in range(len(lens))]
         T = sum(lens)
         self.n_tokens = T
         self.positions = torch.cat([torch.arange(n) for n in lens]).int().to(DEV)
@@ -72,8 +75,15 @@ class _Ctx:
     def block_tables(self, layer):
         return self._tables
 
-    def scratch(self, name, shape, dtype):
-        return torch.empty(shape, dtype=dtype, device=DEV)
+    def scratch(self, name, shape, dtype, capacity=None):
+        return torch.full(shape, float("nan"), dtype=dtype, device=DEV)
+
+    def attention_work(self, per_tile):
+        single = [s for s, n in zip(self._starts, self._lens) if n == 1]
+        tiles = [(s + t, min(per_tile, n - t), r) for r, (s, n) in enumerate(zip(self._starts, self._lens)) if n > 1
+                 for t in range(0, n, per_tile)]
+        return (torch.tensor(single, dtype=torch.int32, device=DEV),
+                torch.tensor(tiles, dtype=torch.int32, device=DEV).reshape(len(tiles), 3), 1)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -104,7 +114,7 @@ def test_attention_mixer_part(dtype):
         q = rnd(pm.plain_rope(qkv[:, :H * hd].reshape(n, H, hd), cos, sin))
         k = rnd(pm.plain_rope(qkv[:, H * hd:(H + Hkv) * hd].reshape(n, Hkv, hd), cos, sin))
         v = rnd(qkv[:, (H + Hkv) * hd:].reshape(n, Hkv, hd))
-        want = x[start:start + n] + rnd(pm.plain_attention(q, k, v, 0.25)).reshape(n, H * hd) @ w_o.T
+        want = x[start:start + n] + rnd(pm.plain_attention(q, k, v, 0.25, None, None if dtype is torch.float32 else rnd)).reshape(n, H * hd) @ w_o.T
         err = tt.rel_err(x_dev[start:start + n].cpu().numpy(), want.numpy())
         assert err < (1e-5 if dtype is torch.float32 else 1.5e-2), f"segment at {start}: {err}"
         start += n
