@@ -325,6 +325,244 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     }
 }
 
+// ------------------------------------------------------------------------------------------ persistent kernel
+// Many tokens: one CTA per SM walks over output tiles. Tensor memory holds two accumulators, so
+// the epilogue of one tile (tcgen05.ld -> swizzled staging in shared memory -> TMA store or TMA
+// reduce-add into the 32-bit residual stream) runs while the MMAs of the next tile are issued.
+// Epilogues: store 32-bit, add to 32-bit, or SwiGLU: the tile's first half of columns are gate
+// channels and the second half the matching up channels (two TMA loads per stage from the
+// [gate; up] weight), and silu(gate) * up is stored as bfloat16.
+enum TcEpilogue : int { kEpiStoreF32 = 0, kEpiAddF32 = 1, kEpiSwiGLU = 2 };
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <int BLOCK_Q>
+struct TcPersistentConfig {
+    static constexpr int kStageBytesP = kBlockP * kBlockK * 2;
+    static constexpr int kStageBytesQ = BLOCK_Q * kBlockK * 2;
+    static constexpr int kStageBytes = kStageBytesP + kStageBytesQ;
+    static constexpr int kStages = (BLOCK_Q >= 256) ? 4 : 6;
+    static constexpr int kStagingBytes = kBlockP * 128;          // 128 rows x 128 bytes, two of them
+    static constexpr int kTmemCols = 2 * BLOCK_Q;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 2 * kStagingBytes + 1024 + 256;
+    static constexpr uint32_t kIdesc = TcConfig<BLOCK_Q>::kIdesc;
+};
+
+struct TcPersistentParams {
+    int rows_p, rows_q, K;       // tokens, output columns of the accumulator tile space, reduction length
+    int tiles_p, tiles_q;
+    int up_row_offset;           // SwiGLU: row of the first up channel in the weight (= I)
+    int* status;
+};
+
+template <int BLOCK_Q, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                          const __grid_constant__ CUtensorMap map_c, const TcPersistentParams p) {
+    using Cfg = TcPersistentConfig<BLOCK_Q>;
+    constexpr int kStages = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* staging = smem + kStages * Cfg::kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + 2 * Cfg::kStagingBytes);
+    // bars: [0,S) full, [S,2S) empty, [2S,2S+2) accumulator full, [2S+2,2S+4) accumulator empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_kb = (p.K + kBlockK - 1) / kBlockK;
+    const int n_tiles = p.tiles_p * p.tiles_q;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);
+            mbar_init(smem_u32(&bars[kStages + s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bars[2 * kStages + b]), 1);
+            mbar_init(smem_u32(&bars[2 * kStages + 2 + b]), 128);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    grid_launch_dependents();
+    grid_dependency_wait();          // everything below reads what earlier kernels wrote
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0, issued_ok = 1;
+            for (int t = blockIdx.x; t < n_tiles && issued_ok; t += gridDim.x) {
+                const int tile_p = t % p.tiles_p, tile_q = t / p.tiles_p;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait(smem_u32(&bars[kStages + s]), ((it / kStages) & 1) ^ 1, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, kErrProducerWait); }
+                        issued_ok = 0;
+                        break;
+                    }
+                    const uint32_t full = smem_u32(&bars[s]);
+                    mbar_expect_tx(full, Cfg::kStageBytes);
+                    uint8_t* stage = smem + s * Cfg::kStageBytes;
+                    const int k0 = kb * kBlockK;
+                    tma_load_2d(smem_u32(stage), &map_p, k0, tile_p * kBlockP, full);
+                    if (EPI == kEpiSwiGLU) {
+                        const int n0 = tile_q * (BLOCK_Q / 2);
+                        tma_load_2d(smem_u32(stage + Cfg::kStageBytesP), &map_q, k0, n0, full);
+                        tma_load_2d(smem_u32(stage + Cfg::kStageBytesP + Cfg::kStageBytesQ / 2), &map_q, k0, p.up_row_offset + n0, full);
+                    } else {
+                        tma_load_2d(smem_u32(stage + Cfg::kStageBytesP), &map_q, k0, tile_q * BLOCK_Q, full);
+                    }
+                }
+            }
+            if (*abort_flag) {
+                const int first = max(0, it - kStages);
+                for (int i = first; i < it; ++i) {
+                    const unsigned long long t0 = clock64();
+                    while (!mbar_try_wait(smem_u32(&bars[i % kStages]), (i / kStages) & 1)) {
+                        if (clock64() - t0 > kWaitCycles) { atomicCAS(p.status, 0, kErrDrain); break; }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int it = 0, j = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++j) {
+                const int buf = j & 1;
+                if (!mbar_wait(smem_u32(&bars[2 * kStages + 2 + buf]), ((j >> 1) & 1) ^ 1, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, kErrMmaWait); }
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + buf * BLOCK_Q;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait(smem_u32(&bars[s]), (it / kStages) & 1, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, kErrMmaWait); }
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes);
+                    const uint64_t desc_p = umma_desc(a_addr);
+                    const uint64_t desc_q = umma_desc(a_addr + Cfg::kStageBytesP);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 16; ++k)
+                        umma_bf16(tmem_d, desc_p + 2 * k, desc_q + 2 * k, Cfg::kIdesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(smem_u32(&bars[kStages + s]));
+                }
+                if (ok) umma_commit(smem_u32(&bars[2 * kStages + buf]));
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..5)
+        const int lane_group = warp & 3;
+        const int row = lane_group * 32 + lane;                  // row of the tile = TMEM lane
+        const bool leader = (warp == 2 && lane == 0);
+        const uint32_t lane_addr = static_cast<uint32_t>(lane_group * 32) << 16;
+        int j = 0, n_stores = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++j) {
+            const int tile_p = t % p.tiles_p, tile_q = t / p.tiles_p;
+            const int buf = j & 1;
+            if (ok && !mbar_wait(smem_u32(&bars[2 * kStages + buf]), (j >> 1) & 1, abort_flag)) {
+                if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, kErrEpilogueWait); }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (*abort_flag) ok = false;                          // read after the barrier: one decision for all
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t tmem_d = tmem_base + buf * BLOCK_Q + lane_addr;
+            constexpr int kChunks = (EPI == kEpiSwiGLU) ? BLOCK_Q / 128 : BLOCK_Q / 32;   // TMA stores per tile
+            for (int c = 0; c < kChunks; ++c) {
+                uint8_t* stg = staging + (n_stores & 1) * Cfg::kStagingBytes;
+                if (leader) bulk_wait_read1();                    // the store issued two chunks ago has read its staging
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                uint32_t r[32];
+                if (EPI == kEpiSwiGLU) {
+                    // 64 output channels per store, in two halves of 32: gate at column ch, up at BLOCK_Q/2 + ch
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const int ch = c * 64 + half * 32;
+                        uint32_t u[32];
+                        tmem_ld_x16(tmem_d + ch, r);
+                        tmem_ld_x16(tmem_d + ch + 16, r + 16);
+                        tmem_ld_x16(tmem_d + BLOCK_Q / 2 + ch, u);
+                        tmem_ld_x16(tmem_d + BLOCK_Q / 2 + ch + 16, u + 16);
+                        tmem_ld_wait();
+                        if (c == kChunks - 1 && half == 1) { tc_fence_before(); mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf])); }
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {          // 8 channels = 16 bytes of bfloat16 per step
+                            uint32_t packed[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float g0 = __uint_as_float(r[q4 * 8 + 2 * e]), g1 = __uint_as_float(r[q4 * 8 + 2 * e + 1]);
+                                const float u0 = __uint_as_float(u[q4 * 8 + 2 * e]), u1 = __uint_as_float(u[q4 * 8 + 2 * e + 1]);
+                                const float h0 = g0 * (1.0f / (1.0f + expf(-g0))) * u0;
+                                const float h1 = g1 * (1.0f / (1.0f + expf(-g1))) * u1;
+                                __nv_bfloat162 hb = __floats2bfloat162_rn(h0, h1);
+                                packed[e] = *reinterpret_cast<uint32_t*>(&hb);
+                            }
+                            const int chunk16 = half * 4 + q4;
+                            *reinterpret_cast<uint4*>(stg + row * 128 + ((chunk16 ^ (row & 7)) * 16)) =
+                                make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        }
+                    }
+                } else {
+                    tmem_ld_x16(tmem_d + c * 32, r);
+                    tmem_ld_x16(tmem_d + c * 32 + 16, r + 16);
+                    tmem_ld_wait();
+                    if (c == kChunks - 1) { tc_fence_before(); mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf])); }
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; ++q4)
+                        *reinterpret_cast<uint4*>(stg + row * 128 + ((q4 ^ (row & 7)) * 16)) =
+                            make_uint4(r[q4 * 4], r[q4 * 4 + 1], r[q4 * 4 + 2], r[q4 * 4 + 3]);
+                }
+                fence_async_smem();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (leader) {
+                    const int col = (EPI == kEpiSwiGLU) ? tile_q * (BLOCK_Q / 2) + c * 64 : tile_q * BLOCK_Q + c * 32;
+                    if (EPI == kEpiAddF32) tma_reduce_add_2d(&map_c, smem_u32(stg), col, tile_p * kBlockP);
+                    else tma_store_2d(&map_c, smem_u32(stg), col, tile_p * kBlockP);
+                    bulk_commit();
+                }
+                ++n_stores;
+            }
+        }
+        if (leader) bulk_wait_all();
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
 // ------------------------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -357,6 +595,50 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, long lo
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("gemm_tc: cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r)); return 1; }
     return 0;
+}
+
+// The output matrix [rows, cols] (row stride ld elements) as boxes of 128 rows x 128 bytes with the
+// 128-byte swizzle the epilogue writes its staging in; stores beyond rows or cols are clipped.
+static int make_out_map(CUtensorMap* map, void* base, int rows, int cols, long long ld, bool bf16) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("gemm_tc: cuTensorMapEncodeTiled is not available from the driver"); return 1; }
+    const int elt = bf16 ? 2 : 4;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elt};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elt), static_cast<cuuint32_t>(kBlockP)};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides,
+                    box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("gemm_tc: cuTensorMapEncodeTiled (output) failed with code %d", static_cast<int>(r)); return 1; }
+    return 0;
+}
+
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 1;
+    }
+    return n;
+}
+
+template <int BLOCK_Q, int EPI>
+static int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, const CUtensorMap& mc,
+                             const TcPersistentParams& p, cudaStream_t st) {
+    using Cfg = TcPersistentConfig<BLOCK_Q>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BLOCK_Q, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) { set_error("gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::kSmemBytes, cudaGetErrorString(e)); return 1; }
+        configured = true;
+    }
+    const int tiles = p.tiles_p * p.tiles_q;
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    gemm_tc_persistent_kernel<BLOCK_Q, EPI><<<grid, kThreads, Cfg::kSmemBytes, st>>>(mp, mq, mc, p);
+    return check_launch("gemm_tc_persistent");
 }
 
 template <int BLOCK_Q>
@@ -444,4 +726,46 @@ extern "C" int gi_gemm_tc_status(const void* status, void* stream, int* out) {
     if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) { set_error("gemm_tc_status: %s", cudaGetErrorString(e)); return 1; }
     return 0;
+}
+
+// Many tokens, one persistent CTA per SM. epilogue 0: C[M,N] = A W^T (32-bit); 1: C += A W^T (32-bit);
+// 2: W is [2N, K] = [gate; up] and C[M,N] = silu(A Wgate^T) * (A Wup^T) as bfloat16.
+// block_q: 256 or 128 accumulator columns per tile.
+extern "C" int gi_gemm_tc_persistent(const void* A, const void* W, void* C, int epilogue, int M, int N, int K,
+                                     long long lda, long long ldw, long long ldc, int block_q, void* status,
+                                     void* stream) {
+    if (M == 0 || N == 0) return 0;
+    GI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: sizes must be positive (M=%d, N=%d, K=%d)", M, N, K);
+    GI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
+               "gemm_tc: K=%d and the row strides (%lld, %lld) must be multiples of 8 (16-byte rows for TMA)", K, lda, ldw);
+    GI_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_tc: unknown epilogue %d", epilogue);
+    const bool bf16_out = epilogue == kEpiSwiGLU;
+    GI_REQUIRE((ldc * (bf16_out ? 2 : 4)) % 16 == 0, "gemm_tc: the output row stride %lld is not a multiple of 16 bytes", ldc);
+    GI_REQUIRE((reinterpret_cast<uintptr_t>(A) % 16 == 0) && (reinterpret_cast<uintptr_t>(W) % 16 == 0) &&
+               (reinterpret_cast<uintptr_t>(C) % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
+    GI_REQUIRE(block_q == 128 || block_q == 256, "gemm_tc: block_q=%d is not 128 or 256", block_q);
+    GI_REQUIRE(status != nullptr, "gemm_tc: a status word is required");
+    TcPersistentParams p;
+    p.rows_p = M; p.rows_q = N; p.K = K;
+    p.tiles_p = (M + kBlockP - 1) / kBlockP;
+    p.up_row_offset = N;
+    p.status = static_cast<int*>(status);
+    CUtensorMap mp, mq, mc;
+    if (make_map(&mp, A, M, K, lda, kBlockP)) return 1;
+    if (make_out_map(&mc, C, M, N, ldc, bf16_out)) return 1;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (epilogue == kEpiSwiGLU) {
+        p.tiles_q = (N + block_q / 2 - 1) / (block_q / 2);
+        if (make_map(&mq, W, 2 * N, K, ldw, block_q / 2)) return 1;
+        if (block_q == 256) return launch_persistent<256, kEpiSwiGLU>(mp, mq, mc, p, st);
+        return launch_persistent<128, kEpiSwiGLU>(mp, mq, mc, p, st);
+    }
+    p.tiles_q = (N + block_q - 1) / block_q;
+    if (make_map(&mq, W, N, K, ldw, block_q)) return 1;
+    if (block_q == 256) {
+        if (epilogue == kEpiAddF32) return launch_persistent<256, kEpiAddF32>(mp, mq, mc, p, st);
+        return launch_persistent<256, kEpiStoreF32>(mp, mq, mc, p, st);
+    }
+    if (epilogue == kEpiAddF32) return launch_persistent<128, kEpiAddF32>(mp, mq, mc, p, st);
+    return launch_persistent<128, kEpiStoreF32>(mp, mq, mc, p, st);
 }

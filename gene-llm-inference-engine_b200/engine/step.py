@@ -65,6 +65,12 @@ class StepContext:
         self._cache: Dict = {}
         self.all_single = all(s.length == 1 for s in segments)
         self.max_context = max((s.first_position + s.length for s in segments), default=0)
+        # longest context among requests that bring a single token, rounded up to 1024 positions:
+        # the grid of the decode attention depends on it, and a coarse value keeps the set of
+        # distinct step shapes (and of captured graphs) small; chunks beyond a row's own
+        # position exit at once
+        longest = max((s.first_position + 1 for s in segments if s.length == 1), default=0)
+        self.longest_single = min(engine.model.max_position, (longest + 1023) // 1024 * 1024)
 
     def pages(self, layer: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """(keys, values) of a layer, each [pages, Hkv, page_size, head_dim]."""
@@ -86,6 +92,10 @@ class StepContext:
         that bring a single token [n] on the device, tiles of longer portions [m, 3] = (first
         row, tokens, request), longest context among the single tokens). Built once per step."""
         key = ("attention_work", tokens_per_tile)
+        if key not in self._cache and self.all_single:
+            # decode-only step: rows 0..R-1 in order, no tiles, nothing to upload (and so nothing
+            # that a captured graph would have to re-read from the host)
+            self._cache[key] = (self._engine.row_index[:self.n_tokens], self._engine.no_work, self.longest_single)
         if key not in self._cache:
             single = [s.start for s in self.segments if s.length == 1]
             tiles = []
@@ -93,7 +103,7 @@ class StepContext:
                 if s.length > 1:
                     for t in range(0, s.length, tokens_per_tile):
                         tiles.append((s.start + t, min(tokens_per_tile, s.length - t), r))
-            longest = max((s.first_position + 1 for s in self.segments if s.length == 1), default=0)
+            longest = self.longest_single
             flat = single + [v for tile in tiles for v in tile]
             dev = self._engine.upload_ints(flat)
             rows = dev[:len(single)]
@@ -104,7 +114,7 @@ class StepContext:
 
 class StepEngine:
     def __init__(self, model: DecoderModel, page_size: int = 16, n_pages: int = 256, max_requests: int = 8,
-                 max_step_tokens: int = 2048, max_logit_rows: Optional[int] = None):
+                 max_step_tokens: int = 2048, max_logit_rows: Optional[int] = None, use_graphs: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("StepEngine needs a CUDA device: this engine has no CPU path")
         self.model = model
@@ -135,6 +145,15 @@ class StepEngine:
                                                   device=self.device)
         self._scratch: Dict[Tuple, torch.Tensor] = {}
         self._init_descriptor()
+        self.row_index = torch.arange(max(max_step_tokens, max_requests), dtype=torch.int32, device=self.device)
+        self.no_work = torch.zeros((0, 3), dtype=torch.int32, device=self.device)
+        # decode-only steps are captured into CUDA graphs, one per (requests, wanted rows, context bucket)
+        # (only when every part says that its launches depend on nothing but the step's shape)
+        self.use_graphs = use_graphs and all(
+            getattr(layer.mixer, "graph_safe", False) and getattr(layer.feed_forward, "graph_safe", False)
+            for layer in model.layers)
+        self._graphs: Dict[Tuple, Tuple] = {}
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ memory
     def scratch(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype, capacity: Optional[int] = None) -> torch.Tensor:
@@ -313,10 +332,37 @@ class StepEngine:
                 for st in self.layer_state.values():
                     st[seg.state_slot].zero_()
         ctx = StepContext(self, total, R, k, segments, views)
-        logits = self.model.forward(ctx)
+        logits = self._run(ctx)
         for e in entries:
             self.cache.advance(self.cache.requests[e.key], len(e.tokens))
         return logits
+
+    def _run(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        """The model's forward pass for this step. A decode-only step (one token per request, no
+        state to zero) has a fixed launch sequence for its shape: it is run once directly, then
+        captured into a CUDA graph and replayed from then on, which removes the per-launch cost on
+        the host. Everything a replay reads that changes from step to step (tokens, positions,
+        block tables) lives in the descriptor buffer, refreshed before the replay."""
+        fresh = any(s.fresh_state for s in ctx.segments) and self.layer_state
+        if not (self.use_graphs and ctx.all_single and not fresh):
+            return self.model.forward(ctx)
+        key = (ctx.n_tokens, ctx.n_logit_rows, ctx.longest_single)
+        entry = self._graphs.get(key)
+        if entry is None:
+            out = self.model.forward(ctx)          # also sizes scratch and configures the kernels
+            before = kernels.launch_count()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                captured = self.model.forward(ctx)
+            n_kernels = kernels.launch_count() - before
+            kernels.count_launches(-n_kernels)     # captured, not launched
+            self._graphs[key] = (graph, captured, n_kernels)
+            return out
+        graph, captured, n_kernels = entry
+        graph.replay()
+        self.graph_replays += 1
+        kernels.count_launches(n_kernels)
+        return captured
 
     def _copy_pages(self, copies) -> None:
         for g, pages in enumerate(self.group_pages):

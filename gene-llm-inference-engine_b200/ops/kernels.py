@@ -31,6 +31,12 @@ def launch_count() -> int:
     return _launches
 
 
+def count_launches(n: int) -> None:
+    """Adjusts the count for kernels that run from a replayed CUDA graph (or were only captured)."""
+    global _launches
+    _launches += n
+
+
 def _stream() -> int:
     global _launches
     _launches += 1
@@ -251,10 +257,35 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
         raise KernelError(f"gemm: shapes do not agree (a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)})")
     swap, block_q, splits = plan or gemm_tc_plan(M, N, K)
     st = _tc_state(a.device)
+    if not swap and out.dtype is torch.float32 and N % 4 == 0 and block_q >= 128:
+        # many tokens, 32-bit output: the persistent kernel (epilogue overlapped, TMA stores)
+        check(lib().gi_gemm_tc_persistent(_dev(a, "a", torch.bfloat16), _dev(w, "w", torch.bfloat16),
+                                          _dev(out, "out", torch.float32), 1 if accumulate else 0, M, N, K, K, K, N,
+                                          block_q, st.status.data_ptr(), _stream()), "gemm_tc")
+        return
     check(lib().gi_gemm_tc(_dev(a, "a", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"),
                            dtype_code(out.dtype), int(accumulate), M, N, K, K, K, N, int(swap), block_q, splits,
                            st.workspace.data_ptr(), st.workspace.numel(), st.counters.data_ptr(), st.counters.numel(),
                            st.status.data_ptr(), _stream()), "gemm_tc")
+
+
+def gemm_swiglu_supported(M: int, I: int, K: int) -> bool:
+    """The fused gate/up product needs many tokens (tokens on the 128-row side) and TMA-addressable rows."""
+    return M > 128 and K % 8 == 0 and I % 8 == 0
+
+
+def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, I] = silu(a @ w_gate^T) * (a @ w_up^T) as bfloat16, w_gate_up = [gate rows; up rows]
+    [2I, K]: one tensor-core kernel whose epilogue applies the activation (the [M, 2I] intermediate
+    never exists in memory)."""
+    M, K = a.shape
+    I = out.shape[1]
+    if w_gate_up.shape != (2 * I, K) or out.shape[0] != M:
+        raise KernelError("gemm_swiglu: shapes do not agree")
+    st = _tc_state(a.device)
+    check(lib().gi_gemm_tc_persistent(_dev(a, "a", torch.bfloat16), _dev(w_gate_up, "w_gate_up", torch.bfloat16),
+                                      _dev(out, "out", torch.bfloat16), 2, M, I, K, K, K, I, 256,
+                                      st.status.data_ptr(), _stream()), "gemm_swiglu")
 
 
 def gemm_tc_status(device: torch.device) -> int:

@@ -20,6 +20,9 @@ class AttentionMixer:
     after the dot product), ``window`` (None = all keys) and ``position`` (a PartSpec).
     Weights: ``w_qkv`` [(H+2Hkv)*hd, hidden] and ``w_o`` [hidden, H*hd]."""
 
+    graph_safe = True      # launches depend only on the step's shape: decode steps may be captured in a CUDA graph
+
+
     def __init__(self, params, weights, build):
         self.hidden_size = int(params["hidden_size"])
         self.num_heads = int(params["num_heads"])

@@ -15,6 +15,9 @@ class SwiGLUFeedForward:
     Params: ``hidden_size``, ``intermediate_size``. Weights: ``w_gate_up`` [2I, hidden] (gate rows
     first, then up rows) and ``w_down`` [hidden, I]."""
 
+    graph_safe = True      # launches depend only on the step's shape: decode steps may be captured in a CUDA graph
+
+
     def __init__(self, params, weights, build):
         self.hidden_size = int(params["hidden_size"])
         self.intermediate_size = int(params["intermediate_size"])
@@ -29,8 +32,11 @@ class SwiGLUFeedForward:
 
     def forward(self, ctx, xn: torch.Tensor, x: torch.Tensor) -> None:
         T = xn.shape[0]
-        gu = ctx.scratch("gate_up", (T, 2 * self.intermediate_size), torch.float32)
-        self.w_gate_up.forward(xn, gu)
         h = ctx.scratch("ffn_hidden", (T, self.intermediate_size), self.dtype)
-        kernels.swiglu(gu, h)
+        if self.dtype is torch.bfloat16 and kernels.gemm_swiglu_supported(T, self.intermediate_size, self.hidden_size):
+            kernels.gemm_swiglu(xn, self.w_gate_up.weight, h)      # activation in the product's epilogue
+        else:
+            gu = ctx.scratch("gate_up", (T, 2 * self.intermediate_size), torch.float32)
+            self.w_gate_up.forward(xn, gu)
+            kernels.swiglu(gu, h)
         self.w_down.forward(h, x, accumulate=True)

@@ -386,3 +386,39 @@ def test_attention_tensor_cores_window_edge(window):
                                 spike=(0, ctx - window), fast=True)          # just inside
     close(got, want, "bfloat16", f"window {window} inside", bf16_tol=1e-2)
     assert float(want[-1].abs().mean()) > 2.0
+
+
+@pytest.mark.parametrize("M,I,K_", [(129, 128, 64), (300, 200, 96), (256, 1000, 512), (2048, 264, 160)])
+def test_gemm_swiglu_fused(M, I, K_):
+    """The gate/up product with the activation in its epilogue against the plain two-step form."""
+    g = torch.Generator().manual_seed(12)
+    a = torch.randn(M, K_, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * I, K_, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
+    guard = torch.full((M + 2, I), -1024.0, dtype=torch.bfloat16, device=DEV)
+    out = guard[1:M + 1]
+    out.fill_(float("nan"))
+    assert K().gemm_swiglu_supported(M, I, K_)
+    K().gemm_swiglu(a, w, out)
+    assert K().gemm_tc_status(torch.device(DEV)) == 0
+    gu = a.float().cpu().double() @ w.float().cpu().double().T
+    want = pm.plain_swiglu(gu[:, :I].float(), gu[:, I:].float())
+    close(out, want, "bfloat16", "gemm_swiglu", bf16_tol=1e-2)
+    assert float(guard[0].float().min()) == -1024.0 == float(guard[-1].float().max()), "wrote outside the output"
+
+
+@pytest.mark.parametrize("M,N,K_,block_q", [(128, 256, 64, 256), (1000, 1028, 200, 256), (130, 96, 96, 128), (2048, 3072, 2048, 256),
+                                            (517, 384, 160, 128)])
+def test_gemm_persistent_many_tiles(M, N, K_, block_q):
+    """More tiles than SMs, both accumulator buffers in use, store and add epilogues."""
+    g = torch.Generator().manual_seed(13)
+    a = torch.randn(M, K_, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(N, K_, generator=g).to(torch.bfloat16).to(DEV)
+    want = a.float().cpu().double() @ w.float().cpu().double().T
+    out = torch.full((M, N), float("nan"), device=DEV)
+    K().gemm_tc(a, w, out, plan=(False, block_q, 1))
+    close(out, want, "float32", "persistent store", f32_tol=2e-6 * max(1, K_ / 64))
+    base = torch.randn(M, N, generator=g).to(DEV)
+    acc = base.clone()
+    K().gemm_tc(a, w, acc, accumulate=True, plan=(False, block_q, 1))
+    close(acc, want + base.cpu().double(), "float32", "persistent add", f32_tol=2e-6 * max(1, K_ / 64))
+    assert K().gemm_tc_status(torch.device(DEV)) == 0
