@@ -59,6 +59,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                const int* __restrict__ row_req, const int* __restrict__ positions,
                                const int* __restrict__ block_tables, int table_stride, int H, int Hkv, int hd,
                                int page_size, float scale, int window) {
+    pdl_prologue();
     __shared__ float s_q[kMaxHeadDim];
     __shared__ float s_acc[kAttWarps][kMaxHeadDim];
     __shared__ float s_m[kAttWarps], s_l[kAttWarps];
@@ -156,12 +157,12 @@ extern "C" int gi_attention_generic(const void* q, const void* k_cache, const vo
     dim3 grid(H, T);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == kF32) {
-        paged_attention_generic_kernel<float><<<grid, kAttWarps * 32, 0, st>>>(
+        launch_kernel((paged_attention_generic_kernel<float>), dim3(grid), dim3(kAttWarps * 32), 0, st, 
             static_cast<const float*>(q), static_cast<const float*>(k_cache), static_cast<const float*>(v_cache),
             static_cast<float*>(out), row_req, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale,
             window);
     } else if (dtype == kBF16) {
-        paged_attention_generic_kernel<__nv_bfloat16><<<grid, kAttWarps * 32, 0, st>>>(
+        launch_kernel((paged_attention_generic_kernel<__nv_bfloat16>), dim3(grid), dim3(kAttWarps * 32), 0, st, 
             static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
             static_cast<const __nv_bfloat16*>(v_cache), static_cast<__nv_bfloat16*>(out), row_req, positions,
             block_tables, table_stride, H, Hkv, hd, page_size, scale, window);

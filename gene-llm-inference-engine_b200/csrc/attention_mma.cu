@@ -193,6 +193,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int* __restrict__ block_tables, int table_stride, int H, int Hkv, int page_size,
                         float scale_log2, int window, float* __restrict__ part_o, float* __restrict__ part_ml,
                         int max_chunks) {
+    pdl_prologue();
     extern __shared__ __align__(128) uint8_t smem[];
     const int G = H / Hkv;
     const int chunk = blockIdx.x, g = blockIdx.y, idx = blockIdx.z;
@@ -293,6 +294,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          const int* __restrict__ rows, const int* __restrict__ positions,
                                          __nv_bfloat16* __restrict__ out, int H, int HD, int max_chunks, int window) {
+    pdl_prologue();
     const int h = blockIdx.x, idx = blockIdx.y;
     const int t = rows[idx];
     const int pos = positions[t];
@@ -324,6 +326,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ work, const int* __restrict__ positions,
                          const int* __restrict__ block_tables, int table_stride, int H, int Hkv, int page_size,
                          float scale_log2, int window) {
+    pdl_prologue();
     extern __shared__ __align__(128) uint8_t smem[];
     const int G = H / Hkv;
     const int g = blockIdx.y;
@@ -424,12 +427,12 @@ static int launch_decode(const void* q, const void* kc, const void* vc, void* ou
         configured = true;
     }
     dim3 grid(n_chunks, Hkv, n_rows);
-    attention_decode_kernel<HD><<<grid, kAttThreads, bytes, st>>>(
+    launch_kernel((attention_decode_kernel<HD>), dim3(grid), dim3(kAttThreads), bytes, st, 
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc),
         rows, row_req, positions, tables, table_stride, H, Hkv, page_size, scale * kLog2e, window, part_o, part_ml, max_chunks);
     if (check_launch("attention_decode")) return 1;
     dim3 grid2(H, n_rows);
-    attention_combine_kernel<<<grid2, HD < 32 ? 32 : HD, 0, st>>>(part_o, part_ml, rows, positions,
+    launch_kernel((attention_combine_kernel), dim3(grid2), dim3(HD < 32 ? 32 : HD), 0, st, part_o, part_ml, rows, positions,
                                                                    static_cast<__nv_bfloat16*>(out), H, HD, max_chunks, window);
     return check_launch("attention_combine");
 }
@@ -446,7 +449,7 @@ static int launch_prefill(const void* q, const void* kc, const void* vc, void* o
         configured = true;
     }
     dim3 grid(n_work, Hkv);
-    attention_prefill_kernel<HD><<<grid, kAttThreads, bytes, st>>>(
+    launch_kernel((attention_prefill_kernel<HD>), dim3(grid), dim3(kAttThreads), bytes, st, 
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc),
         static_cast<__nv_bfloat16*>(out), work, positions, tables, table_stride, H, Hkv, page_size, scale * kLog2e, window);
     return check_launch("attention_prefill");

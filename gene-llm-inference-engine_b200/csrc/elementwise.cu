@@ -14,6 +14,8 @@ namespace gi {
 
 static thread_local std::string g_error;
 
+int g_pdl_enabled = 1;
+
 void set_error(const char* fmt, ...) {
     char buf[1024];
     va_list ap;
@@ -27,6 +29,7 @@ void set_error(const char* fmt, ...) {
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int D, float scale) {
+    pdl_prologue();
     const int t = blockIdx.x;
     const TW* row = table + static_cast<size_t>(tokens[t]) * D;
     float* o = out + static_cast<size_t>(t) * D;
@@ -39,6 +42,7 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
 template <typename TOut>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                const float* __restrict__ weight, TOut* __restrict__ out, int D, float eps) {
+    pdl_prologue();
     __shared__ float warp_part[32];
     __shared__ float s_scale;
     const int r = blockIdx.x;
@@ -63,6 +67,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 // ---------------------------------------------------------------------------------- SwiGLU
 template <typename TOut>
 __global__ void swiglu_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int I, size_t total) {
+    pdl_prologue();
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t t = i / I;
@@ -83,6 +88,7 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, const int* __re
                                   const float* __restrict__ sin_t, int rot_half, int interleaved,
                                   TQ* __restrict__ q_out, TKV* __restrict__ k_cache, TKV* __restrict__ v_cache,
                                   int H, int Hkv, int hd, int page_size, int write_kv) {
+    pdl_prologue();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const float* row = qkv + static_cast<size_t>(t) * (H + 2 * Hkv) * hd;
@@ -131,6 +137,7 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, const int* __re
 // ---------------------------------------------------------------------------------- page copy
 __global__ void copy_pages_kernel(char* base, size_t array_stride, size_t page_bytes,
                                   const int* __restrict__ src, const int* __restrict__ dst) {
+    pdl_prologue();
     char* arr = base + blockIdx.y * array_stride;
     const uint4* s = reinterpret_cast<const uint4*>(arr + static_cast<size_t>(src[blockIdx.x]) * page_bytes);
     uint4* d = reinterpret_cast<uint4*>(arr + static_cast<size_t>(dst[blockIdx.x]) * page_bytes);
@@ -145,15 +152,21 @@ extern "C" {
 
 const char* gi_last_error() { return g_error.c_str(); }
 
+// Switches programmatic dependent launch on (1, the default) or off (0) for all later launches.
+int gi_set_pdl(int enabled) {
+    g_pdl_enabled = enabled ? 1 : 0;
+    return 0;
+}
+
 int gi_embed(const void* table, int table_dtype, const int* tokens, float* out, int T, int D, float scale,
              void* stream) {
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && D > 0, "embed: T and D must be positive (T=%d, D=%d)", T, D);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (table_dtype == kF32) {
-        embed_kernel<float><<<T, 256, 0, st>>>(static_cast<const float*>(table), tokens, out, D, scale);
+        launch_kernel((embed_kernel<float>), dim3(T), dim3(256), 0, st, static_cast<const float*>(table), tokens, out, D, scale);
     } else if (table_dtype == kBF16) {
-        embed_kernel<__nv_bfloat16><<<T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(table), tokens, out, D, scale);
+        launch_kernel((embed_kernel<__nv_bfloat16>), dim3(T), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(table), tokens, out, D, scale);
     } else {
         GI_REQUIRE(false, "embed: unsupported table dtype code %d", table_dtype);
     }
@@ -166,9 +179,9 @@ int gi_rmsnorm(const float* x, const int* rows, const float* weight, void* out, 
     GI_REQUIRE(n_rows > 0 && D > 0, "rmsnorm: sizes must be positive (rows=%d, D=%d)", n_rows, D);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (out_dtype == kF32) {
-        rmsnorm_kernel<float><<<n_rows, 256, 0, st>>>(x, rows, weight, static_cast<float*>(out), D, eps);
+        launch_kernel((rmsnorm_kernel<float>), dim3(n_rows), dim3(256), 0, st, x, rows, weight, static_cast<float*>(out), D, eps);
     } else if (out_dtype == kBF16) {
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, 256, 0, st>>>(x, rows, weight, static_cast<__nv_bfloat16*>(out), D, eps);
+        launch_kernel((rmsnorm_kernel<__nv_bfloat16>), dim3(n_rows), dim3(256), 0, st, x, rows, weight, static_cast<__nv_bfloat16*>(out), D, eps);
     } else {
         GI_REQUIRE(false, "rmsnorm: unsupported output dtype code %d", out_dtype);
     }
@@ -182,9 +195,9 @@ int gi_swiglu(const float* gate_up, void* out, int out_dtype, int T, int I, void
     const size_t total = static_cast<size_t>(T) * I;
     const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
     if (out_dtype == kF32) {
-        swiglu_kernel<float><<<blocks, 256, 0, st>>>(gate_up, static_cast<float*>(out), I, total);
+        launch_kernel((swiglu_kernel<float>), dim3(blocks), dim3(256), 0, st, gate_up, static_cast<float*>(out), I, total);
     } else if (out_dtype == kBF16) {
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(gate_up, static_cast<__nv_bfloat16*>(out), I, total);
+        launch_kernel((swiglu_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, st, gate_up, static_cast<__nv_bfloat16*>(out), I, total);
     } else {
         GI_REQUIRE(false, "swiglu: unsupported output dtype code %d", out_dtype);
     }
@@ -201,12 +214,12 @@ int gi_rope_store(const float* qkv, const int* positions, const int* row_req, co
     GI_REQUIRE(2 * rot_half <= hd, "rope_store: rotary size %d exceeds the head size %d", 2 * rot_half, hd);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == kF32) {
-        rope_store_kernel<float, float><<<T, 256, 0, st>>>(
+        launch_kernel((rope_store_kernel<float, float>), dim3(T), dim3(256), 0, st, 
             qkv, positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved,
             static_cast<float*>(q_out), static_cast<float*>(k_cache), static_cast<float*>(v_cache), H, Hkv, hd,
             page_size, write_kv);
     } else if (dtype == kBF16) {
-        rope_store_kernel<__nv_bfloat16, __nv_bfloat16><<<T, 256, 0, st>>>(
+        launch_kernel((rope_store_kernel<__nv_bfloat16, __nv_bfloat16>), dim3(T), dim3(256), 0, st, 
             qkv, positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved,
             static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
             static_cast<__nv_bfloat16*>(v_cache), H, Hkv, hd, page_size, write_kv);
@@ -221,7 +234,7 @@ int gi_copy_pages(void* base, long long array_stride_bytes, int n_arrays, long l
     if (n_copies == 0 || n_arrays == 0) return 0;
     GI_REQUIRE(page_bytes % 16 == 0, "copy_pages: a page of %lld bytes is not a multiple of 16", page_bytes);
     dim3 grid(n_copies, n_arrays);
-    copy_pages_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    launch_kernel((copy_pages_kernel), dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), 
         static_cast<char*>(base), static_cast<size_t>(array_stride_bytes), static_cast<size_t>(page_bytes), src, dst);
     return check_launch("copy_pages");
 }

@@ -15,6 +15,7 @@ template <typename TA, typename TW, typename TC, bool kAccumulate>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C, int M, int N, int K,
                  int lda, int ldw, int ldc) {
+    pdl_prologue();
     __shared__ float sA[kBK][kBM + 4];
     __shared__ float sW[kBK][kBN + 4];
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;      // 16 x 16 threads, 4 x 4 outputs each
@@ -74,12 +75,12 @@ int launch_simt(const void* A, const void* W, void* C, int c_dtype, int accumula
     const TW* w = static_cast<const TW*>(W);
     if (c_dtype == kF32) {
         float* c = static_cast<float*>(C);
-        if (accumulate) gemm_simt_kernel<TA, TW, float, true><<<grid, 256, 0, st>>>(a, w, c, M, N, K, lda, ldw, ldc);
-        else gemm_simt_kernel<TA, TW, float, false><<<grid, 256, 0, st>>>(a, w, c, M, N, K, lda, ldw, ldc);
+        if (accumulate) launch_kernel((gemm_simt_kernel<TA, TW, float, true>), dim3(grid), dim3(256), 0, st, a, w, c, M, N, K, lda, ldw, ldc);
+        else launch_kernel((gemm_simt_kernel<TA, TW, float, false>), dim3(grid), dim3(256), 0, st, a, w, c, M, N, K, lda, ldw, ldc);
     } else {
         __nv_bfloat16* c = static_cast<__nv_bfloat16*>(C);
-        if (accumulate) gemm_simt_kernel<TA, TW, __nv_bfloat16, true><<<grid, 256, 0, st>>>(a, w, c, M, N, K, lda, ldw, ldc);
-        else gemm_simt_kernel<TA, TW, __nv_bfloat16, false><<<grid, 256, 0, st>>>(a, w, c, M, N, K, lda, ldw, ldc);
+        if (accumulate) launch_kernel((gemm_simt_kernel<TA, TW, __nv_bfloat16, true>), dim3(grid), dim3(256), 0, st, a, w, c, M, N, K, lda, ldw, ldc);
+        else launch_kernel((gemm_simt_kernel<TA, TW, __nv_bfloat16, false>), dim3(grid), dim3(256), 0, st, a, w, c, M, N, K, lda, ldw, ldc);
     }
     return check_launch("gemm_simt");
 }

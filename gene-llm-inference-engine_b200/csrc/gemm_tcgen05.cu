@@ -130,6 +130,8 @@ struct TcParams {
     float* workspace;        // [tile][split][BLOCK_Q][128] partial tiles when splits > 1
     unsigned* counters;      // one per tile, zero between launches
     int* status;
+    int prefetch_p;          // P is a weight matrix no earlier kernel writes: its first tiles may be
+                             // fetched before the kernel waits for the kernels it depends on
 };
 
 template <int BLOCK_Q>
@@ -186,12 +188,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
         if (lane == 0) {
             int issued = 0;
-            for (int i = 0; i < n_kb; ++i) {
+            // The first stages are free: with prefetch_p their weight tiles are requested before
+            // this kernel waits for its predecessors, so the weight stream never pauses between
+            // the kernels of a decode step; the activation tiles follow after the wait.
+            const int early = p.prefetch_p ? min(n_kb, kStages) : 0;
+            for (int i = 0; i < early; ++i) {
+                const uint32_t full = smem_u32(&bars[i]);
+                mbar_expect_tx(full, Cfg::kStageBytes);
+                tma_load_2d(smem_u32(smem + i * Cfg::kStageBytes), &map_p, (kb_begin + i) * kBlockK, tile_p * kBlockP, full);
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (int i = 0; i < early; ++i) {
+                tma_load_2d(smem_u32(smem + i * Cfg::kStageBytes + Cfg::kStageBytesP), &map_q, (kb_begin + i) * kBlockK,
+                            tile_q * BLOCK_Q, smem_u32(&bars[i]));
+                issued = i + 1;
+            }
+            for (int i = early; i < n_kb; ++i) {
                 const int s = i % kStages;
                 const uint32_t parity = ((i / kStages) & 1) ^ 1;
                 if (!mbar_wait(smem_u32(&bars[kStages + s]), parity, abort_flag)) {
@@ -243,6 +261,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         }
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..5)
+        asm volatile("griddepcontrol.wait;" ::: "memory");      // C and the workspace belong to earlier kernels until now
         const int lane_group = warp & 3;                        // the TMEM lanes this warp may read
         const int row_in_tile = lane_group * 32 + lane;
         const int row_p = tile_p * kBlockP + row_in_tile;
@@ -637,7 +656,7 @@ static int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, const
     }
     const int tiles = p.tiles_p * p.tiles_q;
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    gemm_tc_persistent_kernel<BLOCK_Q, EPI><<<grid, kThreads, Cfg::kSmemBytes, st>>>(mp, mq, mc, p);
+    launch_kernel((gemm_tc_persistent_kernel<BLOCK_Q, EPI>), dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, mp, mq, mc, p);
     return check_launch("gemm_tc_persistent");
 }
 
@@ -650,7 +669,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
         if (e != cudaSuccess) { set_error("gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::kSmemBytes, cudaGetErrorString(e)); return 1; }
         configured = true;
     }
-    gemm_tc_kernel<BLOCK_Q><<<grid, kThreads, Cfg::kSmemBytes, st>>>(mp, mq, p);
+    launch_kernel((gemm_tc_kernel<BLOCK_Q>), dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, mp, mq, p);
     return check_launch("gemm_tc");
 }
 
@@ -694,6 +713,7 @@ extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
 
     CUtensorMap mp, mq;
+    p.prefetch_p = swap ? 1 : 0;
     if (swap) {
         p.rows_p = N; p.rows_q = M; p.stride_p = 1; p.stride_q = ldc;
         if (make_map(&mp, W, N, K, ldw, kBlockP) || make_map(&mq, A, M, K, lda, block_q)) return 1;

@@ -34,6 +34,7 @@ __device__ __forceinline__ double block_sum_double(double v, double* scratch) {
 
 __global__ void __launch_bounds__(kSampleThreads)
 argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+    pdl_prologue();
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     const float* row = logits + static_cast<size_t>(blockIdx.x) * V;
@@ -162,6 +163,7 @@ __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const float* __restrict__ logits, float* __restrict__ probs_all, int V,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ uniform, int* __restrict__ out) {
+    pdl_prologue();
     __shared__ double s_red[32];
     __shared__ double s_hist_w[257];
     __shared__ unsigned s_hist_c[256];
@@ -327,7 +329,7 @@ using namespace gi;
 extern "C" int gi_argmax(const float* logits, int rows, int V, int* out, void* stream) {
     if (rows == 0) return 0;
     GI_REQUIRE(rows > 0 && V > 0, "argmax: sizes must be positive (rows=%d, V=%d)", rows, V);
-    argmax_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(logits, V, out);
+    launch_kernel((argmax_kernel), dim3(rows), dim3(kSampleThreads), 0, static_cast<cudaStream_t>(stream), logits, V, out);
     return check_launch("argmax");
 }
 
@@ -336,7 +338,7 @@ extern "C" int gi_sample(const float* logits, float* probs_scratch, int rows, in
                          const int* top_k, const float* top_p, const float* uniform, int* out, void* stream) {
     if (rows == 0) return 0;
     GI_REQUIRE(rows > 0 && V > 0, "sample: sizes must be positive (rows=%d, V=%d)", rows, V);
-    sample_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+    launch_kernel((sample_kernel), dim3(rows), dim3(kSampleThreads), 0, static_cast<cudaStream_t>(stream), 
         logits, probs_scratch, V, temperature, top_k, top_p, uniform, out);
     return check_launch("sample");
 }
@@ -398,7 +400,7 @@ extern "C" int gi_sample_no_alloc(const float* logits, int rows, int vocab, cons
     float* work = nullptr;
     const int rc = work_area_for_current_device(&work);
     if (rc != 0) return rc;
-    sample_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+    launch_kernel((sample_kernel), dim3(rows), dim3(kSampleThreads), 0, static_cast<cudaStream_t>(stream), 
         logits, work, vocab, temperature, top_k, top_p, uniform, out);
     return check_launch("sample_no_alloc");
 }
