@@ -16,6 +16,7 @@
 // unwritten page contents (tests fill them with NaN) can never reach a result.
 // Head sizes 16, 32, 64 and 128 are built; other sizes use the general kernel.
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace gi {
 
@@ -69,6 +70,16 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk)
     return base + static_cast<uint32_t>((row * (HD / 8) + swizzled_chunk<HD>(row, chunk)) * 16);
 }
 
+// Tiles written by TMA: the same permutation for head sizes up to 64 (TMA's 128/64/32-byte
+// swizzles are exactly the ones above); a head size of 128 is stored as two half tiles of
+// [TILE][64], because a swizzled TMA box is at most 128 bytes wide.
+template <int HD, int TILE, bool TMA>
+__device__ __forceinline__ uint32_t kv_addr(uint32_t base, int row, int chunk) {
+    if (TMA && HD == 128)
+        return base + static_cast<uint32_t>((chunk >> 3) * (TILE * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+    return tile_addr<HD>(base, row, chunk);
+}
+
 // Loads keys [key0, key0 + n_rows) of one key/value head into a tile; rows outside [lo, hi] (the
 // union of what the tile's queries may read) are zero-filled and their pages are not touched.
 template <int HD>
@@ -89,15 +100,34 @@ __device__ __forceinline__ void load_tile_async(uint32_t tile, const __nv_bfloat
     }
 }
 
-// One warp: S = Q K^T for 16 query rows x 64 keys, online softmax update, O += P V.
+// Byte offsets of this lane's ldmatrix rows inside a tile, for every k-step of Q K^T and every
+// n-tile of P V. The swizzle depends only on the low bits of the row, which the 8- and 16-row
+// strides of the loops below leave alone, so the offsets are computed once per kernel.
+template <int HD, int TILE, bool TMA>
+struct LaneOffsets {
+    static constexpr uint32_t kRowStride = (TMA && HD == 128) ? 128 : HD * 2;
+    uint32_t k[HD / 16];
+    uint32_t v[HD / 8];
+    __device__ __forceinline__ void init(int lane) {
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) k[kk] = kv_addr<HD, TILE, TMA>(0, lane & 7, kk * 2 + ((lane >> 3) & 1));
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) v[n] = kv_addr<HD, TILE, TMA>(0, (lane & 7) + ((lane >> 3) & 1) * 8, n);
+    }
+};
+
+// One warp: S = Q K^T for 16 query rows x TILE keys, online softmax update, O += P V.
 // q_frag: A fragments of the 16 x HD query tile. Row limits (lo, pos) are those of the two rows
-// this lane holds (lane/4 and lane/4 + 8). o: HD/8 n-tiles x 4 accumulators. m, l: per row.
-template <int HD>
+// this lane holds (lane/4 and lane/4 + 8) and are applied only when kMasked (a tile at the edge
+// of some row's range). o: HD/8 n-tiles x 4 accumulators. m (in the scaled log2 domain), l: per row.
+template <int HD, int TILE, bool TMA, bool kMasked>
 __device__ __forceinline__ void warp_tile_step(const uint32_t (*q_frag)[4], uint32_t k_tile, uint32_t v_tile, int key0,
                                                const int* row_lo, const int* row_pos, float scale_log2,
-                                               float (*o)[4], float* m, float* l, int lane) {
+                                               float (*o)[4], float* m, float* l, int lane,
+                                               const LaneOffsets<HD, TILE, TMA>& off) {
     constexpr int kK = HD / 16;                 // k-steps of Q K^T
-    constexpr int kN = kTileKeys / 8;           // n-tiles of S
+    constexpr int kN = TILE / 8;                // n-tiles of S
+    constexpr uint32_t RS = LaneOffsets<HD, TILE, TMA>::kRowStride;
     float s[kN][4];
 #pragma unroll
     for (int j = 0; j < kN; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
@@ -107,31 +137,33 @@ __device__ __forceinline__ void warp_tile_step(const uint32_t (*q_frag)[4], uint
         for (int kk = 0; kk < kK; ++kk) {
             uint32_t b0, b1;
             // B fragment of K^T: keys j*8 + lane%8 (rows), head dims kk*16 + {0, 8} (two 8x8 matrices)
-            ldmatrix_x2(tile_addr<HD>(k_tile, j * 8 + (lane & 7), kk * 2 + ((lane >> 3) & 1)), b0, b1);
+            ldmatrix_x2(k_tile + j * 8 * RS + off.k[kk], b0, b1);
             mma_bf16(s[j], q_frag[kk], b0, b1);
         }
     }
-    // scale, mask, row maxima
+    // mask (edge tiles only) and row maxima of the raw scores
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int j = 0; j < kN; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
-            const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
-            const bool ok = key >= row_lo[r] && key <= row_pos[r];
-            s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
+            if (kMasked) {
+                const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+                if (!(key >= row_lo[r] && key <= row_pos[r])) s[j][e] = -INFINITY;
+            }
             mx[r] = fmaxf(mx[r], s[j][e]);
         }
     }
-    float corr[2];
+    float corr[2], m_use[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        const float m_new = fmaxf(m[r], mx[r]);
+        const float m_new = fmaxf(m[r], mx[r] * scale_log2);            // scale > 0: the maximum commutes with it
         corr[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - m_new);
         m[r] = m_new;
+        m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;                   // a row that has seen no key yet: all weights 0
     }
     float sum[2] = {0.f, 0.f};
 #pragma unroll
@@ -139,7 +171,7 @@ __device__ __forceinline__ void warp_tile_step(const uint32_t (*q_frag)[4], uint
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
-            const float p = (m[r] == -INFINITY) ? 0.f : exp2f(s[j][e] - m[r]);     // masked scores give 0
+            const float p = exp2f(fmaf(s[j][e], scale_log2, -m_use[r]));  // masked scores (-inf) give 0
             s[j][e] = p;
             sum[r] += p;
         }
@@ -156,7 +188,7 @@ __device__ __forceinline__ void warp_tile_step(const uint32_t (*q_frag)[4], uint
     }
     // O += P V: P as A fragments (16 keys per k-step), V^T through transposed ldmatrix
 #pragma unroll
-    for (int t = 0; t < kTileKeys / 16; ++t) {
+    for (int t = 0; t < TILE / 16; ++t) {
         uint32_t a[4];
         a[0] = pack_bf16(s[2 * t][0], s[2 * t][1]);
         a[1] = pack_bf16(s[2 * t][2], s[2 * t][3]);
@@ -166,7 +198,7 @@ __device__ __forceinline__ void warp_tile_step(const uint32_t (*q_frag)[4], uint
         for (int n = 0; n < HD / 8; ++n) {
             uint32_t b0, b1;
             // keys t*16 + {0..7, 8..15} (rows of V), head dims n*8..n*8+7, transposed on load
-            ldmatrix_x2_trans(tile_addr<HD>(v_tile, t * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, n), b0, b1);
+            ldmatrix_x2_trans(v_tile + t * 16 * RS + off.v[n], b0, b1);
             mma_bf16(o[n], a, b0, b1);
         }
     }
@@ -248,8 +280,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     int row_lo[2], row_pos[2];
     row_lo[0] = lo; row_pos[0] = (r0 < G) ? pos : -1;            // rows beyond the group see nothing
     row_lo[1] = lo; row_pos[1] = (r0 + 8 < G) ? pos : -1;
+    LaneOffsets<HD, kTileKeys, false> off;
+    off.init(lane);
     if (key0 <= pos && key0 + kTileKeys > lo)
-        warp_tile_step<HD>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane);
+        warp_tile_step<HD, kTileKeys, false, true>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
     __syncthreads();                                               // tiles are read; reuse the memory
 
     // merge the four warps in warp order through shared memory: [warp][16 rows][HD + 2]
@@ -287,6 +321,268 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             my_ml[static_cast<size_t>(row) * max_chunks * 2] = M;
             my_ml[static_cast<size_t>(row) * max_chunks * 2 + 1] = L;
         }
+    }
+}
+
+// ------------------------------------------------------------------------------------------ decode, fed by TMA
+// The same arithmetic as attention_decode_kernel per 256-key chunk, organised for bandwidth: one
+// persistent CTA per SM, whose four warps are independent. A warp takes whole chunks (work item =
+// request x key/value head x chunk, dealt round-robin), walks a chunk's tiles in order with the
+// online softmax, and writes the chunk's partial result itself, so no warp ever waits for another.
+// Each warp owns a ring of three stages (K tile + V tile) filled by TMA: one lane issues one box
+// per page and head (pages [pages, Hkv, page_size, hd] are rows of a 2D tensor map), running up to
+// three tiles ahead, across chunk borders. Pages wholly outside a query's range are not fetched.
+template <int HD>
+struct DecodeTma {
+    static constexpr int kTile = HD <= 64 ? 64 : 32;
+    static constexpr int kTilesPerChunk = kChunkKeys / kTile;
+    static constexpr int kBoxCols = HD < 64 ? HD : 64;
+    static constexpr int kHalves = HD / kBoxCols;                 // 2 for HD = 128
+    static constexpr int kTileBytes = kTile * HD * 2;
+    static constexpr int kStageBytes = 2 * kTileBytes;
+    static constexpr int kStages = 3;
+    static constexpr int kQBytes = 16 * HD * 2;
+    static constexpr int kMetaRows = 512;          // requests whose (row, position, request) are staged in shared memory
+    static constexpr int kSmemBytes = 4 * kStages * kStageBytes + 4 * kQBytes + 128 + 3 * kMetaRows * 4 + 1024;
+};
+
+__device__ __forceinline__ void att_mbar_init(uint32_t bar) { asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar)); }
+__device__ __forceinline__ void att_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool att_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool att_wait(uint32_t bar, uint32_t parity) {     // bounded: about two seconds
+    if (att_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = clock64();
+    while (!att_try_wait(bar, parity)) {
+        if (clock64() - t0 > 4000000000ull) return false;
+    }
+    return true;
+}
+__device__ __forceinline__ void att_tma_load(uint32_t dst, const void* map, int col, int row, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(col), "r"(row), "r"(bar) : "memory");
+}
+
+struct DecodeItem {
+    int idx, g, chunk, t, pos, req, lo, c0, tile0, tile1;
+    bool visible;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kAttThreads, 1)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const __nv_bfloat16* __restrict__ q, const int* __restrict__ rows, int n_rows,
+                            const int* __restrict__ row_req, const int* __restrict__ positions,
+                            const int* __restrict__ block_tables, int table_stride, int H, int Hkv, int page_size,
+                            float scale_log2, int window, float* __restrict__ part_o, float* __restrict__ part_ml,
+                            int max_chunks, int n_chunks, int* status) {
+    using Cfg = DecodeTma<HD>;
+    constexpr int kTile = Cfg::kTile, kStages = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t stages = smem_addr(smem) + warp * kStages * Cfg::kStageBytes;
+    uint8_t* q_ptr = smem + 4 * kStages * Cfg::kStageBytes + warp * Cfg::kQBytes;
+    const uint32_t q_tile = smem_addr(q_ptr);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 4 * kStages * Cfg::kStageBytes + 4 * Cfg::kQBytes) + warp * kStages;
+    int* meta = reinterpret_cast<int*>(smem + 4 * kStages * Cfg::kStageBytes + 4 * Cfg::kQBytes + 128);
+    const int G = H / Hkv;
+
+    if (lane == 0) {
+        for (int s = 0; s < kStages; ++s) att_mbar_init(smem_addr(&bars[s]));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    pdl_prologue();
+    // (step row, position, request) of every decoded token, once per CTA: the per-item look-ups
+    // below would otherwise be chains of dependent global loads on each warp's critical path
+    for (int i = threadIdx.x; i < n_rows && i < Cfg::kMetaRows; i += kAttThreads) {
+        const int t = rows[i];
+        meta[i] = t;
+        meta[Cfg::kMetaRows + i] = positions[t];
+        meta[2 * Cfg::kMetaRows + i] = row_req[t];
+    }
+    __syncthreads();
+
+    const int total = n_rows * Hkv * n_chunks;
+    const int stride = gridDim.x * 4;
+    const int box_rows = page_size < kTile ? page_size : kTile;
+    const int boxes = kTile / box_rows;
+
+    auto item_at = [&](int w, DecodeItem& it) {
+        it.chunk = w % n_chunks;
+        const int rest = w / n_chunks;
+        it.g = rest % Hkv;
+        it.idx = rest / Hkv;
+        if (it.idx < Cfg::kMetaRows) {
+            it.t = meta[it.idx]; it.pos = meta[Cfg::kMetaRows + it.idx]; it.req = meta[2 * Cfg::kMetaRows + it.idx];
+        } else {
+            it.t = rows[it.idx]; it.pos = positions[it.t]; it.req = row_req[it.t];
+        }
+        it.lo = (window > 0 && it.pos - window + 1 > 0) ? it.pos - window + 1 : 0;
+        it.c0 = it.chunk * kChunkKeys;
+        it.visible = it.c0 <= it.pos && it.c0 + kChunkKeys > it.lo;
+        it.tile0 = it.lo > it.c0 ? (it.lo - it.c0) / kTile : 0;
+        const int last = (it.pos - it.c0) / kTile;
+        it.tile1 = last < Cfg::kTilesPerChunk - 1 ? last : Cfg::kTilesPerChunk - 1;
+    };
+
+    // ---- producer cursor: the next tile to request
+    DecodeItem pi;
+    int pw = blockIdx.x * 4 + warp, ptile = 0, n_issued = 0;
+    int p_pages = 0;                           // lane i: the page of the chunk's i-th page-sized run of keys
+    const int pages_per_chunk = kChunkKeys / page_size > 0 ? kChunkKeys / page_size : 1;
+    auto p_seek = [&]() {
+        while (pw < total) {
+            item_at(pw, pi);
+            if (pi.visible) {
+                ptile = pi.tile0;
+                // the chunk's block-table entries, one per lane, requested now and used tiles later
+                const int first = pi.c0 / page_size;
+                const int key_of_lane = (first + lane) * page_size;
+                p_pages = (lane < pages_per_chunk && key_of_lane <= pi.pos && key_of_lane + page_size - 1 >= pi.lo)
+                              ? block_tables[static_cast<size_t>(pi.req) * table_stride + first + lane] : 0;
+                return;
+            }
+            pw += stride;
+        }
+    };
+    auto issue = [&]() {                       // requests tile (pi, ptile) into stage n_issued % kStages
+        const int s = n_issued % kStages;
+        const uint32_t k_tile = stages + s * Cfg::kStageBytes, v_tile = k_tile + Cfg::kTileBytes;
+        const int key0 = pi.c0 + ptile * kTile;
+        int my_box_page = 0;                   // lane b: the page of box b of this tile
+        {
+            const int kb = key0 + (lane < boxes ? lane : 0) * box_rows;
+            my_box_page = __shfl_sync(0xffffffffu, p_pages, ((kb - pi.c0) / page_size) & 31);
+        }
+        int box_pages[8];
+#pragma unroll
+        for (int b = 0; b < 8; ++b) box_pages[b] = __shfl_sync(0xffffffffu, my_box_page, b);
+        if (lane == 0) {
+            int n_boxes = 0;
+            for (int b = 0; b < boxes; ++b) {
+                const int kb = key0 + b * box_rows;
+                if (kb <= pi.pos && kb + box_rows - 1 >= pi.lo) ++n_boxes;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the stage was read and maybe zeroed by ordinary accesses
+            const uint32_t bar = smem_addr(&bars[s]);
+            att_expect_tx(bar, static_cast<uint32_t>(n_boxes) * 2u * box_rows * HD * 2u);
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                const int kb = key0 + b * box_rows;
+                if (b < boxes && kb <= pi.pos && kb + box_rows - 1 >= pi.lo) {
+                    const int row = (box_pages[b] * Hkv + pi.g) * page_size + kb % page_size;
+#pragma unroll
+                    for (int h = 0; h < Cfg::kHalves; ++h) {
+                        const uint32_t off = static_cast<uint32_t>(h * (kTile * 128) + b * box_rows * (Cfg::kBoxCols * 2));
+                        att_tma_load(k_tile + off, &map_k, h * 64, row, bar);
+                        att_tma_load(v_tile + off, &map_v, h * 64, row, bar);
+                    }
+                }
+            }
+        }
+        ++n_issued;
+        if (++ptile > pi.tile1) { pw += stride; p_seek(); }
+    };
+
+    p_seek();
+    while (pw < total && n_issued < kStages) issue();
+
+    // ---- consumer
+    DecodeItem ci;
+    int n_done = 0;
+    uint32_t q_frag[HD / 16][4];
+    float o[HD / 8][4];
+    float m[2], l[2];
+    int row_lo[2], row_pos[2];
+    const int r0 = lane >> 2;
+    bool failed = false;
+    LaneOffsets<HD, kTile, true> off;
+    off.init(lane);
+    for (int cw = blockIdx.x * 4 + warp; cw < total && !failed; cw += stride) {
+        item_at(cw, ci);
+        float* my_o = part_o + ((static_cast<size_t>(ci.idx) * H + ci.g * G) * max_chunks + ci.chunk) * HD;
+        float* my_ml = part_ml + ((static_cast<size_t>(ci.idx) * H + ci.g * G) * max_chunks + ci.chunk) * 2;
+        if (!ci.visible) {
+            if (lane < G) {
+                my_ml[static_cast<size_t>(lane) * max_chunks * 2] = -INFINITY;
+                my_ml[static_cast<size_t>(lane) * max_chunks * 2 + 1] = 0.f;
+            }
+            continue;
+        }
+        {   // the query tile of this item: rows 0..G-1 are the heads of the group, the rest zero
+            constexpr int cpr = HD / 8;
+            const uint4* src = reinterpret_cast<const uint4*>(q + (static_cast<size_t>(ci.t) * H + ci.g * G) * HD);
+            __syncwarp();
+            for (int i = lane; i < 16 * cpr; i += 32) {
+                const int row = i / cpr, c = i % cpr;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (row < G) v = src[row * cpr + c];
+                *reinterpret_cast<uint4*>(q_ptr + (row * cpr + swizzled_chunk<HD>(row, c)) * 16) = v;
+            }
+            __syncwarp();
+            load_q_frags<HD>(q_tile, 0, q_frag, lane);
+        }
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+        m[0] = m[1] = -INFINITY;
+        l[0] = l[1] = 0.f;
+        row_lo[0] = row_lo[1] = ci.lo;
+        row_pos[0] = (r0 < G) ? ci.pos : -1;
+        row_pos[1] = (r0 + 8 < G) ? ci.pos : -1;
+        for (int tile = ci.tile0; tile <= ci.tile1; ++tile, ++n_done) {
+            const int s = n_done % kStages;
+            if (!att_wait(smem_addr(&bars[s]), (n_done / kStages) & 1)) {
+                if (lane == 0) atomicCAS(status, 0, 5);
+                failed = true;
+                break;
+            }
+            const uint32_t k_tile = stages + s * Cfg::kStageBytes, v_tile = k_tile + Cfg::kTileBytes;
+            const int key0 = ci.c0 + tile * kTile;
+            if (key0 < ci.lo || key0 + kTile - 1 > ci.pos) {
+                // an edge tile: value rows outside the range were not fetched or hold unwritten
+                // positions; they are multiplied by weights of exactly 0, so they must be finite
+                constexpr int cpr = HD / 8;
+                for (int i = lane; i < kTile * cpr; i += 32) {
+                    const int row = i / cpr, c = i % cpr;
+                    const int key = key0 + row;
+                    if (key < ci.lo || key > ci.pos)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(kv_addr<HD, kTile, true>(v_tile, row, c)), "r"(0) : "memory");
+                }
+                __syncwarp();
+                warp_tile_step<HD, kTile, true, true>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
+            } else {
+                warp_tile_step<HD, kTile, true, false>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
+            }
+            __syncwarp();                                   // every lane is done reading the stage
+            if (pw < total) issue();
+        }
+        if (failed) break;
+        // the chunk's partial result: unnormalised output, running maximum (log2 domain) and sum
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = r0 + 8 * r;
+            if (row >= G) continue;
+            float* dst = my_o + static_cast<size_t>(row) * max_chunks * HD + (lane & 3) * 2;
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n)
+                *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][2 * r], o[n][2 * r + 1]);
+            if ((lane & 3) == 0) {
+                my_ml[static_cast<size_t>(row) * max_chunks * 2] = m[r];
+                my_ml[static_cast<size_t>(row) * max_chunks * 2 + 1] = l[r];
+            }
+        }
+    }
+    if (failed) {
+        // wait (bounded) for the copies this warp still has in flight before its memory is released
+        for (int i = n_done; i < n_issued; ++i) att_wait(smem_addr(&bars[i % kStages]), (i / kStages) & 1);
     }
 }
 
@@ -387,14 +683,23 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     const int warp_pos_max = (warp_row_first < n_rows) ? pos_first + warp_row_last / G : -1;
     const int warp_pos_min = pos_first + warp_row_first / G;
     const int warp_lo_min = (window > 0 && warp_pos_min - window + 1 > 0) ? warp_pos_min - window + 1 : 0;
+    const int warp_lo_max = (window > 0 && warp_pos_max - window + 1 > 0) ? warp_pos_max - window + 1 : 0;
+    LaneOffsets<HD, kTileKeys, false> off;
+    off.init(lane);
 
     for (int i = 0; i < n_tiles; ++i) {
         if (i + 1 < n_tiles) { issue(i + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         __syncthreads();
         const uint32_t kt = kv_base + (i & 1) * 2 * kTileBytes;
         const int key0 = (first_tile + i) * kTileKeys;
-        if (key0 <= warp_pos_max && key0 + kTileKeys > warp_lo_min)
-            warp_tile_step<HD>(q_frag, kt, kt + kTileBytes, key0, row_lo, row_pos, scale_log2, o, m, l, lane);
+        if (key0 <= warp_pos_max && key0 + kTileKeys > warp_lo_min) {
+            // no mask where every key of the tile is visible to every row of the warp (rows beyond
+            // the tile's tokens have zero queries and are never stored)
+            if (key0 >= warp_lo_max && key0 + kTileKeys - 1 <= warp_pos_min)
+                warp_tile_step<HD, kTileKeys, false, false>(q_frag, kt, kt + kTileBytes, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
+            else
+                warp_tile_step<HD, kTileKeys, false, true>(q_frag, kt, kt + kTileBytes, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
+        }
         __syncthreads();                                // the stage may be overwritten by the next issue
     }
 
@@ -438,6 +743,41 @@ static int launch_decode(const void* q, const void* kc, const void* vc, void* ou
 }
 
 template <int HD>
+static int launch_decode_tma(const void* q, const void* kc, const void* vc, void* out, const int* rows, int n_rows,
+                             const int* row_req, const int* positions, const int* tables, int table_stride, int H, int Hkv,
+                             int page_size, float scale, int window, float* part_o, float* part_ml, int max_chunks,
+                             int n_chunks, long long n_pages, int* status, cudaStream_t st) {
+    using Cfg = DecodeTma<HD>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) { set_error("attention_decode: %s", cudaGetErrorString(e)); return 1; }
+        configured = true;
+    }
+    const int box_rows = page_size < Cfg::kTile ? page_size : Cfg::kTile;
+    CUtensorMap mk, mv;
+    const unsigned long long rows_total = static_cast<unsigned long long>(n_pages) * Hkv * page_size;
+    if (make_tensor_map_2d(&mk, kc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_total, HD, HD, box_rows, Cfg::kBoxCols,
+                           CU_TENSOR_MAP_L2_PROMOTION_NONE, "attention_decode")) return 1;
+    if (make_tensor_map_2d(&mv, vc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_total, HD, HD, box_rows, Cfg::kBoxCols,
+                           CU_TENSOR_MAP_L2_PROMOTION_NONE, "attention_decode")) return 1;
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int items = n_rows * Hkv * n_chunks;
+    int grid = (items + 3) / 4;
+    if (grid > sms) grid = sms;
+    launch_kernel((attention_decode_tma_kernel<HD>), dim3(grid), dim3(kAttThreads), Cfg::kSmemBytes, st, mk, mv,
+                  static_cast<const __nv_bfloat16*>(q), rows, n_rows, row_req, positions, tables, table_stride, H, Hkv,
+                  page_size, scale * kLog2e, window, part_o, part_ml, max_chunks, n_chunks, status);
+    if (check_launch("attention_decode_tma")) return 1;
+    dim3 grid2(H, n_rows);
+    launch_kernel((attention_combine_kernel), dim3(grid2), dim3(HD < 32 ? 32 : HD), 0, st, part_o, part_ml, rows, positions,
+                  static_cast<__nv_bfloat16*>(out), H, HD, max_chunks, window);
+    return check_launch("attention_combine");
+}
+
+template <int HD>
 static int launch_prefill(const void* q, const void* kc, const void* vc, void* out, const int* work, int n_work,
                           const int* positions, const int* tables, int table_stride, int H, int Hkv, int page_size,
                           float scale, int window, cudaStream_t st) {
@@ -471,12 +811,29 @@ extern "C" int gi_attention_chunk_keys() { return kChunkKeys; }
 extern "C" int gi_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* rows,
                                    int n_rows, const int* row_req, const int* positions, const int* block_tables,
                                    int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window,
-                                   float* part_o, float* part_ml, int max_chunks, int n_chunks, void* stream) {
+                                   float* part_o, float* part_ml, int max_chunks, int n_chunks, long long n_pages,
+                                   void* status, void* stream) {
     if (n_rows == 0) return 0;
     GI_REQUIRE(gi_attention_fast_supported(hd, H, Hkv), "attention_decode: head size %d with %d/%d heads is not built", hd, H, Hkv);
     GI_REQUIRE(n_chunks >= 1 && n_chunks <= max_chunks, "attention_decode: %d chunks exceed the workspace's %d", n_chunks, max_chunks);
     GI_REQUIRE(n_rows <= 65535 && Hkv <= 65535, "attention_decode: grid too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // Pages that TMA boxes can tile (8, 16, 32 ... rows that divide or are divided by the tile) take
+    // the TMA-fed kernel; any other page size takes the cp.async kernel.
+    const int tile = hd <= 64 ? 64 : 32;
+    const bool tma_ok = page_size % 8 == 0 && (tile % page_size == 0 || page_size % tile == 0) && status != nullptr &&
+                        reinterpret_cast<uintptr_t>(k_cache) % 16 == 0 && reinterpret_cast<uintptr_t>(v_cache) % 16 == 0;
+    if (tma_ok) {
+#define GI_DECODE_TMA(HD) return launch_decode_tma<HD>(q, k_cache, v_cache, out, rows, n_rows, row_req, positions, block_tables, \
+        table_stride, H, Hkv, page_size, scale, window, part_o, part_ml, max_chunks, n_chunks, n_pages, static_cast<int*>(status), st)
+        switch (hd) {
+            case 16: GI_DECODE_TMA(16);
+            case 32: GI_DECODE_TMA(32);
+            case 64: GI_DECODE_TMA(64);
+            default: GI_DECODE_TMA(128);
+        }
+#undef GI_DECODE_TMA
+    }
 #define GI_DECODE(HD) return launch_decode<HD>(q, k_cache, v_cache, out, rows, n_rows, row_req, positions, block_tables, \
                                                table_stride, H, Hkv, page_size, scale, window, part_o, part_ml, max_chunks, n_chunks, st)
     switch (hd) {

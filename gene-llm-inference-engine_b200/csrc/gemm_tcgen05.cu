@@ -19,8 +19,7 @@
 // status word, stops issuing work, drains its own copies with bounded waits, frees its tensor
 // memory and returns; the host reads the status word with gi_gemm_tc_status().
 #include "common.cuh"
-
-#include <cuda.h>
+#include "tma.cuh"
 
 namespace gi {
 
@@ -583,27 +582,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
 }
 
 // ------------------------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult status;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) == cudaSuccess &&
-            status == cudaDriverEntryPointSuccess) {
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-        }
-    }
-    return fn;
-}
-
 // A [rows, K] row-major bf16 matrix viewed as boxes of [box_rows, 64] with 128-byte swizzle; reads
 // beyond rows or K give zeros.
 static int make_map(CUtensorMap* map, const void* base, int rows, int K, long long ld, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
+    EncodeTiledFn fn = tensor_map_encoder();
     if (!fn) { set_error("gemm_tc: cuTensorMapEncodeTiled is not available from the driver"); return 1; }
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
@@ -619,7 +601,7 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, long lo
 // The output matrix [rows, cols] (row stride ld elements) as boxes of 128 rows x 128 bytes with the
 // 128-byte swizzle the epilogue writes its staging in; stores beyond rows or cols are clipped.
 static int make_out_map(CUtensorMap* map, void* base, int rows, int cols, long long ld, bool bf16) {
-    EncodeTiledFn fn = encode_fn();
+    EncodeTiledFn fn = tensor_map_encoder();
     if (!fn) { set_error("gemm_tc: cuTensorMapEncodeTiled is not available from the driver"); return 1; }
     const int elt = bf16 ? 2 : 4;
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};

@@ -177,7 +177,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         _dev(positions, "positions", torch.int32), _dev(block_tables, "block_tables", torch.int32),
         block_tables.shape[1], num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
         _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), max_chunks, n_chunks,
-        _stream()), "attention_decode")
+        k_cache.shape[0], _tc_state(q.device).status.data_ptr(), _stream()), "attention_decode")
     global _launches
     _launches += 1            # the combine kernel
 

@@ -35,7 +35,8 @@ _SIGNATURES = {
                               c_int, c_void_p, c_void_p],
     "gi_gemm_tc_status": [c_void_p, c_void_p, c_void_p],
     "gi_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                            c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+                            c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_longlong,
+                            c_void_p, c_void_p],
     "gi_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                              c_int, c_int, c_int, c_float, c_int, c_void_p],
     "gi_attention_fast_supported": [c_int, c_int, c_int],
