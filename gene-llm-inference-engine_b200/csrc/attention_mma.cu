@@ -717,6 +717,187 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     }
 }
 
+// ------------------------------------------------------------------------------------------ prefill, fed by TMA
+// 128 query rows per CTA (eight warps of 16 rows: tokens x heads of one key/value group), keys in
+// tiles of 64 through a three-stage ring that a ninth warp fills by TMA, one box per page. A warp
+// skips the tiles beyond its own rows' positions and masks only the tiles at the edge of some
+// row's range.
+template <int HD>
+struct PrefillTma {
+    static constexpr int kRows = 128;
+    static constexpr int kWarps = 8;
+    static constexpr int kThreads = (kWarps + 1) * 32;
+    static constexpr int kTile = 64;
+    static constexpr int kBoxCols = HD < 64 ? HD : 64;
+    static constexpr int kHalves = HD / kBoxCols;
+    static constexpr int kTileBytes = kTile * HD * 2;
+    static constexpr int kStageBytes = 2 * kTileBytes;
+    static constexpr int kStages = 3;
+    static constexpr int kQBytes = kRows * HD * 2;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kQBytes + 128 + 1024;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(PrefillTma<HD>::kThreads, (HD <= 64 ? 2 : 1))
+attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                             const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                             const int* __restrict__ work, const int* __restrict__ positions,
+                             const int* __restrict__ block_tables, int table_stride, int H, int Hkv, int page_size,
+                             float scale_log2, int window, int* status) {
+    using Cfg = PrefillTma<HD>;
+    constexpr int kTile = Cfg::kTile, kStages = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const uint32_t stages = smem_addr(smem);
+    uint8_t* q_ptr = smem + kStages * Cfg::kStageBytes;
+    const uint32_t q_tile = smem_addr(q_ptr);
+    uint64_t* full = reinterpret_cast<uint64_t*>(q_ptr + Cfg::kQBytes);
+    uint64_t* empty = full + kStages;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = H / Hkv;
+    const int g = blockIdx.y;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            att_mbar_init(smem_addr(&full[s]));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&empty[s])), "r"(Cfg::kWarps));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_prologue();
+
+    const int t0 = work[blockIdx.x * 3], n_tok = work[blockIdx.x * 3 + 1], req = work[blockIdx.x * 3 + 2];
+    const int n_rows = n_tok * G;
+    const int* table = block_tables + static_cast<size_t>(req) * table_stride;
+    const int pos_first = positions[t0], pos_last = pos_first + n_tok - 1;
+    const int lo_first = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+    const int first_tile = lo_first / kTile, last_tile = pos_last / kTile;
+    const int n_tiles = last_tile - first_tile + 1;
+    const int box_rows = page_size < kTile ? page_size : kTile;
+    const int boxes = kTile / box_rows;
+
+    if (warp == Cfg::kWarps) {
+        // ---------------------------------------------------------------- producer warp
+        if (lane == 0) {
+            for (int i = 0; i < n_tiles; ++i) {
+                const int s = i % kStages;
+                if (i >= kStages && !att_wait(smem_addr(&empty[s]), ((i / kStages) - 1) & 1)) {
+                    atomicCAS(status, 0, 6);
+                    break;
+                }
+                const int key0 = (first_tile + i) * kTile;
+                const uint32_t k_tile = stages + s * Cfg::kStageBytes, v_tile = k_tile + Cfg::kTileBytes;
+                int n_boxes = 0;
+                for (int b = 0; b < boxes; ++b) {
+                    const int kb = key0 + b * box_rows;
+                    if (kb <= pos_last && kb + box_rows - 1 >= lo_first) ++n_boxes;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                const uint32_t bar = smem_addr(&full[s]);
+                att_expect_tx(bar, static_cast<uint32_t>(n_boxes) * 2u * box_rows * HD * 2u);
+                for (int b = 0; b < boxes; ++b) {
+                    const int kb = key0 + b * box_rows;
+                    if (!(kb <= pos_last && kb + box_rows - 1 >= lo_first)) continue;
+                    const int page = table[kb / page_size];
+                    const int row = (page * Hkv + g) * page_size + kb % page_size;
+#pragma unroll
+                    for (int h = 0; h < Cfg::kHalves; ++h) {
+                        const uint32_t off = static_cast<uint32_t>(h * (kTile * 128) + b * box_rows * (Cfg::kBoxCols * 2));
+                        att_tma_load(k_tile + off, &map_k, h * 64, row, bar);
+                        att_tma_load(v_tile + off, &map_v, h * 64, row, bar);
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumer warps
+    // this warp's 16 query rows: row r <- q[t0 + r / G][g * G + r % G]
+    {
+        constexpr int cpr = HD / 8;
+        for (int i = lane; i < 16 * cpr; i += 32) {
+            const int row = warp * 16 + i / cpr, c = i % cpr;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row < n_rows) {
+                const int tok = row / G, hh = row % G;
+                v = *reinterpret_cast<const uint4*>(q + (static_cast<size_t>(t0 + tok) * H + g * G + hh) * HD + c * 8);
+            }
+            *reinterpret_cast<uint4*>(q_ptr + (row * cpr + swizzled_chunk<HD>(row, c)) * 16) = v;
+        }
+        __syncwarp();
+    }
+    uint32_t q_frag[HD / 16][4];
+    load_q_frags<HD>(q_tile, warp * 16, q_frag, lane);
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    int row_lo[2], row_pos[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + (lane >> 2) + r * 8;
+        if (row < n_rows) {
+            row_pos[r] = pos_first + row / G;
+            row_lo[r] = (window > 0 && row_pos[r] - window + 1 > 0) ? row_pos[r] - window + 1 : 0;
+        } else {
+            row_pos[r] = -1; row_lo[r] = 0;
+        }
+    }
+    const int warp_row_first = warp * 16, warp_row_last = min(n_rows - 1, warp * 16 + 15);
+    const bool warp_has_rows = warp_row_first < n_rows;
+    const int warp_pos_max = warp_has_rows ? pos_first + warp_row_last / G : -1;
+    const int warp_pos_min = pos_first + warp_row_first / G;
+    const int warp_lo_min = (window > 0 && warp_pos_min - window + 1 > 0) ? warp_pos_min - window + 1 : 0;
+    const int warp_lo_max = (window > 0 && warp_pos_max - window + 1 > 0) ? warp_pos_max - window + 1 : 0;
+    LaneOffsets<HD, kTile, true> off;
+    off.init(lane);
+
+    for (int i = 0; i < n_tiles; ++i) {
+        const int s = i % kStages;
+        if (!att_wait(smem_addr(&full[s]), (i / kStages) & 1)) {
+            if (lane == 0) atomicCAS(status, 0, 7);
+            break;
+        }
+        const uint32_t k_tile = stages + s * Cfg::kStageBytes, v_tile = k_tile + Cfg::kTileBytes;
+        const int key0 = (first_tile + i) * kTile;
+        if (key0 <= warp_pos_max && key0 + kTile > warp_lo_min) {
+            if (key0 >= warp_lo_max && key0 + kTile - 1 <= warp_pos_min) {
+                warp_tile_step<HD, kTile, true, false>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
+            } else {
+                if (key0 < lo_first || key0 + kTile - 1 > pos_last) {
+                    // value rows outside every query's range were not fetched or were never written:
+                    // each warp zeroes them for itself (all warps store the same zeros)
+                    constexpr int cpr = HD / 8;
+                    for (int j = lane; j < kTile * cpr; j += 32) {
+                        const int row = j / cpr, c = j % cpr;
+                        const int key = key0 + row;
+                        if (key < lo_first || key > pos_last)
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(kv_addr<HD, kTile, true>(v_tile, row, c)), "r"(0) : "memory");
+                    }
+                    __syncwarp();
+                }
+                warp_tile_step<HD, kTile, true, true>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(&empty[s])) : "memory");
+    }
+
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + (lane >> 2) + r * 8;
+        if (row >= n_rows) continue;
+        const int tok = row / G, hh = row % G;
+        const float inv = 1.0f / l[r];
+        __nv_bfloat16* dst = out + (static_cast<size_t>(t0 + tok) * H + g * G + hh) * HD + (lane & 3) * 2;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n)
+            *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) = __floats2bfloat162_rn(o[n][2 * r] * inv, o[n][2 * r + 1] * inv);
+    }
+}
+
 template <int HD>
 static int launch_decode(const void* q, const void* kc, const void* vc, void* out, const int* rows, int n_rows,
                          const int* row_req, const int* positions, const int* tables, int table_stride, int H, int Hkv,
@@ -795,9 +976,42 @@ static int launch_prefill(const void* q, const void* kc, const void* vc, void* o
     return check_launch("attention_prefill");
 }
 
+template <int HD>
+static int launch_prefill_tma(const void* q, const void* kc, const void* vc, void* out, const int* work, int n_work,
+                              const int* positions, const int* tables, int table_stride, int H, int Hkv, int page_size,
+                              float scale, int window, long long n_pages, int* status, cudaStream_t st) {
+    using Cfg = PrefillTma<HD>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) { set_error("attention_prefill: %s", cudaGetErrorString(e)); return 1; }
+        configured = true;
+    }
+    const int box_rows = page_size < Cfg::kTile ? page_size : Cfg::kTile;
+    CUtensorMap mk, mv;
+    const unsigned long long rows_total = static_cast<unsigned long long>(n_pages) * Hkv * page_size;
+    if (make_tensor_map_2d(&mk, kc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_total, HD, HD, box_rows, Cfg::kBoxCols,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "attention_prefill")) return 1;
+    if (make_tensor_map_2d(&mv, vc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_total, HD, HD, box_rows, Cfg::kBoxCols,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "attention_prefill")) return 1;
+    dim3 grid(n_work, Hkv);
+    launch_kernel((attention_prefill_tma_kernel<HD>), dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, mk, mv,
+                  static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), work, positions, tables,
+                  table_stride, H, Hkv, page_size, scale * kLog2e, window, status);
+    return check_launch("attention_prefill_tma");
+}
+
 }  // namespace gi
 
 using namespace gi;
+
+// Query rows per work item of the prefill kernels for this page size and head size: 128 where the
+// pages can be fetched by TMA boxes, 64 otherwise. A work item holds rows / group-size tokens.
+extern "C" int gi_attention_prefill_rows(int page_size, int hd) {
+    const int tile = 64;
+    (void)hd;
+    return (page_size % 8 == 0 && (tile % page_size == 0 || page_size % tile == 0)) ? 128 : 64;
+}
 
 extern "C" int gi_attention_fast_supported(int head_dim, int H, int Hkv) {
     return (head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128) && Hkv > 0 && H % Hkv == 0 && H / Hkv <= 16;
@@ -848,11 +1062,23 @@ extern "C" int gi_attention_decode(const void* q, const void* k_cache, const voi
 // Prompt portions: work[3*i..] = (first step row of the tile, tokens in the tile, request index).
 extern "C" int gi_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work,
                                     int n_work, const int* positions, const int* block_tables, int table_stride, int H,
-                                    int Hkv, int hd, int page_size, float scale, int window, void* stream) {
+                                    int Hkv, int hd, int page_size, float scale, int window, long long n_pages,
+                                    void* status, void* stream) {
     if (n_work == 0) return 0;
     GI_REQUIRE(gi_attention_fast_supported(hd, H, Hkv), "attention_prefill: head size %d with %d/%d heads is not built", hd, H, Hkv);
     GI_REQUIRE(Hkv <= 65535, "attention_prefill: grid too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (gi_attention_prefill_rows(page_size, hd) == 128 && status != nullptr) {
+#define GI_PREFILL_TMA(HD) return launch_prefill_tma<HD>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, \
+        table_stride, H, Hkv, page_size, scale, window, n_pages, static_cast<int*>(status), st)
+        switch (hd) {
+            case 16: GI_PREFILL_TMA(16);
+            case 32: GI_PREFILL_TMA(32);
+            case 64: GI_PREFILL_TMA(64);
+            default: GI_PREFILL_TMA(128);
+        }
+#undef GI_PREFILL_TMA
+    }
 #define GI_PREFILL(HD) return launch_prefill<HD>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, \
                                                  H, Hkv, page_size, scale, window, st)
     switch (hd) {

@@ -152,6 +152,11 @@ def attention_fast_supported(head_dim: int, num_heads: int, num_kv_heads: int) -
     return bool(lib().gi_attention_fast_supported(head_dim, num_heads, num_kv_heads))
 
 
+def attention_prefill_rows(page_size: int, head_dim: int) -> int:
+    """Query rows (tokens x heads of one key/value group) per work item of the prefill kernel."""
+    return int(lib().gi_attention_prefill_rows(page_size, head_dim))
+
+
 def attention_chunk_keys() -> int:
     """Positions per chunk of the decode kernel's split over the context (a fixed length)."""
     return int(lib().gi_attention_chunk_keys())
@@ -186,7 +191,7 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                       work: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor, num_heads: int,
                       num_kv_heads: int, head_dim: int, page_size: int, scale: float, window: Optional[int]) -> None:
     """Attention of prompt portions (bfloat16): ``work`` [n, 3] = (first step row of a tile, tokens
-    in it (at most 64 // group size), request index)."""
+    in it (at most attention_prefill_rows() // group size), request index)."""
     if work.dim() != 2 or work.shape[1] != 3:
         raise KernelError("attention_prefill: work must be [n, 3]")
     if k_cache.shape[1:] != (num_kv_heads, page_size, head_dim) or v_cache.shape != k_cache.shape:
@@ -198,7 +203,7 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         _dev(out, "out", torch.bfloat16), _dev(work, "work", torch.int32), work.shape[0],
         _dev(positions, "positions", torch.int32), _dev(block_tables, "block_tables", torch.int32),
         block_tables.shape[1], num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
-        _stream()), "attention_prefill")
+        k_cache.shape[0], _tc_state(q.device).status.data_ptr(), _stream()), "attention_prefill")
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

@@ -46,9 +46,15 @@ class AttentionMixer:
         # bfloat16 with a head size the tensor-core kernels are built for; else the general kernel
         self.fast = self.dtype is torch.bfloat16 and kernels.attention_fast_supported(
             self.head_dim, self.num_heads, self.num_kv_heads)
+        self._prefill_rows = {}
         if self.fast:
             self.chunk_keys = kernels.attention_chunk_keys()
             self.max_chunks = (build.max_position + self.chunk_keys - 1) // self.chunk_keys
+
+    def prefill_rows(self, page_size: int) -> int:
+        if page_size not in self._prefill_rows:
+            self._prefill_rows[page_size] = kernels.attention_prefill_rows(page_size, self.head_dim)
+        return self._prefill_rows[page_size]
 
     def cache_need(self):
         return CacheNeed(self.num_kv_heads, self.head_dim, self.window)
@@ -73,7 +79,7 @@ class AttentionMixer:
         if self.fast:
             # tensor-core kernels: single decoded tokens split their context over many CTAs,
             # portions of prompts run tile by tile
-            rows, work, longest = ctx.attention_work(64 // (H // Hkv))
+            rows, work, longest = ctx.attention_work(self.prefill_rows(ctx.page_size) // (H // Hkv))
             if rows.numel():
                 n = rows.numel()
                 part_o = ctx.scratch("att_part_o", (n, H * self.max_chunks * hd), torch.float32, capacity=ctx.max_requests)

@@ -155,7 +155,7 @@ def _run_fast_attention(q_all, kc, vc, out, row_req, positions, tables, q_lens, 
     """The tensor-core kernels: single tokens through the decode kernel, portions through prefill."""
     kern = K()
     G = H // Hkv
-    per_tile = 64 // G
+    per_tile = kern.attention_prefill_rows(ps, hd) // G
     decode_rows, work, row = [], [], 0
     for r, n in enumerate(q_lens):
         if n == 1:

@@ -82,6 +82,7 @@ class _Ctx:
         single = [s for s, n in zip(self._starts, self._lens) if n == 1]
         tiles = [(s + t, min(per_tile, n - t), r) for r, (s, n) in enumerate(zip(self._starts, self._lens)) if n > 1
                  for t in range(0, n, per_tile)]
+        assert per_tile in (128 // 3, 64 // 3)
         return (torch.tensor(single, dtype=torch.int32, device=DEV),
                 torch.tensor(tiles, dtype=torch.int32, device=DEV).reshape(len(tiles), 3), 1)
 
