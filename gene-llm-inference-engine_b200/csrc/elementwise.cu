@@ -39,29 +39,86 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
 // ---------------------------------------------------------------------------------- RMSNorm
 // One block per output row. Each thread sums a fixed strided subset with fmaf, lanes are combined
 // by a fixed xor tree and warps in index order, so a row's result never depends on the batch.
+// Rows whose length is a multiple of 4 are read once, 16 bytes at a time, and kept in registers
+// between the sum and the scaling (up to 16 values per thread; longer rows are read twice).
 template <typename TOut>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
-                               const float* __restrict__ weight, TOut* __restrict__ out, int D, float eps) {
+__device__ __forceinline__ void store4(TOut* dst, float a, float b, float c, float d);
+template <>
+__device__ __forceinline__ void store4<float>(float* dst, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = v;
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+               const float* __restrict__ weight, TOut* __restrict__ out, int D, float eps) {
     pdl_prologue();
     __shared__ float warp_part[32];
     __shared__ float s_scale;
     const int r = blockIdx.x;
     const float* xr = x + static_cast<size_t>(rows ? rows[r] : r) * D;
+    TOut* o = out + static_cast<size_t>(r) * D;
+    constexpr int kKeep = 4;                                    // float4 values a thread keeps
+    const bool vec = (D % 4 == 0) && (reinterpret_cast<uintptr_t>(xr) % 16 == 0) &&
+                     (reinterpret_cast<uintptr_t>(o) % 16 == 0) && (reinterpret_cast<uintptr_t>(weight) % 16 == 0);
+    float4 kept[kKeep];
     float ss = 0.f;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) ss = fmaf(xr[d], xr[d], ss);
+    if (vec) {
+        const float4* x4 = reinterpret_cast<const float4*>(xr);
+        const int n4 = D / 4;
+        int i = threadIdx.x;
+#pragma unroll
+        for (int k = 0; k < kKeep; ++k, i += 256) {
+            kept[k] = (i < n4) ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            ss = fmaf(kept[k].x, kept[k].x, ss); ss = fmaf(kept[k].y, kept[k].y, ss);
+            ss = fmaf(kept[k].z, kept[k].z, ss); ss = fmaf(kept[k].w, kept[k].w, ss);
+        }
+        for (; i < n4; i += 256) {
+            const float4 v = x4[i];
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+    } else {
+        for (int d = threadIdx.x; d < D; d += 256) ss = fmaf(xr[d], xr[d], ss);
+    }
     ss = warp_sum(ss);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) warp_part[warp] = ss;
     __syncthreads();
     if (threadIdx.x == 0) {
         float total = 0.f;
-        for (int w = 0; w < nwarp; ++w) total += warp_part[w];
+        for (int w = 0; w < 8; ++w) total += warp_part[w];
         s_scale = 1.0f / sqrtf(total / static_cast<float>(D) + eps);
     }
     __syncthreads();
     const float scale = s_scale;
-    TOut* o = out + static_cast<size_t>(r) * D;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) o[d] = from_float<TOut>(weight[d] * (scale * xr[d]));
+    if (vec) {
+        const float4* x4 = reinterpret_cast<const float4*>(xr);
+        const float4* w4 = reinterpret_cast<const float4*>(weight);
+        const int n4 = D / 4;
+        int i = threadIdx.x;
+#pragma unroll
+        for (int k = 0; k < kKeep; ++k, i += 256) {
+            if (i < n4) {
+                const float4 w = w4[i];
+                store4<TOut>(o + 4 * i, w.x * (scale * kept[k].x), w.y * (scale * kept[k].y), w.z * (scale * kept[k].z),
+                             w.w * (scale * kept[k].w));
+            }
+        }
+        for (; i < n4; i += 256) {
+            const float4 v = x4[i], w = w4[i];
+            store4<TOut>(o + 4 * i, w.x * (scale * v.x), w.y * (scale * v.y), w.z * (scale * v.z), w.w * (scale * v.w));
+        }
+    } else {
+        for (int d = threadIdx.x; d < D; d += 256) o[d] = from_float<TOut>(weight[d] * (scale * xr[d]));
+    }
 }
 
 // ---------------------------------------------------------------------------------- SwiGLU
@@ -80,55 +137,59 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, TOut* __restrict__ o
 // ---------------------------------------------------------------------------------- RoPE + store
 // One block per token. Query heads are rotated and written to q_out; key heads are rotated and
 // written to the token's cache row; value heads are copied there. cos/sin are rows of a table
-// [max_position, rot_half] built on the host in double precision.
+// [max_position, rot_half] built on the host in double precision. A thread rotates one pair
+// (both members read once); dims beyond the rotary size and the values are copied.
 template <typename TQ, typename TKV>
-__global__ void rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positions,
-                                  const int* __restrict__ row_req, const int* __restrict__ block_tables,
-                                  int table_stride, const float* __restrict__ cos_t,
-                                  const float* __restrict__ sin_t, int rot_half, int interleaved,
-                                  TQ* __restrict__ q_out, TKV* __restrict__ k_cache, TKV* __restrict__ v_cache,
-                                  int H, int Hkv, int hd, int page_size, int write_kv) {
+__global__ void __launch_bounds__(256)
+rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positions,
+                  const int* __restrict__ row_req, const int* __restrict__ block_tables,
+                  int table_stride, const float* __restrict__ cos_t,
+                  const float* __restrict__ sin_t, int rot_half, int interleaved,
+                  TQ* __restrict__ q_out, TKV* __restrict__ k_cache, TKV* __restrict__ v_cache,
+                  int H, int Hkv, int hd, int page_size, int write_kv) {
     pdl_prologue();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const float* row = qkv + static_cast<size_t>(t) * (H + 2 * Hkv) * hd;
     const float* c = cos_t ? cos_t + static_cast<size_t>(pos) * rot_half : nullptr;
     const float* s = sin_t ? sin_t + static_cast<size_t>(pos) * rot_half : nullptr;
-    const int rot_dim = c ? 2 * rot_half : 0;
+    const int half = c ? rot_half : 0;
+    const int rot_dim = 2 * half;
     size_t kv_base = 0;
     if (write_kv) {
         const int page = block_tables[static_cast<size_t>(row_req[t]) * table_stride + pos / page_size];
         kv_base = (static_cast<size_t>(page) * Hkv * page_size + (pos % page_size)) * hd;
     }
-    const int n_rot = (H + (write_kv ? Hkv : 0)) * hd;
-    for (int e = threadIdx.x; e < n_rot; e += blockDim.x) {
-        const int head = e / hd, d = e % hd;
+    const int n_heads = H + (write_kv ? Hkv : 0);
+    TQ* q_row = q_out + static_cast<size_t>(t) * H * hd;
+    // rotated pairs
+    for (int e = threadIdx.x; e < n_heads * half; e += 256) {
+        const int head = e / half, k = e - head * half;
         const float* v = row + static_cast<size_t>(head) * hd;
-        float o;
-        if (d < rot_dim) {
-            if (interleaved) {
-                const int k = d >> 1;
-                o = (d & 1) ? v[d - 1] * s[k] + v[d] * c[k] : v[d] * c[k] - v[d + 1] * s[k];
-            } else if (d < rot_half) {
-                o = v[d] * c[d] - v[d + rot_half] * s[d];
-            } else {
-                const int k = d - rot_half;
-                o = v[k] * s[k] + v[d] * c[k];
-            }
-        } else {
-            o = v[d];
-        }
+        const int ia = interleaved ? 2 * k : k, ib = interleaved ? 2 * k + 1 : k + half;
+        const float a = v[ia], b = v[ib], ck = c[k], sk = s[k];
+        const float oa = a * ck - b * sk, ob = a * sk + b * ck;
         if (head < H) {
-            q_out[(static_cast<size_t>(t) * H + head) * hd + d] = from_float<TQ>(o);
+            q_row[head * hd + ia] = from_float<TQ>(oa);
+            q_row[head * hd + ib] = from_float<TQ>(ob);
         } else {
-            const int g = head - H;
-            k_cache[kv_base + static_cast<size_t>(g) * page_size * hd + d] = from_float<TKV>(o);
+            TKV* kr = k_cache + kv_base + static_cast<size_t>(head - H) * page_size * hd;
+            kr[ia] = from_float<TKV>(oa);
+            kr[ib] = from_float<TKV>(ob);
         }
+    }
+    // dims that are not rotated
+    const int rest = hd - rot_dim;
+    for (int e = threadIdx.x; e < n_heads * rest; e += 256) {
+        const int head = e / rest, d = rot_dim + (e - head * rest);
+        const float v = row[static_cast<size_t>(head) * hd + d];
+        if (head < H) q_row[head * hd + d] = from_float<TQ>(v);
+        else k_cache[kv_base + static_cast<size_t>(head - H) * page_size * hd + d] = from_float<TKV>(v);
     }
     if (write_kv) {
         const float* vrow = row + static_cast<size_t>(H + Hkv) * hd;
-        for (int e = threadIdx.x; e < Hkv * hd; e += blockDim.x) {
-            const int g = e / hd, d = e % hd;
+        for (int e = threadIdx.x; e < Hkv * hd; e += 256) {
+            const int g = e / hd, d = e - g * hd;
             v_cache[kv_base + static_cast<size_t>(g) * page_size * hd + d] = from_float<TKV>(vrow[e]);
         }
     }

@@ -102,7 +102,10 @@ class StepContext:
             for r, s in enumerate(self.segments):
                 if s.length > 1:
                     for t in range(0, s.length, tokens_per_tile):
-                        tiles.append((s.start + t, min(tokens_per_tile, s.length - t), r))
+                        tiles.append((s.first_position + t, s.start + t, min(tokens_per_tile, s.length - t), r))
+            # the causal triangle makes late tiles of a prompt the longest ones: they start first
+            tiles.sort(key=lambda tile: -tile[0])
+            tiles = [tile[1:] for tile in tiles]
             longest = self.longest_single
             flat = single + [v for tile in tiles for v in tile]
             dev = self._engine.upload_ints(flat)
