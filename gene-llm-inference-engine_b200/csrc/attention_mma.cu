@@ -120,13 +120,16 @@ struct LaneOffsets {
 // q_frag: A fragments of the 16 x HD query tile. Row limits (lo, pos) are those of the two rows
 // this lane holds (lane/4 and lane/4 + 8) and are applied only when kMasked (a tile at the edge
 // of some row's range). o: HD/8 n-tiles x 4 accumulators. m (in the scaled log2 domain), l: per row.
-template <int HD, int TILE, bool TMA, bool kMasked>
+template <int HD, int TILE, bool TMA, bool kMasked, bool kUpper = true>
 __device__ __forceinline__ void warp_tile_step(const uint32_t (*q_frag)[4], uint32_t k_tile, uint32_t v_tile, int key0,
                                                const int* row_lo, const int* row_pos, float scale_log2,
                                                float (*o)[4], float* m, float* l, int lane,
                                                const LaneOffsets<HD, TILE, TMA>& off) {
+    // kUpper false: rows 8..15 of the tile are padding (a decode tile holds at most 8 query heads);
+    // their softmax and rescaling are skipped and their weights enter P V as zeros.
     constexpr int kK = HD / 16;                 // k-steps of Q K^T
     constexpr int kN = TILE / 8;                // n-tiles of S
+    constexpr int kR = kUpper ? 2 : 1;          // row halves this lane works on
     constexpr uint32_t RS = LaneOffsets<HD, TILE, TMA>::kRowStride;
     float s[kN][4];
 #pragma unroll
@@ -146,7 +149,7 @@ __device__ __forceinline__ void warp_tile_step(const uint32_t (*q_frag)[4], uint
 #pragma unroll
     for (int j = 0; j < kN; ++j) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
+        for (int e = 0; e < 2 * kR; ++e) {
             const int r = e >> 1;
             if (kMasked) {
                 const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
@@ -157,7 +160,7 @@ __device__ __forceinline__ void warp_tile_step(const uint32_t (*q_frag)[4], uint
     }
     float corr[2], m_use[2];
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < kR; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
         const float m_new = fmaxf(m[r], mx[r] * scale_log2);            // scale > 0: the maximum commutes with it
@@ -169,7 +172,7 @@ __device__ __forceinline__ void warp_tile_step(const uint32_t (*q_frag)[4], uint
 #pragma unroll
     for (int j = 0; j < kN; ++j) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
+        for (int e = 0; e < 2 * kR; ++e) {
             const int r = e >> 1;
             const float p = exp2f(fmaf(s[j][e], scale_log2, -m_use[r]));  // masked scores (-inf) give 0
             s[j][e] = p;
@@ -177,23 +180,24 @@ __device__ __forceinline__ void warp_tile_step(const uint32_t (*q_frag)[4], uint
         }
     }
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < kR; ++r) {
         sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
         sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
         l[r] = l[r] * corr[r] + sum[r];
     }
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n) {
-        o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+        o[n][0] *= corr[0]; o[n][1] *= corr[0];
+        if (kUpper) { o[n][2] *= corr[1]; o[n][3] *= corr[1]; }
     }
     // O += P V: P as A fragments (16 keys per k-step), V^T through transposed ldmatrix
 #pragma unroll
     for (int t = 0; t < TILE / 16; ++t) {
         uint32_t a[4];
         a[0] = pack_bf16(s[2 * t][0], s[2 * t][1]);
-        a[1] = pack_bf16(s[2 * t][2], s[2 * t][3]);
+        a[1] = kUpper ? pack_bf16(s[2 * t][2], s[2 * t][3]) : 0u;
         a[2] = pack_bf16(s[2 * t + 1][0], s[2 * t + 1][1]);
-        a[3] = pack_bf16(s[2 * t + 1][2], s[2 * t + 1][3]);
+        a[3] = kUpper ? pack_bf16(s[2 * t + 1][2], s[2 * t + 1][3]) : 0u;
 #pragma unroll
         for (int n = 0; n < HD / 8; ++n) {
             uint32_t b0, b1;
@@ -557,9 +561,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                         asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(kv_addr<HD, kTile, true>(v_tile, row, c)), "r"(0) : "memory");
                 }
                 __syncwarp();
-                warp_tile_step<HD, kTile, true, true>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
+                if (G <= 8) warp_tile_step<HD, kTile, true, true, false>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
+                else warp_tile_step<HD, kTile, true, true, true>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
             } else {
-                warp_tile_step<HD, kTile, true, false>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
+                if (G <= 8) warp_tile_step<HD, kTile, true, false, false>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
+                else warp_tile_step<HD, kTile, true, false, true>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
             }
             __syncwarp();                                   // every lane is done reading the stage
             if (pw < total) issue();
