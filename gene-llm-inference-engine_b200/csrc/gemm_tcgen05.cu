@@ -364,7 +364,7 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32
                  ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -389,8 +389,10 @@ struct TcPersistentParams {
     int* status;
 };
 
+constexpr int kPersistentThreads = 64 + 2 * 128;     // producer warp, MMA warp, two epilogue groups of four warps
+
 template <int BLOCK_Q, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kPersistentThreads, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                           const __grid_constant__ CUtensorMap map_c, const TcPersistentParams p) {
     using Cfg = TcPersistentConfig<BLOCK_Q>;
@@ -414,7 +416,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bars[2 * kStages + b]), 1);
-            mbar_init(smem_u32(&bars[2 * kStages + 2 + b]), 128);
+            mbar_init(smem_u32(&bars[2 * kStages + 2 + b]), kPersistentThreads - 64);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -496,12 +498,19 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
             }
         }
     } else {
-        // ---------------------------------------------------------------- epilogue (warps 2..5)
-        const int lane_group = warp & 3;
+        // ---------------------------------------------------------------- epilogue (warps 2..9)
+        // Two groups of four warps share a tile: group 0 (warps 2..5) takes the even column chunks,
+        // group 1 (warps 6..9) the odd ones. Each group has its own staging buffer, named barrier
+        // and leader thread that issues the group's TMA stores.
+        const int group = (warp - 2) >> 2;
+        const int lane_group = warp & 3;                         // the TMEM lanes this warp may read
         const int row = lane_group * 32 + lane;                  // row of the tile = TMEM lane
-        const bool leader = (warp == 2 && lane == 0);
+        const bool leader = (((warp - 2) & 3) == 0 && lane == 0);
         const uint32_t lane_addr = static_cast<uint32_t>(lane_group * 32) << 16;
-        int j = 0, n_stores = 0;
+        uint8_t* stg = staging + group * Cfg::kStagingBytes;
+        const int bar_id = 1 + group;
+        auto group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory"); };
+        int j = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++j) {
             const int tile_p = t % p.tiles_p, tile_q = t / p.tiles_p;
@@ -509,18 +518,22 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
             if (ok && !mbar_wait(smem_u32(&bars[2 * kStages + buf]), (j >> 1) & 1, abort_flag)) {
                 if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, kErrEpilogueWait); }
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (*abort_flag) ok = false;                          // read after the barrier: one decision for all
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            group_sync();
+            if (*abort_flag) ok = false;                          // read after the barrier: one decision for the group
+            group_sync();
             if (!ok) break;
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + buf * BLOCK_Q + lane_addr;
             constexpr int kChunks = (EPI == kEpiSwiGLU) ? BLOCK_Q / 128 : BLOCK_Q / 32;   // TMA stores per tile
-            for (int c = 0; c < kChunks; ++c) {
-                uint8_t* stg = staging + (n_stores & 1) * Cfg::kStagingBytes;
-                if (leader) bulk_wait_read1();                    // the store issued two chunks ago has read its staging
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (group >= kChunks) {                               // a tile with a single chunk: this group has nothing to read
+                tc_fence_before();
+                mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf]));
+            }
+            for (int c = group; c < kChunks; c += 2) {
+                if (leader) bulk_wait_read0();                    // the group's last store has read the staging buffer
+                group_sync();
                 uint32_t r[32];
+                const bool last = c + 2 >= kChunks;               // this group's last chunk of the tile
                 if (EPI == kEpiSwiGLU) {
                     // 64 output channels per store, in two halves of 32: gate at column ch, up at BLOCK_Q/2 + ch
 #pragma unroll
@@ -532,7 +545,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                         tmem_ld_x16(tmem_d + BLOCK_Q / 2 + ch, u);
                         tmem_ld_x16(tmem_d + BLOCK_Q / 2 + ch + 16, u + 16);
                         tmem_ld_wait();
-                        if (c == kChunks - 1 && half == 1) { tc_fence_before(); mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf])); }
+                        if (last && half == 1) { tc_fence_before(); mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf])); }
 #pragma unroll
                         for (int q4 = 0; q4 < 4; ++q4) {          // 8 channels = 16 bytes of bfloat16 per step
                             uint32_t packed[4];
@@ -554,21 +567,20 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                     tmem_ld_x16(tmem_d + c * 32, r);
                     tmem_ld_x16(tmem_d + c * 32 + 16, r + 16);
                     tmem_ld_wait();
-                    if (c == kChunks - 1) { tc_fence_before(); mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf])); }
+                    if (last) { tc_fence_before(); mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf])); }
 #pragma unroll
                     for (int q4 = 0; q4 < 8; ++q4)
                         *reinterpret_cast<uint4*>(stg + row * 128 + ((q4 ^ (row & 7)) * 16)) =
                             make_uint4(r[q4 * 4], r[q4 * 4 + 1], r[q4 * 4 + 2], r[q4 * 4 + 3]);
                 }
                 fence_async_smem();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                group_sync();
                 if (leader) {
                     const int col = (EPI == kEpiSwiGLU) ? tile_q * (BLOCK_Q / 2) + c * 64 : tile_q * BLOCK_Q + c * 32;
                     if (EPI == kEpiAddF32) tma_reduce_add_2d(&map_c, smem_u32(stg), col, tile_p * kBlockP);
                     else tma_store_2d(&map_c, smem_u32(stg), col, tile_p * kBlockP);
                     bulk_commit();
                 }
-                ++n_stores;
             }
         }
         if (leader) bulk_wait_all();
@@ -638,7 +650,7 @@ static int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, const
     }
     const int tiles = p.tiles_p * p.tiles_q;
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    launch_kernel((gemm_tc_persistent_kernel<BLOCK_Q, EPI>), dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, mp, mq, mc, p);
+    launch_kernel((gemm_tc_persistent_kernel<BLOCK_Q, EPI>), dim3(grid), dim3(kPersistentThreads), Cfg::kSmemBytes, st, mp, mq, mc, p);
     return check_launch("gemm_tc_persistent");
 }
 

@@ -32,18 +32,12 @@ __device__ __forceinline__ double block_sum_double(double v, double* scratch) {
     return total;
 }
 
-__global__ void __launch_bounds__(kSampleThreads)
-argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
-    pdl_prologue();
-    __shared__ float s_val[32];
-    __shared__ int s_idx[32];
-    const float* row = logits + static_cast<size_t>(blockIdx.x) * V;
-    float best = -INFINITY;
-    int best_i = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best || best_i == 0x7fffffff) { best = v; best_i = i; }   // increasing i: ties keep the lower index
-    }
+// Greedy argmax in two steps: kArgmaxParts blocks per row each find the best of a slice of the
+// vocabulary (lowest index among equals), then one block per row picks among the slice winners.
+// One block per row would read 0.5 MB through a single SM.
+constexpr int kArgmaxParts = 32;
+
+__device__ __forceinline__ void argmax_block_reduce(float& best, int& best_i, float* s_val, int* s_idx) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -57,8 +51,44 @@ argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
         for (int w = 1; w < (blockDim.x >> 5); ++w) {
             if (s_val[w] > best || (s_val[w] == best && s_idx[w] < best_i)) { best = s_val[w]; best_i = s_idx[w]; }
         }
-        out[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
     }
+}
+
+// grid (kArgmaxParts, rows): the best of one slice -> part_val / part_idx [rows, kArgmaxParts]
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, int V, float* __restrict__ part_val, int* __restrict__ part_idx) {
+    pdl_prologue();
+    __shared__ float s_val[8];
+    __shared__ int s_idx[8];
+    const float* row = logits + static_cast<size_t>(blockIdx.y) * V;
+    const int per = (V + kArgmaxParts - 1) / kArgmaxParts;
+    const int begin = blockIdx.x * per, end = min(V, begin + per);
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = begin + threadIdx.x; i < end; i += 256) {
+        const float v = row[i];
+        if (v > best || best_i == 0x7fffffff) { best = v; best_i = i; }   // increasing i: ties keep the lower index
+    }
+    argmax_block_reduce(best, best_i, s_val, s_idx);
+    if (threadIdx.x == 0) {
+        part_val[blockIdx.y * kArgmaxParts + blockIdx.x] = best;
+        part_idx[blockIdx.y * kArgmaxParts + blockIdx.x] = best_i;
+    }
+}
+
+// one warp per row
+__global__ void __launch_bounds__(32)
+argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int* __restrict__ out) {
+    pdl_prologue();
+    float best = part_val[blockIdx.x * kArgmaxParts + threadIdx.x];
+    int best_i = part_idx[blockIdx.x * kArgmaxParts + threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
 }
 
 // The bits fixed so far of the value searched for: elements with (bits & mask) == prefix remain.
@@ -326,10 +356,16 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ probs_all, i
 
 using namespace gi;
 
-extern "C" int gi_argmax(const float* logits, int rows, int V, int* out, void* stream) {
+// part_val / part_idx: caller's scratch of rows * 32 floats / ints.
+extern "C" int gi_argmax(const float* logits, int rows, int V, int* out, float* part_val, int* part_idx, void* stream) {
     if (rows == 0) return 0;
     GI_REQUIRE(rows > 0 && V > 0, "argmax: sizes must be positive (rows=%d, V=%d)", rows, V);
-    launch_kernel((argmax_kernel), dim3(rows), dim3(kSampleThreads), 0, static_cast<cudaStream_t>(stream), logits, V, out);
+    GI_REQUIRE(rows <= 65535, "argmax: %d rows exceed the grid limit", rows);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    launch_kernel((argmax_partial_kernel), dim3(kArgmaxParts, rows), dim3(256), 0, st, logits, V, part_val, part_idx);
+    if (check_launch("argmax")) return 1;
+    launch_kernel((argmax_final_kernel), dim3(rows), dim3(32), 0, st, static_cast<const float*>(part_val),
+                  static_cast<const int*>(part_idx), out);
     return check_launch("argmax");
 }
 

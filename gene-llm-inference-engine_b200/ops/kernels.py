@@ -303,10 +303,22 @@ def gemm_tc_status(device: torch.device) -> int:
     return out.value
 
 
+_argmax_scratch = {}
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = index of the largest logit of row r (the lowest index among equals)."""
     rows, V = logits.shape
-    check(lib().gi_argmax(_dev(logits, "logits", torch.float32), rows, V, _dev(out, "out", torch.int32), _stream()),
-          "argmax")
+    key = logits.device.index
+    buf = _argmax_scratch.get(key)
+    if buf is None or buf[0].numel() < rows * 32:
+        n = max(rows, 64) * 32
+        buf = (torch.empty(n, dtype=torch.float32, device=logits.device), torch.empty(n, dtype=torch.int32, device=logits.device))
+        _argmax_scratch[key] = buf
+    check(lib().gi_argmax(_dev(logits, "logits", torch.float32), rows, V, _dev(out, "out", torch.int32),
+                          buf[0].data_ptr(), buf[1].data_ptr(), _stream()), "argmax")
+    global _launches
+    _launches += 1            # two kernels
 
 
 def sample(logits: torch.Tensor, scratch: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,

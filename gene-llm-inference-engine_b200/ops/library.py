@@ -42,7 +42,7 @@ _SIGNATURES = {
     "gi_attention_prefill_rows": [c_int, c_int],
     "gi_attention_fast_supported": [c_int, c_int, c_int],
     "gi_attention_chunk_keys": [],
-    "gi_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "gi_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "gi_sample": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
