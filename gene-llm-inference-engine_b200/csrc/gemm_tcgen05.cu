@@ -137,17 +137,28 @@ template <int BLOCK_Q>
 __device__ __forceinline__ void store_row_chunk(const TcParams& p, int row_p, int q0, const float* v) {
     // v[j] belongs to (row_p, q0 + j), j < 16
     if (row_p >= p.rows_p) return;
+    const long long base = static_cast<long long>(row_p) * p.stride_p + static_cast<long long>(q0) * p.stride_q;
+    const int n = min(16, p.rows_q - q0);
+    if (p.c_bf16) {
+        __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.C) + base;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const int q = q0 + j;
-        if (q >= p.rows_q) break;
-        const long long idx = static_cast<long long>(row_p) * p.stride_p + static_cast<long long>(q) * p.stride_q;
-        if (p.c_bf16) {
-            static_cast<__nv_bfloat16*>(p.C)[idx] = __float2bfloat16_rn(v[j]);
-        } else {
-            float* c = static_cast<float*>(p.C) + idx;
-            *c = p.accumulate ? *c + v[j] : v[j];
-        }
+        for (int j = 0; j < 16; ++j)
+            if (j < n) c[j * p.stride_q] = __float2bfloat16_rn(v[j]);
+    } else if (p.accumulate) {
+        // all loads first, then all stores: the sixteen read-modify-writes overlap instead of
+        // waiting for one another
+        float* c = static_cast<float*>(p.C) + base;
+        float old[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) old[j] = (j < n) ? __ldcg(c + j * p.stride_q) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (j < n) c[j * p.stride_q] = old[j] + v[j];
+    } else {
+        float* c = static_cast<float*>(p.C) + base;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (j < n) c[j * p.stride_q] = v[j];
     }
 }
 
