@@ -338,7 +338,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 // three tiles ahead, across chunk borders. Pages wholly outside a query's range are not fetched.
 template <int HD>
 struct DecodeTma {
-    static constexpr int kTile = HD <= 64 ? 64 : 32;
+    // Eight warps with 32-key tiles where the head size allows it (two warps per scheduler hide each
+    // other's fixed latencies); a head size of 128 keeps four warps for its 16 KB stages.
+    static constexpr int kWarps = HD <= 64 ? 8 : 4;
+    static constexpr int kThreads = kWarps * 32;
+    static constexpr int kTile = 32;
     static constexpr int kTilesPerChunk = kChunkKeys / kTile;
     static constexpr int kBoxCols = HD < 64 ? HD : 64;
     static constexpr int kHalves = HD / kBoxCols;                 // 2 for HD = 128
@@ -347,7 +351,8 @@ struct DecodeTma {
     static constexpr int kStages = 3;
     static constexpr int kQBytes = 16 * HD * 2;
     static constexpr int kMetaRows = 512;          // requests whose (row, position, request) are staged in shared memory
-    static constexpr int kSmemBytes = 4 * kStages * kStageBytes + 4 * kQBytes + 128 + 3 * kMetaRows * 4 + 1024;
+    static constexpr int kBarBytes = 256;
+    static constexpr int kSmemBytes = kWarps * kStages * kStageBytes + kWarps * kQBytes + kBarBytes + 3 * kMetaRows * 4 + 1024;
 };
 
 __device__ __forceinline__ void att_mbar_init(uint32_t bar) { asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar)); }
@@ -379,7 +384,7 @@ struct DecodeItem {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(kAttThreads, 1)
+__global__ void __launch_bounds__(DecodeTma<HD>::kThreads, 1)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const __nv_bfloat16* __restrict__ q, const int* __restrict__ rows, int n_rows,
                             const int* __restrict__ row_req, const int* __restrict__ positions,
@@ -392,10 +397,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t stages = smem_addr(smem) + warp * kStages * Cfg::kStageBytes;
-    uint8_t* q_ptr = smem + 4 * kStages * Cfg::kStageBytes + warp * Cfg::kQBytes;
+    uint8_t* q_ptr = smem + Cfg::kWarps * kStages * Cfg::kStageBytes + warp * Cfg::kQBytes;
     const uint32_t q_tile = smem_addr(q_ptr);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 4 * kStages * Cfg::kStageBytes + 4 * Cfg::kQBytes) + warp * kStages;
-    int* meta = reinterpret_cast<int*>(smem + 4 * kStages * Cfg::kStageBytes + 4 * Cfg::kQBytes + 128);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kWarps * kStages * Cfg::kStageBytes + Cfg::kWarps * Cfg::kQBytes) + warp * kStages;
+    int* meta = reinterpret_cast<int*>(smem + Cfg::kWarps * kStages * Cfg::kStageBytes + Cfg::kWarps * Cfg::kQBytes + Cfg::kBarBytes);
     const int G = H / Hkv;
 
     if (lane == 0) {
@@ -406,7 +411,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     pdl_prologue();
     // (step row, position, request) of every decoded token, once per CTA: the per-item look-ups
     // below would otherwise be chains of dependent global loads on each warp's critical path
-    for (int i = threadIdx.x; i < n_rows && i < Cfg::kMetaRows; i += kAttThreads) {
+    for (int i = threadIdx.x; i < n_rows && i < Cfg::kMetaRows; i += Cfg::kThreads) {
         const int t = rows[i];
         meta[i] = t;
         meta[Cfg::kMetaRows + i] = positions[t];
@@ -415,7 +420,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     __syncthreads();
 
     const int total = n_rows * Hkv * n_chunks;
-    const int stride = gridDim.x * 4;
+    const int stride = gridDim.x * Cfg::kWarps;
     const int box_rows = page_size < kTile ? page_size : kTile;
     const int boxes = kTile / box_rows;
 
@@ -439,7 +444,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
     // ---- producer cursor: the next tile to request
     DecodeItem pi;
-    int pw = blockIdx.x * 4 + warp, ptile = 0, n_issued = 0;
+    int pw = blockIdx.x * Cfg::kWarps + warp, ptile = 0, n_issued = 0;
     int p_pages = 0;                           // lane i: the page of the chunk's i-th page-sized run of keys
     const int pages_per_chunk = kChunkKeys / page_size > 0 ? kChunkKeys / page_size : 1;
     auto p_seek = [&]() {
@@ -510,7 +515,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     bool failed = false;
     LaneOffsets<HD, kTile, true> off;
     off.init(lane);
-    for (int cw = blockIdx.x * 4 + warp; cw < total && !failed; cw += stride) {
+    for (int cw = blockIdx.x * Cfg::kWarps + warp; cw < total && !failed; cw += stride) {
         item_at(cw, ci);
         float* my_o = part_o + ((static_cast<size_t>(ci.idx) * H + ci.g * G) * max_chunks + ci.chunk) * HD;
         float* my_ml = part_ml + ((static_cast<size_t>(ci.idx) * H + ci.g * G) * max_chunks + ci.chunk) * 2;
@@ -952,9 +957,9 @@ static int launch_decode_tma(const void* q, const void* kc, const void* vc, void
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int items = n_rows * Hkv * n_chunks;
-    int grid = (items + 3) / 4;
+    int grid = (items + Cfg::kWarps - 1) / Cfg::kWarps;
     if (grid > sms) grid = sms;
-    launch_kernel((attention_decode_tma_kernel<HD>), dim3(grid), dim3(kAttThreads), Cfg::kSmemBytes, st, mk, mv,
+    launch_kernel((attention_decode_tma_kernel<HD>), dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, mk, mv,
                   static_cast<const __nv_bfloat16*>(q), rows, n_rows, row_req, positions, tables, table_stride, H, Hkv,
                   page_size, scale * kLog2e, window, part_o, part_ml, max_chunks, n_chunks, status);
     if (check_launch("attention_decode_tma")) return 1;
@@ -1040,7 +1045,7 @@ extern "C" int gi_attention_decode(const void* q, const void* k_cache, const voi
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // Pages that TMA boxes can tile (8, 16, 32 ... rows that divide or are divided by the tile) take
     // the TMA-fed kernel; any other page size takes the cp.async kernel.
-    const int tile = hd <= 64 ? 64 : 32;
+    const int tile = 32;
     const bool tma_ok = page_size % 8 == 0 && (tile % page_size == 0 || page_size % tile == 0) && status != nullptr &&
                         reinterpret_cast<uintptr_t>(k_cache) % 16 == 0 && reinterpret_cast<uintptr_t>(v_cache) % 16 == 0;
     if (tma_ok) {
