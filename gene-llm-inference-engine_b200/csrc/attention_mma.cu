@@ -790,27 +790,31 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __
 
     if (warp == Cfg::kWarps) {
         // ---------------------------------------------------------------- producer warp
-        if (lane == 0) {
-            for (int i = 0; i < n_tiles; ++i) {
-                const int s = i % kStages;
-                if (i >= kStages && !att_wait(smem_addr(&empty[s]), ((i / kStages) - 1) & 1)) {
-                    atomicCAS(status, 0, 6);
-                    break;
-                }
-                const int key0 = (first_tile + i) * kTile;
-                const uint32_t k_tile = stages + s * Cfg::kStageBytes, v_tile = k_tile + Cfg::kTileBytes;
-                int n_boxes = 0;
-                for (int b = 0; b < boxes; ++b) {
-                    const int kb = key0 + b * box_rows;
-                    if (kb <= pos_last && kb + box_rows - 1 >= lo_first) ++n_boxes;
-                }
+        // All lanes look up the tile's pages at once (lane b: box b), before the wait for the free
+        // stage; lane 0 issues the boxes.
+        for (int i = 0; i < n_tiles; ++i) {
+            const int s = i % kStages;
+            const int key0 = (first_tile + i) * kTile;
+            const int kb_lane = key0 + lane * box_rows;
+            const bool lane_valid = lane < boxes && kb_lane <= pos_last && kb_lane + box_rows - 1 >= lo_first;
+            const int page_lane = lane_valid ? table[kb_lane / page_size] : 0;
+            const unsigned valid_mask = __ballot_sync(0xffffffffu, lane_valid);
+            bool ok = true;
+            if (lane == 0 && i >= kStages && !att_wait(smem_addr(&empty[s]), ((i / kStages) - 1) & 1)) {
+                atomicCAS(status, 0, 6);
+                ok = false;
+            }
+            if (!__shfl_sync(0xffffffffu, ok ? 1 : 0, 0)) break;
+            const uint32_t k_tile = stages + s * Cfg::kStageBytes, v_tile = k_tile + Cfg::kTileBytes;
+            const uint32_t bar = smem_addr(&full[s]);
+            if (lane == 0) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                const uint32_t bar = smem_addr(&full[s]);
-                att_expect_tx(bar, static_cast<uint32_t>(n_boxes) * 2u * box_rows * HD * 2u);
-                for (int b = 0; b < boxes; ++b) {
+                att_expect_tx(bar, static_cast<uint32_t>(__popc(valid_mask)) * 2u * box_rows * HD * 2u);
+            }
+            for (int b = 0; b < boxes; ++b) {
+                const int page = __shfl_sync(0xffffffffu, page_lane, b);
+                if (lane == 0 && ((valid_mask >> b) & 1u)) {
                     const int kb = key0 + b * box_rows;
-                    if (!(kb <= pos_last && kb + box_rows - 1 >= lo_first)) continue;
-                    const int page = table[kb / page_size];
                     const int row = (page * Hkv + g) * page_size + kb % page_size;
 #pragma unroll
                     for (int h = 0; h < Cfg::kHalves; ++h) {

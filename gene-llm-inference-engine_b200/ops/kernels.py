@@ -206,6 +206,30 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         k_cache.shape[0], _tc_state(q.device).status.data_ptr(), _stream()), "attention_prefill")
 
 
+def attention_prefill_tc_supported(head_dim: int, num_heads: int, num_kv_heads: int, page_size: int) -> bool:
+    """Whether the tcgen05 prefill attention serves this shape (head size 64 or 128, pages TMA can tile)."""
+    return bool(lib().gi_attention_prefill_tc_supported(head_dim, num_heads, num_kv_heads, page_size))
+
+
+def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                         work: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor, num_heads: int,
+                         num_kv_heads: int, head_dim: int, page_size: int, scale: float, window: Optional[int]) -> None:
+    """Attention of prompt portions on the tcgen05 tensor cores: ``work`` [n, 3] = (first step row of
+    a tile, tokens in it (at most 128 // group size), request index)."""
+    if work.dim() != 2 or work.shape[1] != 3:
+        raise KernelError("attention_prefill_tc: work must be [n, 3]")
+    if k_cache.shape[1:] != (num_kv_heads, page_size, head_dim) or v_cache.shape != k_cache.shape:
+        raise KernelError("attention: the cache must be [pages, Hkv, page_size, hd]")
+    if q.shape[1] != num_heads * head_dim or out.shape != q.shape:
+        raise KernelError("attention: q and out must be [T, H*hd]")
+    check(lib().gi_attention_prefill_tc(
+        _dev(q, "q", torch.bfloat16), _dev(k_cache, "k_cache", torch.bfloat16), _dev(v_cache, "v_cache", torch.bfloat16),
+        _dev(out, "out", torch.bfloat16), _dev(work, "work", torch.int32), work.shape[0],
+        _dev(positions, "positions", torch.int32), _dev(block_tables, "block_tables", torch.int32),
+        block_tables.shape[1], num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
+        k_cache.shape[0], _tc_state(q.device).status.data_ptr(), _stream()), "attention_prefill_tc")
+
+
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """out[M,N] (+)= a[M,K] @ w[N,K]^T with 32-bit fused multiply-adds on the CUDA cores."""
     M, K = a.shape

@@ -40,6 +40,9 @@ _SIGNATURES = {
     "gi_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                              c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p, c_void_p],
     "gi_attention_prefill_rows": [c_int, c_int],
+    "gi_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p, c_void_p],
+    "gi_attention_prefill_tc_supported": [c_int, c_int, c_int, c_int],
     "gi_attention_fast_supported": [c_int, c_int, c_int],
     "gi_attention_chunk_keys": [],
     "gi_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],

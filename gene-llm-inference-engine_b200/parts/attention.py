@@ -51,9 +51,19 @@ class AttentionMixer:
             self.chunk_keys = kernels.attention_chunk_keys()
             self.max_chunks = (build.max_position + self.chunk_keys - 1) // self.chunk_keys
 
+    def prefill_on_tcgen05(self, page_size: int) -> bool:
+        """Head sizes 64 and 128 with pages TMA can tile: prompt portions run on the tcgen05 kernel."""
+        key = ("tc", page_size)
+        if key not in self._prefill_rows:
+            self._prefill_rows[key] = kernels.attention_prefill_tc_supported(self.head_dim, self.num_heads,
+                                                                             self.num_kv_heads, page_size)
+        return self._prefill_rows[key]
+
     def prefill_rows(self, page_size: int) -> int:
+        """Query rows (tokens x heads of a group) per work item of the prefill kernel in use."""
         if page_size not in self._prefill_rows:
-            self._prefill_rows[page_size] = kernels.attention_prefill_rows(page_size, self.head_dim)
+            self._prefill_rows[page_size] = 128 if self.prefill_on_tcgen05(page_size) else \
+                kernels.attention_prefill_rows(page_size, self.head_dim)
         return self._prefill_rows[page_size]
 
     def cache_need(self):
@@ -88,8 +98,9 @@ class AttentionMixer:
                 kernels.attention_decode(q, k_cache, v_cache, att, rows, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
                                          ctx.page_size, self.scale, self.window, part_o, part_ml, self.max_chunks, n_chunks)
             if work.shape[0]:
-                kernels.attention_prefill(q, k_cache, v_cache, att, work, ctx.positions, tables, H, Hkv, hd,
-                                          ctx.page_size, self.scale, self.window)
+                prefill = kernels.attention_prefill_tc if self.prefill_on_tcgen05(ctx.page_size) else kernels.attention_prefill
+                prefill(q, k_cache, v_cache, att, work, ctx.positions, tables, H, Hkv, hd, ctx.page_size, self.scale,
+                        self.window)
         else:
             kernels.attention_generic(q, k_cache, v_cache, att, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
                                       ctx.page_size, self.scale, self.window)

@@ -13,13 +13,17 @@ import tiny_configs as tc
 # 32-bit: both sides compute in 32-bit, only summation orders differ.
 TOL_F32 = 2e-5
 # bfloat16: the plain implementation rounds to bfloat16 where the engine does, but two bfloat16
-# computations that round in a slightly different order (the running maximum of an online softmax,
-# the order of a sum) differ by a fraction of the model's own bfloat16 noise, which depends on
-# how much the weights amplify it. The tolerance is therefore tied to that noise, measured per
-# model as the distance between the rounding and the exact plain implementation: an engine must
-# stay within three quarters of it (measured on B200: 0.27 to 0.51 of it, the largest share on the
-# model whose logits are smallest). A wrong key, position or page in the sharp models moves logits
-# by about their own size, an order of magnitude more than this.
+# computations that round in a slightly different order (the running maximum of an online softmax
+# over tiles of keys, the order of a sum) differ by a fraction of the model's own bfloat16 noise,
+# which depends on how much the weights amplify it and on how many tiles a sequence has. The
+# tolerance is therefore tied to that noise, measured per model with the measure the comparison
+# itself uses (per position, max|a-b| / max(1, max|b|), worst position of all requests) as the
+# distance between the rounding and the exact plain implementation: an engine must stay within
+# three quarters of it. Measured on B200: 0.22 to 0.57 of it, the largest share on the model with
+# the longest requests (512 tokens, 8 key tiles), with the mma.sync and the tcgen05 prefill kernel
+# alike; against the exact plain implementation the engine is as close as the rounding one is.
+# A wrong key, position or page in the sharp models moves logits by about their own size, an order
+# of magnitude more than this.
 BF16_NOISE_SHARE = 0.75
 
 _TMP = tempfile.TemporaryDirectory(prefix="geneinfer_tests_")
@@ -27,10 +31,11 @@ _TMP = tempfile.TemporaryDirectory(prefix="geneinfer_tests_")
 CASES = {
     "a": (tc.TINY_A, tc.SHARP_A), "b": (tc.TINY_B, tc.SHARP_B),
     "a_named": (tc.TINY_A, tc.WEIGHTS_A), "b_named": (tc.TINY_B, tc.WEIGHTS_B),
+    "c": (tc.TINY_C, tc.SHARP_C),
 }
 
 REQUEST_LENGTHS = {"a": [40, 75, 128, 100, 64, 33, 90], "b": [1, 5, 24, 64, 100, 200, 256],
-                   "a_named": [7, 16, 33], "b_named": [1, 5, 24, 64, 100]}
+                   "a_named": [7, 16, 33], "b_named": [1, 5, 24, 64, 100], "c": [300, 140, 512, 129, 2, 260]}
 
 
 @functools.lru_cache(maxsize=None)
@@ -58,9 +63,10 @@ def plain_logits(case: str, dtype: str):
 
 @functools.lru_cache(maxsize=None)
 def bf16_noise(case: str) -> float:
-    """max|a-b| / max(1, max|b|) between the bfloat16-rounding and the exact plain implementation."""
+    """Worst position's max|a-b| / max(1, max|b|) between the bfloat16-rounding and the exact plain implementation."""
     exact, rounded = plain_logits(case, "float32"), plain_logits(case, "bfloat16")
-    return max(float(np.abs(rounded[r] - exact[r]).max() / max(1.0, np.abs(exact[r]).max())) for r in exact)
+    per_row = [np.abs(rounded[r] - exact[r]).max(axis=-1) / np.maximum(1.0, np.abs(exact[r]).max(axis=-1)) for r in exact]
+    return float(max(rows.max() for rows in per_row))
 
 
 def tolerance(dtype: str, case: str) -> float:

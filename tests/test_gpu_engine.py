@@ -10,7 +10,7 @@ import trace_tools as tt
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-CASES = ["a", "b"]
+CASES = ["a", "b", "c"]
 
 
 def _play(case, dtype, steps, page_size=16):
@@ -18,6 +18,9 @@ def _play(case, dtype, steps, page_size=16):
     max_tokens = tt.max_tokens_of(steps, reqs)
     engine = gf.make_engine(case, dtype, n_pages=max_tokens // page_size, page_size=page_size)
     got = tt.run_in_process(engine, steps)
+    if dtype == "bfloat16":
+        from geneinfer_b200.ops import kernels
+        assert kernels.gemm_tc_status(engine.device) == 0, "a bounded wait of a tensor-core kernel gave up"
     engine.cache.check_invariants()
     assert not engine.cache.requests, "requests left open"
     assert all(g.pool.free_count == g.pool.n_pages for g in engine.cache.groups), "pages were lost"

@@ -151,11 +151,12 @@ def test_rope_store(dtype, H, Hkv, hd, ps, interleaved, rot):
         "rows of other positions were written"
 
 
-def _run_fast_attention(q_all, kc, vc, out, row_req, positions, tables, q_lens, ctx_lens, H, Hkv, hd, ps, scale, window):
+def _run_fast_attention(q_all, kc, vc, out, row_req, positions, tables, q_lens, ctx_lens, H, Hkv, hd, ps, scale, window,
+                        tcgen05=False):
     """The tensor-core kernels: single tokens through the decode kernel, portions through prefill."""
     kern = K()
     G = H // Hkv
-    per_tile = kern.attention_prefill_rows(ps, hd) // G
+    per_tile = (128 if tcgen05 else kern.attention_prefill_rows(ps, hd)) // G
     decode_rows, work, row = [], [], 0
     for r, n in enumerate(q_lens):
         if n == 1:
@@ -173,11 +174,11 @@ def _run_fast_attention(q_all, kc, vc, out, row_req, positions, tables, q_lens, 
         kern.attention_decode(q_all, kc, vc, out, torch.tensor(decode_rows, dtype=torch.int32, device=DEV), row_req,
                               positions, tables, H, Hkv, hd, ps, scale, window, part_o, part_ml, max_chunks, n_chunks)
     if work:
-        kern.attention_prefill(q_all, kc, vc, out, torch.tensor(work, dtype=torch.int32, device=DEV), positions, tables,
-                               H, Hkv, hd, ps, scale, window)
+        fn = kern.attention_prefill_tc if tcgen05 else kern.attention_prefill
+        fn(q_all, kc, vc, out, torch.tensor(work, dtype=torch.int32, device=DEV), positions, tables, H, Hkv, hd, ps, scale, window)
 
 
-def _attention_case(dtype, H, Hkv, hd, ps, ctx_lens, q_lens, window, seed, spike=None, fast=False):
+def _attention_case(dtype, H, Hkv, hd, ps, ctx_lens, q_lens, window, seed, spike=None, fast=False, tcgen05=False):
     """Requests with ``ctx_lens`` cached positions of which the last ``q_lens`` are this step's
     queries. Pages are scattered and unused pages hold NaN. ``spike`` = (request, key position):
     that key is made to match every query of the request strongly."""
@@ -218,7 +219,7 @@ def _attention_case(dtype, H, Hkv, hd, ps, ctx_lens, q_lens, window, seed, spike
     rr = torch.tensor(row_req, dtype=torch.int32, device=DEV)
     pp = torch.tensor(positions, dtype=torch.int32, device=DEV)
     if fast:
-        _run_fast_attention(q_all, kc, vc, out, rr, pp, tables.to(DEV), q_lens, ctx_lens, H, Hkv, hd, ps, scale, window)
+        _run_fast_attention(q_all, kc, vc, out, rr, pp, tables.to(DEV), q_lens, ctx_lens, H, Hkv, hd, ps, scale, window, tcgen05)
     else:
         K().attention_generic(q_all, kc, vc, out, rr, pp, tables.to(DEV), H, Hkv, hd, ps, scale, window)
     want = []
@@ -422,3 +423,30 @@ def test_gemm_persistent_many_tiles(M, N, K_, block_q):
     K().gemm_tc(a, w, acc, accumulate=True, plan=(False, block_q, 1))
     close(acc, want + base.cpu().double(), "float32", "persistent add", f32_tol=2e-6 * max(1, K_ / 64))
     assert K().gemm_tc_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.parametrize("H,Hkv,hd,ps", [(8, 2, 64, 16), (32, 8, 64, 16), (3, 1, 64, 8), (8, 2, 128, 32), (5, 5, 64, 16), (4, 4, 128, 128)])
+def test_attention_tcgen05_prefill(H, Hkv, hd, ps):
+    """The tcgen05 prefill kernel: whole prompts of several key tiles, a portion deep in a context
+    over page edges, a two-token portion, with single tokens beside them through the decode kernel."""
+    assert K().attention_prefill_tc_supported(hd, H, Hkv, ps)
+    got, want = _attention_case("bfloat16", H, Hkv, hd, ps, ctx_lens=[300, 700, 3 * ps + 1, 1, 130, 129], q_lens=[300, 45, ps + 2, 1, 2, 129],
+                                window=None, seed=16, fast=True, tcgen05=True)
+    assert K().gemm_tc_status(torch.device(DEV)) == 0
+    close(got, want, "bfloat16", "attention (tcgen05)", bf16_tol=1e-2)
+
+
+@pytest.mark.parametrize("far", [0, 127, 128, 255, 256, 500, 597])
+def test_attention_tcgen05_far_key(far):
+    got, want = _attention_case("bfloat16", 8, 2, 64, 16, ctx_lens=[600], q_lens=[40], window=None, seed=7, spike=(0, far),
+                                fast=True, tcgen05=True)
+    close(got, want, "bfloat16", f"far key {far}", bf16_tol=1e-2)
+
+
+@pytest.mark.parametrize("window", [1, 5, 33, 130, 300])
+def test_attention_tcgen05_window(window):
+    ctx = 700
+    got, want = _attention_case("bfloat16", 4, 2, 64, 16, ctx_lens=[ctx], q_lens=[window + 2], window=window, seed=8,
+                                spike=(0, ctx - 1 - window), fast=True, tcgen05=True)
+    close(got, want, "bfloat16", f"window {window}", bf16_tol=1e-2)
+    assert float(want[-1].abs().mean()) < 2.0 and float(want[-2].abs().mean()) > 2.0

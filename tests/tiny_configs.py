@@ -41,3 +41,14 @@ def make_model_dir(config, weights, out_dir):
 def random_tokens(n, vocab, seed):
     import numpy as np
     return [int(t) for t in np.random.default_rng(seed).integers(0, vocab, size=n)]
+
+TINY_C = {   # head size 64 (the tcgen05 prefill attention and the fused gate/up product are built for it), 6:2 heads
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_act": "silu",
+    "hidden_size": 192, "intermediate_size": 264, "num_hidden_layers": 2, "num_attention_heads": 6,
+    "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 500, "max_position_embeddings": 512,
+    "rope_theta": 100000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 128},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+}
+SHARP_C = {"seed": 31, "dtype": "bfloat16", "std": 0.12, "norm_mean": 1.0, "norm_std": 0.1}
