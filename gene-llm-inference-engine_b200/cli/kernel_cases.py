@@ -6,7 +6,7 @@ Cases at the Llama-3.2-1B layer sizes (random data, sizes larger than L2 where b
   gemm_prefill       the four products of a layer for T tokens (tensor cores, persistent kernel)
   gemm_decode        the same products for B tokens (weights on the 128-row side, split over K)
   attention_decode   B single tokens, each over a context of C cached positions
-  attention_prefill  one prompt of T tokens
+  attention_prefill  one prompt of T tokens, with the mma.sync kernel and with the tcgen05 kernel
   decode_step        R whole decode steps of B requests at context C through the step function
   prefill_step       R whole prefills of T tokens through the step function
 Each case prints the time per launch measured with CUDA events. Under a profiler, give --repeat a
@@ -94,11 +94,16 @@ def attention_prefill_case(tokens, repeat, dev, kernels):
     pos = torch.arange(tokens, dtype=torch.int32, device=dev)
     q = torch.randn(tokens, H * HD, device=dev).bfloat16()
     out = torch.empty_like(q)
-    per = kernels.attention_prefill_rows(PAGE, HD) // (H // HKV)
-    work = torch.tensor([[t, min(per, tokens - t), 0] for t in reversed(range(0, tokens, per))], dtype=torch.int32, device=dev)
-    _time(f"attention prefill T={tokens}", lambda i: kernels.attention_prefill(q, kc, vc, out, work, pos, tables, H, HKV, HD, PAGE,
-                                                                               HD ** -0.5, None),
-          repeat, flops=2 * tokens * tokens * HD * H)
+    variants = [("mma.sync", kernels.attention_prefill, kernels.attention_prefill_rows(PAGE, HD))]
+    if kernels.attention_prefill_tc_supported(HD, H, HKV, PAGE):
+        variants.append(("tcgen05", kernels.attention_prefill_tc, 128))
+    for name, fn, rows in variants:
+        per = rows // (H // HKV)
+        work = torch.tensor([[t, min(per, tokens - t), 0] for t in reversed(range(0, tokens, per))], dtype=torch.int32,
+                            device=dev)
+        _time(f"attention prefill T={tokens} ({name})",
+              lambda i: fn(q, kc, vc, out, work, pos, tables, H, HKV, HD, PAGE, HD ** -0.5, None),
+              repeat, flops=2 * tokens * tokens * HD * H)
 
 
 def step_case(kind, batch, context, tokens, layers, repeat):

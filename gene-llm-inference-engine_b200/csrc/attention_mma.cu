@@ -408,7 +408,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
-    pdl_prologue();
+    // Everything up to the first tiles' requests runs before the wait on the kernel ahead: the
+    // step's descriptors were copied in before the step's first kernel, and of the cache only the
+    // token's own position is written in this step (the tile that holds it waits, see issue()).
+    pdl_launch_dependents();
+    bool waited = false;
     // (step row, position, request) of every decoded token, once per CTA: the per-item look-ups
     // below would otherwise be chains of dependent global loads on each warp's critical path
     for (int i = threadIdx.x; i < n_rows && i < Cfg::kMetaRows; i += Cfg::kThreads) {
@@ -466,6 +470,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const int s = n_issued % kStages;
         const uint32_t k_tile = stages + s * Cfg::kStageBytes, v_tile = k_tile + Cfg::kTileBytes;
         const int key0 = pi.c0 + ptile * kTile;
+        if (!waited && key0 + kTile > pi.pos) { pdl_wait(); waited = true; }      // the key written in this step
         int my_box_page = 0;                   // lane b: the page of box b of this tile
         {
             const int kb = key0 + (lane < boxes ? lane : 0) * box_rows;
@@ -503,6 +508,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
     p_seek();
     while (pw < total && n_issued < kStages) issue();
+    if (!waited) { pdl_wait(); waited = true; }
 
     // ---- consumer
     DecodeItem ci;
@@ -597,29 +603,69 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
 }
 
-// grid (H, decode requests); one thread per head dim. Chunks are merged in increasing order.
-__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         const int* __restrict__ rows, const int* __restrict__ positions,
-                                         __nv_bfloat16* __restrict__ out, int H, int HD, int max_chunks, int window) {
-    pdl_prologue();
+// grid (H, decode requests), four warps. Warp w sums the chunks first + w, first + w + 4, ... in
+// increasing order, each lane its own head dims, with every load requested before the first is
+// used; the four sums are then added in warp order. The order depends on the row's own chunks only.
+constexpr int kCombineWarps = 4;
+constexpr int kCombineMaxDims = 4;                 // head dims per lane: the head sizes of these kernels end at 128
+
+__global__ void __launch_bounds__(kCombineWarps * 32)
+attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                         const int* __restrict__ rows, const int* __restrict__ positions,
+                         __nv_bfloat16* __restrict__ out, int H, int HD, int max_chunks, int window) {
+    __shared__ float s_acc[kCombineWarps][kCombineMaxDims * 32];
+    __shared__ float s_l[kCombineWarps];
     const int h = blockIdx.x, idx = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = rows[idx];
     const int pos = positions[t];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int first = lo / kChunkKeys, last = pos / kChunkKeys;
+    pdl_prologue();
     const float* ml = part_ml + (static_cast<size_t>(idx) * H + h) * max_chunks * 2;
     const float* po = part_o + (static_cast<size_t>(idx) * H + h) * max_chunks * HD;
     float M = -INFINITY;
-    for (int c = first; c <= last; ++c) M = fmaxf(M, ml[c * 2]);
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float acc = 0.f, L = 0.f;
-        for (int c = first; c <= last; ++c) {
-            const float mc = ml[c * 2];
-            const float f = (mc == -INFINITY) ? 0.f : exp2f(mc - M);
-            acc += po[static_cast<size_t>(c) * HD + d] * f;
-            L += ml[c * 2 + 1] * f;
+    for (int c = first + lane; c <= last; c += 32) M = fmaxf(M, ml[c * 2]);
+    M = warp_max(M);
+    float acc[kCombineMaxDims];
+#pragma unroll
+    for (int i = 0; i < kCombineMaxDims; ++i) acc[i] = 0.f;
+    float L = 0.f;
+    constexpr int kBatch = 8;                       // chunks whose loads are in flight together
+    for (int c0 = first + warp; c0 <= last; c0 += kCombineWarps * kBatch) {
+        float v[kBatch][kCombineMaxDims], mc[kBatch], lc[kBatch];
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+            const int c = c0 + j * kCombineWarps;
+            const bool in = c <= last;
+            mc[j] = in ? ml[c * 2] : -INFINITY;
+            lc[j] = in ? ml[c * 2 + 1] : 0.f;
+#pragma unroll
+            for (int i = 0; i < kCombineMaxDims; ++i) {
+                const int d = lane + 32 * i;
+                v[j][i] = (in && d < HD) ? po[static_cast<size_t>(c) * HD + d] : 0.f;
+            }
         }
-        out[(static_cast<size_t>(t) * H + h) * HD + d] = __float2bfloat16_rn(acc / L);
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+            const float f = (mc[j] == -INFINITY) ? 0.f : exp2f(mc[j] - M);
+            L += lc[j] * f;
+#pragma unroll
+            for (int i = 0; i < kCombineMaxDims; ++i) acc[i] += v[j][i] * f;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kCombineMaxDims; ++i) s_acc[warp][lane + 32 * i] = acc[i];
+    if (lane == 0) s_l[warp] = L;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < kCombineWarps; ++w) total += s_l[w];
+    for (int d = threadIdx.x; d < HD; d += kCombineWarps * 32) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < kCombineWarps; ++w) o += s_acc[w][d];
+        out[(static_cast<size_t>(t) * H + h) * HD + d] = __float2bfloat16_rn(o / total);
     }
 }
 
@@ -933,7 +979,7 @@ static int launch_decode(const void* q, const void* kc, const void* vc, void* ou
         rows, row_req, positions, tables, table_stride, H, Hkv, page_size, scale * kLog2e, window, part_o, part_ml, max_chunks);
     if (check_launch("attention_decode")) return 1;
     dim3 grid2(H, n_rows);
-    launch_kernel((attention_combine_kernel), dim3(grid2), dim3(HD < 32 ? 32 : HD), 0, st, part_o, part_ml, rows, positions,
+    launch_kernel((attention_combine_kernel), dim3(grid2), dim3(kCombineWarps * 32), 0, st, part_o, part_ml, rows, positions,
                                                                    static_cast<__nv_bfloat16*>(out), H, HD, max_chunks, window);
     return check_launch("attention_combine");
 }
@@ -968,7 +1014,7 @@ static int launch_decode_tma(const void* q, const void* kc, const void* vc, void
                   page_size, scale * kLog2e, window, part_o, part_ml, max_chunks, n_chunks, status);
     if (check_launch("attention_decode_tma")) return 1;
     dim3 grid2(H, n_rows);
-    launch_kernel((attention_combine_kernel), dim3(grid2), dim3(HD < 32 ? 32 : HD), 0, st, part_o, part_ml, rows, positions,
+    launch_kernel((attention_combine_kernel), dim3(grid2), dim3(kCombineWarps * 32), 0, st, part_o, part_ml, rows, positions,
                   static_cast<__nv_bfloat16*>(out), H, HD, max_chunks, window);
     return check_launch("attention_combine");
 }
