@@ -11,9 +11,11 @@
 // The 128-row operand "P" and the BLOCK_Q-row operand "Q" can be either matrix: for many tokens P
 // is the activations (C[p, q]); for few tokens the weights take the 128-row side and the tokens
 // become the narrow side (C[q, p]), so that a decode step streams every weight once at full tile
-// efficiency. The split over K (few tokens, narrow weight matrices) writes partial tiles to a
-// workspace; the CTA that arrives last adds them in split order, so results do not depend on
-// the order of arrival.
+// efficiency. The split over K (few tokens, narrow weight matrices) runs the splits of a tile as
+// one thread-block cluster where they fit: splits 1.. write their partial tiles into the shared
+// memory of split 0 (st.shared::cluster) and arrive on its mbarrier, and split 0 adds them in split
+// order. Where a cluster does not fit, partial tiles go to a workspace in global memory and the CTA
+// that arrives last adds them, again in split order; results never depend on the order of arrival.
 //
 // Every wait on an mbarrier is bounded: when a limit is hit the kernel records a code in the
 // status word, stops issuing work, drains its own copies with bounded waits, frees its tensor
@@ -28,7 +30,7 @@ constexpr int kBlockK = 64;                 // 64 bf16 = 128 bytes = one swizzle
 constexpr int kThreads = 192;
 constexpr unsigned long long kWaitCycles = 4000000000ull;   // about two seconds
 
-enum TcError : int { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3, kErrDrain = 4 };
+enum TcError : int { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3, kErrDrain = 4, kErrClusterWait = 6 };
 
 // ------------------------------------------------------------------------------------------ PTX
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -49,6 +51,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// ---- thread-block cluster: shared memory of another CTA, barriers across CTAs
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ void cluster_store_f32(uint32_t remote_addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_mbar_arrive(uint32_t remote_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // Bounded wait: false when the limit is hit or another role has already given up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -112,6 +139,11 @@ struct TcConfig {
     static constexpr int kStages = (BLOCK_Q >= 256) ? 4 : (BLOCK_Q >= 128) ? 6 : 8;
     static constexpr int kTmemCols = BLOCK_Q < 32 ? 32 : BLOCK_Q;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
+    // a cluster's split 0 also holds the partial tiles of the other splits, [split - 1][q][128 rows]
+    static constexpr int kPartialBytes = BLOCK_Q * kBlockP * 4;
+    static constexpr int smem_bytes(int cluster_splits) {
+        return kSmemBytes + (cluster_splits > 1 ? (cluster_splits - 1) * kPartialBytes : 0);
+    }
     // instruction descriptor: D f32 (bits 4..5 = 1), A and B bf16 (bits 7..9, 10..12 = 1), both
     // K-major, N >> 3 at bits 17..22, M >> 4 at bits 24..28
     static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BLOCK_Q >> 3) << 17) |
@@ -131,6 +163,7 @@ struct TcParams {
     int* status;
     int prefetch_p;          // P is a weight matrix no earlier kernel writes: its first tiles may be
                              // fetched before the kernel waits for the kernels it depends on
+    int cluster;             // the splits of a tile are one cluster (dims 1 x 1 x splits): reduce in shared memory
 };
 
 template <int BLOCK_Q>
@@ -170,8 +203,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
-    // bars[0..kStages) full, [kStages..2kStages) empty, [2kStages] accumulator ready
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
+    // bars[0..kStages) full, [kStages..2kStages) empty, [2kStages] accumulator ready,
+    // [2kStages + 1] the other splits' partial tiles have arrived (cluster reduce, split 0)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2);
+    float* partials = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes + 256);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = const_cast<int*>(abort_flag) + 1;
     int* epi_abort = last_flag + 1;
@@ -189,6 +224,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             mbar_init(smem_u32(&bars[kStages + s]), 1);
         }
         mbar_init(smem_u32(&bars[2 * kStages]), 1);
+        mbar_init(smem_u32(&bars[2 * kStages + 1]), p.cluster ? static_cast<uint32_t>(p.splits - 1) * 128u : 1u);
         *abort_flag = 0;
         *last_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -199,6 +235,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (p.cluster) cluster_sync_all();          // split 0's barrier exists before anyone arrives on it
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
@@ -286,8 +323,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         if (warp == 2 && lane == 0) *epi_abort = *abort_flag;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const bool aborted = *epi_abort != 0;
-        if (!aborted) {
-            constexpr int kChunks = (BLOCK_Q + 15) / 16;
+        constexpr int kChunks = (BLOCK_Q + 15) / 16;
+        if (p.cluster) {
+            // Splits 1.. hand their partial tile to split 0 (rank 0 of the cluster) and arrive on
+            // its barrier, even after giving up, so that split 0 never waits for a CTA that is gone;
+            // split 0 waits (bounded) before it leaves, so its memory outlives every write to it.
+            if (split != 0) {
+                if (!aborted) {
+                    const uint32_t remote = cluster_map(smem_u32(partials), 0) +
+                                            static_cast<uint32_t>((split - 1) * BLOCK_Q * kBlockP + row_in_tile) * 4u;
+#pragma unroll 1
+                    for (int c = 0; c < kChunks; ++c) {
+                        uint32_t r[16];
+                        if (have) {
+                            tmem_ld_x16(tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + c * 16, r);
+                            tmem_ld_wait();
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            cluster_store_f32(remote + static_cast<uint32_t>((c * 16 + j) * kBlockP) * 4u, have ? __uint_as_float(r[j]) : 0.f);
+                    }
+                }
+                cluster_mbar_arrive(cluster_map(smem_u32(&bars[2 * kStages + 1]), 0));
+            } else {
+                bool all_here = mbar_try_wait_cluster(smem_u32(&bars[2 * kStages + 1]), 0);
+                const unsigned long long t0 = clock64();
+                while (!all_here) {
+                    all_here = mbar_try_wait_cluster(smem_u32(&bars[2 * kStages + 1]), 0);
+                    if (!all_here && clock64() - t0 > kWaitCycles) { atomicCAS(p.status, 0, kErrClusterWait); break; }
+                }
+                if (all_here && !aborted) {
+#pragma unroll 1
+                    for (int c = 0; c < kChunks; ++c) {
+                        uint32_t r[16];
+                        float v[16];
+                        if (have) {
+                            tmem_ld_x16(tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + c * 16, r);
+                            tmem_ld_wait();
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = have ? __uint_as_float(r[j]) : 0.f;
+                        for (int s = 1; s < p.splits; ++s) {
+                            const float* part = partials + static_cast<size_t>(s - 1) * BLOCK_Q * kBlockP;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] += part[(c * 16 + j) * kBlockP + row_in_tile];
+                        }
+                        store_row_chunk<BLOCK_Q>(p, row_p, tile_q * BLOCK_Q + c * 16, v);
+                    }
+                }
+            }
+        } else if (!aborted) {
             if (p.splits == 1) {
 #pragma unroll 1
                 for (int c = 0; c < kChunks; ++c) {
@@ -665,18 +750,74 @@ static int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, const
     return check_launch("gemm_tc_persistent");
 }
 
+static int g_cluster_reduce = 1;
+constexpr int kMaxSmemPerBlock = 232448;       // 227 KB
+constexpr int kMaxClusterSplits = 8;           // the portable cluster size
+
+// How many clusters of `splits` CTAs of this kernel the device holds at once (0: none, or the
+// partial tiles do not fit into shared memory). Asked once per size.
 template <int BLOCK_Q>
-static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParams& p, dim3 grid, cudaStream_t st) {
+static int cluster_capacity(int splits) {
+    using Cfg = TcConfig<BLOCK_Q>;
+    static int cached[kMaxClusterSplits + 1] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
+    if (splits < 2 || splits > kMaxClusterSplits || Cfg::smem_bytes(splits) > kMaxSmemPerBlock) return 0;
+    if (cached[splits] >= 0) return cached[splits];
+    int n = 0;
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BLOCK_Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemPerBlock) == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, 1, splits);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = Cfg::smem_bytes(splits);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = splits;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BLOCK_Q>, &cfg) != cudaSuccess) n = 0;
+    }
+    cudaGetLastError();
+    cached[splits] = n;
+    return n;
+}
+
+template <int BLOCK_Q>
+static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, TcParams p, dim3 grid, cudaStream_t st) {
     using Cfg = TcConfig<BLOCK_Q>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BLOCK_Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-        if (e != cudaSuccess) { set_error("gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::kSmemBytes, cudaGetErrorString(e)); return 1; }
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BLOCK_Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemPerBlock);
+        if (e != cudaSuccess) { set_error("gemm_tc: cannot reserve %d bytes of shared memory: %s", kMaxSmemPerBlock, cudaGetErrorString(e)); return 1; }
         configured = true;
     }
-    launch_kernel((gemm_tc_kernel<BLOCK_Q>), dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, mp, mq, p);
+    // all clusters of the launch resident at once, or the workspace path: a second wave of clusters
+    // would cost more than the reduce through global memory
+    const long long tiles = static_cast<long long>(grid.x) * grid.y;
+    p.cluster = (p.splits > 1 && g_cluster_reduce && tiles <= cluster_capacity<BLOCK_Q>(p.splits)) ? 1 : 0;
+    if (!p.cluster) {
+        launch_kernel((gemm_tc_kernel<BLOCK_Q>), dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, mp, mq, p);
+        return check_launch("gemm_tc");
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = Cfg::smem_bytes(p.splits);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = g_pdl_enabled ? 1 : 0;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = p.splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BLOCK_Q>, mp, mq, p);
+    if (e != cudaSuccess) { set_error("gemm_tc: cluster launch failed: %s", cudaGetErrorString(e)); return 1; }
     return check_launch("gemm_tc");
 }
+
 
 }  // namespace gi
 
@@ -688,6 +829,25 @@ using namespace gi;
 //   swap = 1: weights on the 128-row side, block_q >= tokens on the narrow side.
 //   splits > 1 (swap only): K is cut into `splits` ranges; workspace must hold
 //   tiles * splits * 128 * block_q floats and counters one zeroed word per tile.
+// Switches the cluster reduce of split products on or off (on by default); returns the old value.
+extern "C" int gi_gemm_tc_set_cluster(int on) {
+    const int old = g_cluster_reduce;
+    g_cluster_reduce = on ? 1 : 0;
+    return old;
+}
+
+// Clusters of `splits` CTAs the device holds at once for the kernel of this block_q (0: the
+// workspace path is used).
+extern "C" int gi_gemm_tc_cluster_capacity(int block_q, int splits) {
+    switch (block_q) {
+        case 16: return cluster_capacity<16>(splits);
+        case 32: return cluster_capacity<32>(splits);
+        case 64: return cluster_capacity<64>(splits);
+        case 128: return cluster_capacity<128>(splits);
+        default: return 0;
+    }
+}
+
 extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int accumulate, int M, int N, int K,
                           long long lda, long long ldw, long long ldc, int swap, int block_q, int splits,
                           void* workspace, long long workspace_floats, void* counters, int n_counters, void* status,

@@ -279,6 +279,24 @@ def gemm_tc_plan(M: int, N: int, K: int):
     return False, (256 if N >= 256 else 128 if N > 64 else 64), 1
 
 
+_cluster_splits_cache = {}
+
+
+def gemm_tc_cluster_splits(block_q: int, tiles: int, splits: int) -> int:
+    """The split count to run: the planned one, or up to two fewer if only then all the launch's
+    clusters (one per tile, a CTA per split) are resident at once, which lets the splits be added up
+    in shared memory instead of through global memory. A property of the device, asked once."""
+    key = (block_q, tiles, splits)
+    if key not in _cluster_splits_cache:
+        chosen = splits
+        for s in range(splits, max(1, splits - 3), -1):
+            if s >= 2 and lib().gi_gemm_tc_cluster_capacity(block_q, s) >= tiles:
+                chosen = s
+                break
+        _cluster_splits_cache[key] = chosen
+    return _cluster_splits_cache[key]
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, plan=None) -> None:
     """out[M,N] (+)= a[M,K] @ w[N,K]^T on the tensor cores: bfloat16 operands, 32-bit accumulation,
     output 32-bit (optionally accumulated into) or bfloat16. K must be a multiple of 8."""
@@ -287,6 +305,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     if w.shape[1] != K or out.shape != (M, N):
         raise KernelError(f"gemm: shapes do not agree (a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)})")
     swap, block_q, splits = plan or gemm_tc_plan(M, N, K)
+    if plan is None and splits > 1:
+        splits = gemm_tc_cluster_splits(block_q, (N + 127) // 128, splits)
     st = _tc_state(a.device)
     if not swap and out.dtype is torch.float32 and N % 4 == 0 and block_q >= 128:
         # many tokens, 32-bit output: the persistent kernel (epilogue overlapped, TMA stores)
