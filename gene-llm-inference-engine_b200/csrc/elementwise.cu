@@ -135,10 +135,20 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, TOut* __restrict__ o
 }
 
 // ---------------------------------------------------------------------------------- RoPE + store
+__device__ __forceinline__ void store4(float* dst, const float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, const float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = raw;
+}
+
 // One block per token. Query heads are rotated and written to q_out; key heads are rotated and
 // written to the token's cache row; value heads are copied there. cos/sin are rows of a table
 // [max_position, rot_half] built on the host in double precision. A thread rotates one pair
-// (both members read once); dims beyond the rotary size and the values are copied.
+// (both members read once), or four pairs with 16-byte accesses where the sizes allow; dims beyond
+// the rotary size and the values are copied.
 template <typename TQ, typename TKV>
 __global__ void __launch_bounds__(256)
 rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positions,
@@ -162,8 +172,45 @@ rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positio
     }
     const int n_heads = H + (write_kv ? Hkv : 0);
     TQ* q_row = q_out + static_cast<size_t>(t) * H * hd;
+    if (!interleaved && half % 4 == 0 && hd % 4 == 0) {
+        // four pairs (k..k+3, k+half..k+half+3) per thread: 16-byte loads, 8- or 16-byte stores
+        const int groups = half / 4;
+        for (int e = threadIdx.x; e < n_heads * groups; e += blockDim.x) {
+            const int head = e / groups, k = (e - head * groups) * 4;
+            const float* v = row + static_cast<size_t>(head) * hd;
+            const float4 a = *reinterpret_cast<const float4*>(v + k), b = *reinterpret_cast<const float4*>(v + k + half);
+            const float4 ck = *reinterpret_cast<const float4*>(c + k), sk = *reinterpret_cast<const float4*>(s + k);
+            const float4 oa = make_float4(a.x * ck.x - b.x * sk.x, a.y * ck.y - b.y * sk.y, a.z * ck.z - b.z * sk.z, a.w * ck.w - b.w * sk.w);
+            const float4 ob = make_float4(a.x * sk.x + b.x * ck.x, a.y * sk.y + b.y * ck.y, a.z * sk.z + b.z * ck.z, a.w * sk.w + b.w * ck.w);
+            if (head < H) {
+                store4(q_row + head * hd + k, oa);
+                store4(q_row + head * hd + k + half, ob);
+            } else {
+                TKV* kr = k_cache + kv_base + static_cast<size_t>(head - H) * page_size * hd;
+                store4(kr + k, oa);
+                store4(kr + k + half, ob);
+            }
+        }
+        const int rest4 = (hd - rot_dim) / 4;                 // dims that are not rotated
+        for (int e = threadIdx.x; e < n_heads * rest4; e += blockDim.x) {
+            const int head = e / rest4, d = rot_dim + (e - head * rest4) * 4;
+            const float4 v = *reinterpret_cast<const float4*>(row + static_cast<size_t>(head) * hd + d);
+            if (head < H) store4(q_row + head * hd + d, v);
+            else store4(k_cache + kv_base + static_cast<size_t>(head - H) * page_size * hd + d, v);
+        }
+        if (write_kv) {
+            const float* vrow = row + static_cast<size_t>(H + Hkv) * hd;
+            const int per_head = hd / 4;
+            for (int e = threadIdx.x; e < Hkv * per_head; e += blockDim.x) {
+                const int g = e / per_head, d = (e - g * per_head) * 4;
+                store4(v_cache + kv_base + static_cast<size_t>(g) * page_size * hd + d,
+                       *reinterpret_cast<const float4*>(vrow + static_cast<size_t>(g) * hd + d));
+            }
+        }
+        return;
+    }
     // rotated pairs
-    for (int e = threadIdx.x; e < n_heads * half; e += 256) {
+    for (int e = threadIdx.x; e < n_heads * half; e += blockDim.x) {
         const int head = e / half, k = e - head * half;
         const float* v = row + static_cast<size_t>(head) * hd;
         const int ia = interleaved ? 2 * k : k, ib = interleaved ? 2 * k + 1 : k + half;
@@ -180,7 +227,7 @@ rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positio
     }
     // dims that are not rotated
     const int rest = hd - rot_dim;
-    for (int e = threadIdx.x; e < n_heads * rest; e += 256) {
+    for (int e = threadIdx.x; e < n_heads * rest; e += blockDim.x) {
         const int head = e / rest, d = rot_dim + (e - head * rest);
         const float v = row[static_cast<size_t>(head) * hd + d];
         if (head < H) q_row[head * hd + d] = from_float<TQ>(v);
@@ -188,7 +235,7 @@ rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positio
     }
     if (write_kv) {
         const float* vrow = row + static_cast<size_t>(H + Hkv) * hd;
-        for (int e = threadIdx.x; e < Hkv * hd; e += 256) {
+        for (int e = threadIdx.x; e < Hkv * hd; e += blockDim.x) {
             const int g = e / hd, d = e - g * hd;
             v_cache[kv_base + static_cast<size_t>(g) * page_size * hd + d] = from_float<TKV>(vrow[e]);
         }
@@ -274,13 +321,16 @@ int gi_rope_store(const float* qkv, const int* positions, const int* row_req, co
     GI_REQUIRE(T > 0 && H > 0 && Hkv > 0 && hd > 0 && page_size > 0, "rope_store: sizes must be positive");
     GI_REQUIRE(2 * rot_half <= hd, "rope_store: rotary size %d exceeds the head size %d", 2 * rot_half, hd);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // a thread handles four pairs where it can: a quarter of the threads do for a token
+    const bool vec = !interleaved && rot_half % 4 == 0 && hd % 4 == 0 && cos_t != nullptr;
+    const int threads = vec ? 128 : 256;
     if (dtype == kF32) {
-        launch_kernel((rope_store_kernel<float, float>), dim3(T), dim3(256), 0, st, 
+        launch_kernel((rope_store_kernel<float, float>), dim3(T), dim3(threads), 0, st, 
             qkv, positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved,
             static_cast<float*>(q_out), static_cast<float*>(k_cache), static_cast<float*>(v_cache), H, Hkv, hd,
             page_size, write_kv);
     } else if (dtype == kBF16) {
-        launch_kernel((rope_store_kernel<__nv_bfloat16, __nv_bfloat16>), dim3(T), dim3(256), 0, st, 
+        launch_kernel((rope_store_kernel<__nv_bfloat16, __nv_bfloat16>), dim3(T), dim3(threads), 0, st, 
             qkv, positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved,
             static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
             static_cast<__nv_bfloat16*>(v_cache), H, Hkv, hd, page_size, write_kv);
