@@ -28,10 +28,12 @@ void set_error(const char* fmt, ...) {
 // ---------------------------------------------------------------------------------- embedding
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ out, int D, float scale) {
+                             const int* __restrict__ feedback, float* __restrict__ out, int D, float scale) {
     pdl_prologue();
     const int t = blockIdx.x;
-    const TW* row = table + static_cast<size_t>(tokens[t]) * D;
+    int tok = tokens[t];
+    if (tok < 0) tok = feedback[-tok - 1];      // the token a sampling kernel left on the device
+    const TW* row = table + static_cast<size_t>(tok) * D;
     float* o = out + static_cast<size_t>(t) * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) o[d] = to_float(row[d]) * scale;
 }
@@ -266,15 +268,17 @@ int gi_set_pdl(int enabled) {
     return 0;
 }
 
-int gi_embed(const void* table, int table_dtype, const int* tokens, float* out, int T, int D, float scale,
-             void* stream) {
+// tokens[t] >= 0 is a token id; tokens[t] = -(k + 1) takes the id from feedback[k] (device memory
+// that an earlier sampling kernel wrote; may be null when no entry is negative).
+int gi_embed(const void* table, int table_dtype, const int* tokens, const int* feedback, float* out, int T, int D,
+             float scale, void* stream) {
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && D > 0, "embed: T and D must be positive (T=%d, D=%d)", T, D);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (table_dtype == kF32) {
-        launch_kernel((embed_kernel<float>), dim3(T), dim3(256), 0, st, static_cast<const float*>(table), tokens, out, D, scale);
+        launch_kernel((embed_kernel<float>), dim3(T), dim3(256), 0, st, static_cast<const float*>(table), tokens, feedback, out, D, scale);
     } else if (table_dtype == kBF16) {
-        launch_kernel((embed_kernel<__nv_bfloat16>), dim3(T), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(table), tokens, out, D, scale);
+        launch_kernel((embed_kernel<__nv_bfloat16>), dim3(T), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(table), tokens, feedback, out, D, scale);
     } else {
         GI_REQUIRE(false, "embed: unsupported table dtype code %d", table_dtype);
     }

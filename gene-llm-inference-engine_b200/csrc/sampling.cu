@@ -204,6 +204,7 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ probs_all, i
     const float* row = logits + static_cast<size_t>(r) * V;
     float* probs = probs_all + static_cast<size_t>(r) * V;
     const float temp = temperature[r];
+    if (!(temp > 0.f)) return;          // a greedy row: out[r] keeps what the caller put there (its argmax)
 
     // max
     float mx = -INFINITY;
@@ -369,7 +370,8 @@ extern "C" int gi_argmax(const float* logits, int rows, int V, int* out, float* 
     return check_launch("argmax");
 }
 
-// probs_scratch: [rows, V] floats owned by the caller. temperature[r] must be > 0.
+// probs_scratch: [rows, V] floats owned by the caller. Rows with temperature[r] <= 0 are skipped:
+// out[r] is left as it is (the caller writes the row's argmax there first).
 extern "C" int gi_sample(const float* logits, float* probs_scratch, int rows, int V, const float* temperature,
                          const int* top_k, const float* top_p, const float* uniform, int* out, void* stream) {
     if (rows == 0) return 0;

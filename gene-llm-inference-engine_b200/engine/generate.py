@@ -45,9 +45,10 @@ class Engine:
         step_tokens = max(1, min(step_tokens, max_running * context))
         self.steps = StepEngine(self.model, page_size=page_size, n_pages=kv_pages, max_requests=max_running,
                                 max_step_tokens=step_tokens, max_logit_rows=max_running)
-        self.sampler = DeviceSampler(self.model.vocab_size, self.model.device)
+        self.sampler = DeviceSampler(self.model.vocab_size, self.model.device, ids=self.steps.feedback)
         self.scheduler = Scheduler(self.steps, self.sampler.sample,
-                                   SchedulerConfig(max_running, step_tokens, prefill_chunk, prefix_cache))
+                                   SchedulerConfig(max_running, step_tokens, prefill_chunk, prefix_cache),
+                                   sample_async=self.sampler.sample_async)
 
     # ------------------------------------------------------------------ the reference's Engine interface
     def submit(self, prompt: Sequence[int], max_positions: int = 0, sampling: Optional[SamplingParams] = None,

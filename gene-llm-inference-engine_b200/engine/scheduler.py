@@ -19,6 +19,16 @@ Policy of the reference engine (src/runtime/engine.cpp:64-208):
 
 The scheduler drives any backend with ``cache`` (a CacheManager), ``open``, ``close``, ``step`` and
 ``model`` (``max_position``, ``vocab_size``); tests run it on the CPU with a counting backend.
+
+One step ahead. With a backend whose steps can take a token from the device (``token_feedback``)
+and a sampler that answers later (``sample_async``), a step of plain decoding is launched before
+the ids of the step before it have reached the host: each request's next token is named by its
+place in the sampler's output. The host then reads the earlier step's ids while the device already
+runs the next one. What a step computes is the same; only a request that ends on a stop token has
+taken part in one step too many, whose row is dropped (its pages go back with the rest). A step is
+launched ahead only when the set of running requests cannot change in between: nothing waits for
+a free place, every running request has just fed its last known token, none reaches its position
+limit, and the pages are free without eviction.
 """
 from __future__ import annotations
 
@@ -90,12 +100,28 @@ class _Job:
         self.result = RequestResult(jid, list(request.prompt))
 
 
+class _InFlight:
+    """A step that has been launched: who took part, and the ids on their way to the host."""
+
+    def __init__(self, number: int, jobs: List[_Job], takes: List[int], owners: List[_Job], pending):
+        self.number = number         # the step's count (stats.steps when it was launched)
+        self.jobs = jobs             # requests that fed tokens, in step order
+        self.takes = takes           # tokens each fed
+        self.owners = owners         # the requests whose last row asked for logits, in row order
+        self.pending = pending       # None, a list of ids, or an object with result()
+
+
 class Scheduler:
-    def __init__(self, backend, sample_rows: Callable, config: Optional[SchedulerConfig] = None):
+    def __init__(self, backend, sample_rows: Callable, config: Optional[SchedulerConfig] = None,
+                 sample_async: Optional[Callable] = None):
         """``sample_rows(logits, params, uniforms) -> token ids`` turns the wanted logits rows of a
-        step into one token each."""
+        step into one token each; ``sample_async`` does the same but returns an object whose
+        ``result()`` gives the ids later (it lets a step be launched ahead)."""
         self.backend = backend
         self.sample_rows = sample_rows
+        self.sample_async = sample_async
+        self.lookahead = sample_async is not None and getattr(backend, "token_feedback", False)
+        self._ahead: Optional[_InFlight] = None
         self.cfg = config or SchedulerConfig()
         if self.cfg.max_running < 1:
             raise ValueError("Scheduler: max_running must be >= 1")
@@ -133,7 +159,7 @@ class Scheduler:
         return self.jobs[jid].result
 
     def idle(self) -> bool:
-        return not self.waiting and not self.running
+        return not self.waiting and not self.running and self._ahead is None
 
     # ------------------------------------------------------------------ life of a request
     def _admit(self) -> None:
@@ -163,10 +189,10 @@ class Scheduler:
         self.prefix.insert(job.tokens, job.fed, job.cache.tables[0][:job.cache.n_pages[0]])
         job.cached_upto = job.fed
 
-    def _finish(self, job: _Job, error: str = "") -> None:
+    def _finish(self, job: _Job, error: str = "", step: int = -1) -> None:
         job.result.finished = True
         job.result.error = error
-        job.result.last_step = self.stats.steps
+        job.result.last_step = self.stats.steps if step < 0 else step
         self.backend.close(("job", job.id))
         job.cache = None
         self.running.remove(job)
@@ -207,10 +233,23 @@ class Scheduler:
         return takes, needed
 
     def step(self) -> bool:
-        """Runs one step of the model. False (and nothing done) when no request waits or runs."""
+        """Completes one step of the model. False (and nothing done) when no request waits or runs."""
+        cur = self._ahead
+        self._ahead = None
+        if cur is None:
+            cur = self._launch()
+            if cur is None:
+                return False
+        if cur.jobs and self.lookahead:
+            self._ahead = self._launch_ahead(cur)
+        self._complete(cur)
+        return True
+
+    def _launch(self) -> Optional[_InFlight]:
+        """Plans and launches a step from what the host knows. None when nothing waits or runs."""
         self._admit()
         if not self.running:
-            return False
+            return None
         cache = self.backend.cache
         while True:
             takes, needed = self.plan()
@@ -218,40 +257,66 @@ class Scheduler:
                 break
             if len(self.running) == 1:
                 self._finish(self.running[0], "the KV pool is too small for this request")
-                return True
+                return _InFlight(self.stats.steps, [], [], [], None)
             self._preempt_youngest()
         if self.prefix is not None and needed > cache.free_pages():
             self.stats.evicted_pages += self.prefix.evict(needed - cache.free_pages())
 
-        entries, owners = [], []
+        entries, owners, jobs, fed_takes = [], [], [], []
         for job, take in zip(self.running, takes):
             if take == 0:
                 continue
             last = job.fed + take == len(job.tokens)
             entries.append(StepEntry(("job", job.id), job.tokens[job.fed:job.fed + take], [take - 1] if last else []))
+            jobs.append(job)
+            fed_takes.append(take)
             if last:
                 owners.append(job)
+        return self._run(entries, jobs, fed_takes, owners)
+
+    def _run(self, entries, jobs, takes, owners) -> _InFlight:
         logits = self.backend.step(entries)
         self.stats.steps += 1
         n_tokens = sum(takes)
         self.stats.tokens += n_tokens
         self.stats.max_tokens_in_step = max(self.stats.max_tokens_in_step, n_tokens)
         self.stats.max_chunk = max(self.stats.max_chunk, max(takes))
-
-        sampled: Dict[int, int] = {}
+        pending = None
         if owners:
             params = [j.request.sampling for j in owners]
             uniforms = [0.0 if p.greedy else j.stream.next_uniform() for j, p in zip(owners, params)]
-            ids = self.sample_rows(logits, params, uniforms)
-            sampled = {j.id: int(t) for j, t in zip(owners, ids)}
+            pending = (self.sample_async or self.sample_rows)(logits, params, uniforms)
             self.stats.logits_rows += len(owners)
+        return _InFlight(self.stats.steps, jobs, takes, owners, pending)
 
+    def _launch_ahead(self, cur: _InFlight) -> Optional[_InFlight]:
+        """Launches the step after ``cur`` from the ids ``cur`` leaves on the device, if nothing the
+        host does not know yet can change who runs in it."""
+        if self.waiting or len(cur.owners) != len(self.running) or len(cur.owners) != len(cur.jobs):
+            return None                                   # a request could be admitted, or some still feed their prompt
+        cache = self.backend.cache
+        needed = 0
+        for job, take in zip(cur.jobs, cur.takes):
+            if job.fed + take + 1 > job.limit:
+                return None                               # it ends with this step: the set of requests changes
+            needed += cache.pages_needed(job.cache, 1)
+        if needed > cache.free_pages():
+            return None                                   # eviction or preemption: decided with all ids known
+        entries = [StepEntry(("job", job.id), [-(k + 1)], [0]) for k, job in enumerate(cur.owners)]
+        return self._run(entries, list(cur.owners), [1] * len(entries), list(cur.owners))
+
+    def _complete(self, cur: _InFlight) -> None:
+        """Takes a launched step's ids and does the bookkeeping that follows them."""
+        sampled: Dict[int, int] = {}
+        if cur.owners:
+            ids = cur.pending.result() if hasattr(cur.pending, "result") else cur.pending
+            sampled = {j.id: int(t) for j, t in zip(cur.owners, ids)}
         done = []
-        for job, take in zip(list(self.running), takes):
-            if take == 0:
-                continue
+        for job, take in zip(cur.jobs, cur.takes):
+            if job.result.finished:
+                continue                                  # it ended on a stop token one step earlier: this row is dropped
             if job.result.first_step < 0:
-                job.result.first_step = self.stats.steps
+                job.result.first_step = cur.number
             job.fed += take
             self._index_new_pages(job)
             if job.id in sampled:
@@ -259,7 +324,7 @@ class Scheduler:
                 job.result.generated_tokens.append(nxt)
                 job.tokens.append(nxt)
                 if job.result.first_token_step < 0:
-                    job.result.first_token_step = self.stats.steps
+                    job.result.first_token_step = cur.number
                 if job.request.on_token:
                     job.request.on_token(nxt)
                 if nxt in job.request.stop_ids:
@@ -269,8 +334,7 @@ class Scheduler:
             if job.fed >= job.limit:
                 done.append(job)
         for job in done:
-            self._finish(job)
-        return True
+            self._finish(job, step=cur.number)
 
     def run_until_idle(self) -> None:
         while self.step():

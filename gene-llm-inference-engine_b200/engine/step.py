@@ -24,7 +24,9 @@ _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": 
 
 @dataclass
 class StepEntry:
-    """The next tokens of one request and the places among them whose logits are wanted."""
+    """The next tokens of one request and the places among them whose logits are wanted. A token
+    given as -(k + 1) is taken on the device from place k of the engine's ``feedback`` buffer, where
+    a sampler left the id it drew from the step before (the host need not know it yet)."""
     key: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=list)
@@ -55,6 +57,7 @@ class StepContext:
         self.max_requests = engine.max_requests
         self.compute_dtype = engine.model.dtype
         self.tokens = views["tokens"]
+        self.feedback = engine.feedback          # sampled ids of the step before, for tokens given as -(k + 1)
         self.positions = views["positions"]
         self.row_req = views["row_req"]
         self.logit_rows = views["logit_rows"]
@@ -116,6 +119,8 @@ class StepContext:
 
 
 class StepEngine:
+    token_feedback = True        # entries may name tokens by their place in ``feedback``
+
     def __init__(self, model: DecoderModel, page_size: int = 16, n_pages: int = 256, max_requests: int = 8,
                  max_step_tokens: int = 2048, max_logit_rows: Optional[int] = None, use_graphs: bool = True):
         if not torch.cuda.is_available():
@@ -127,6 +132,8 @@ class StepEngine:
         self.max_requests = max_requests
         self.max_step_tokens = max_step_tokens
         self.max_logit_rows = max_logit_rows or max_step_tokens
+        # sampled token ids stay here on the device, so that the next step can start from them
+        self.feedback = torch.zeros(self.max_logit_rows, dtype=torch.int32, device=model.device)
         needs = model.cache_needs()
         state_needs = model.state_needs()
         self.cache = CacheManager(needs, page_size, n_pages, model.max_position, max_requests,
@@ -253,7 +260,7 @@ class StepEngine:
                 raise KeyError(f"request {e.key!r} is not open")
             n = len(e.tokens)
             for tok in e.tokens:
-                if not (0 <= int(tok) < V):
+                if not (0 <= int(tok) < V) and not (-self.max_logit_rows <= int(tok) < 0):
                     raise IndexError(f"token id {tok} is outside the vocabulary of {V}")
             for w in e.want:
                 if not (0 <= int(w) < n):

@@ -57,13 +57,16 @@ def _opt(t: Optional[torch.Tensor], name: str, dtype: torch.dtype) -> int:
     return 0 if t is None else _dev(t, name, dtype)
 
 
-def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
-    """out[t, :] = table[tokens[t], :] * scale, widened to 32-bit."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0,
+          feedback: Optional[torch.Tensor] = None) -> None:
+    """out[t, :] = table[tokens[t], :] * scale, widened to 32-bit. A negative tokens[t] = -(k + 1)
+    stands for feedback[k], a token id that a sampling kernel left on the device."""
     T, D = out.shape
     if table.shape[1] != D or tokens.numel() != T:
         raise KernelError("embed: shapes of table, tokens and out do not agree")
     check(lib().gi_embed(_dev(table, "table"), dtype_code(table.dtype), _dev(tokens, "tokens", torch.int32),
-                         _dev(out, "out", torch.float32), T, D, float(scale), _stream()), "embed")
+                         _opt(feedback, "feedback", torch.int32), _dev(out, "out", torch.float32), T, D, float(scale),
+                         _stream()), "embed")
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,

@@ -19,7 +19,7 @@ class KernelError(RuntimeError):
 
 
 _SIGNATURES = {
-    "gi_embed": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+    "gi_embed": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
     "gi_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "gi_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "gi_rope_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,

@@ -111,7 +111,7 @@ class DecoderModel:
         [wanted rows, vocab] (None when no row wants logits)."""
         T = ctx.n_tokens
         x = ctx.scratch("residual", (T, self.hidden_size), torch.float32)
-        kernels.embed(self.embedding, ctx.tokens, x, self.embedding_scale)
+        kernels.embed(self.embedding, ctx.tokens, x, self.embedding_scale, ctx.feedback)
         for run in self.runs:
             self.layers[run.layer].forward(ctx, run, x)
         k = ctx.n_logit_rows

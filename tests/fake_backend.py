@@ -79,6 +79,42 @@ class FakeBackend:
         return out
 
 
+class FakeFeedbackBackend(FakeBackend):
+    """The same, for steps launched ahead: a token given as -(k + 1) is place k of ``feedback``,
+    where the sampler below leaves its ids at once, as a sampling kernel does on the device."""
+    token_feedback = True
+
+    def __init__(self, *args, **kw):
+        super().__init__(*args, **kw)
+        self.feedback = []
+        self.ahead_steps = 0
+
+    def step(self, entries):
+        from geneinfer_b200.engine.step import StepEntry
+        if any(int(t) < 0 for e in entries for t in e.tokens):
+            self.ahead_steps += 1
+        resolved = [StepEntry(e.key, [self.feedback[-int(t) - 1] if int(t) < 0 else t for t in e.tokens], e.want)
+                    for e in entries]
+        return super().step(resolved)
+
+
+class _Later:
+    def __init__(self, ids):
+        self._ids = ids
+
+    def result(self):
+        return self._ids
+
+
+def sample_async(backend, vocab):
+    """The ids are on the "device" (backend.feedback) at once; the host gets them on result()."""
+    def fn(logits, params, uniforms):
+        ids = [pick_token(h, p, u, vocab) for h, p, u in zip(logits, params, uniforms)]
+        backend.feedback = list(ids)
+        return _Later(ids)
+    return fn
+
+
 def sample_rows(vocab):
     def fn(logits, params, uniforms):
         return [pick_token(h, p, u, vocab) for h, p, u in zip(logits, params, uniforms)]

@@ -82,6 +82,27 @@ def test_top_k_top_p_and_stop_ids_through_the_engine():
     assert engine.result(rid2).cached_tokens == 0 and engine.cached_blocks() >= 0
 
 
+def test_greedy_and_sampled_requests_in_one_batch_with_steps_launched_ahead():
+    """A greedy and a sampled request decode side by side: the sampling kernel leaves the greedy row's
+    argmax in place, and the ids stay on the device for the step that is launched ahead."""
+    from geneinfer_b200 import Engine, SamplingParams
+    engine = Engine(gf.model_dir("b"), dtype="float32", max_running=2, kv_pages=16, prefix_cache=False)
+    assert engine.scheduler.lookahead
+    p1, p2 = tc.random_tokens(6, 384, 21), tc.random_tokens(11, 384, 22)
+    want1, _ = _plain_continue("b", "float32", p1, 14, pm.PlainSampler(0.0))
+    want2, _ = _plain_continue("b", "float32", p2, 14, pm.PlainSampler(0.9, 0, 1.0, seed=5))
+    launched = []
+    run = engine.scheduler._launch_ahead
+    engine.scheduler._launch_ahead = lambda cur: launched.append(run(cur)) or launched[-1]
+    r1 = engine.submit(p1, len(p1) + 13, SamplingParams(0.0))
+    r2 = engine.submit(p2, len(p2) + 13, SamplingParams(0.9, 0, 1.0, 5))
+    engine.run_until_idle()
+    assert engine.result(r1).generated_tokens == want1
+    assert engine.result(r2).generated_tokens == want2
+    assert sum(x is not None for x in launched) >= 10, "no step was launched ahead"
+    assert engine.steps.cache.free_pages() == 16 and not engine.steps.cache.requests
+
+
 def test_prefix_cache_gives_the_same_tokens():
     from geneinfer_b200 import Engine
     common = tc.random_tokens(40, 256, 9)

@@ -66,6 +66,59 @@ def test_results_equal_running_alone_for_random_requests():
         assert backend.cache.free_pages() == pages and not backend.cache.requests, "pages or requests were lost"
 
 
+def test_steps_launched_ahead_give_the_same_results():
+    """With a backend that takes tokens from the device, decode steps are launched before the ids of
+    the step before are known to the host; stop tokens, limits, arrivals and short pools in between."""
+    rng = np.random.default_rng(1)
+    ahead = 0
+    for trial in range(12):
+        pages = [64, 20, 9][trial % 3]
+        backend = fb.FakeFeedbackBackend(pages, 4, 64, 50, max_requests=8)
+        s = Scheduler(backend, fb.sample_rows(50),
+                      SchedulerConfig(max_running=int(rng.integers(1, 6)), step_tokens=int(rng.integers(4, 24)),
+                                      prefill_chunk=int(rng.integers(0, 9)), prefix_cache=bool(trial % 2)),
+                      sample_async=fb.sample_async(backend, 50))
+        assert s.lookahead
+        reqs = []
+        for _ in range(int(rng.integers(3, 10))):
+            n = int(rng.integers(1, 28))
+            shared = [7, 7, 7, 7, 3, 3, 3, 3, 9] if rng.random() < 0.4 else []
+            prompt = (shared + [int(t) for t in rng.integers(0, 50, n)])[:32]
+            temp = [0.0, 0.8][int(rng.integers(0, 2))]
+            reqs.append(GenerationRequest(prompt, int(rng.integers(1, 36)),
+                                          SamplingParams(temp, 0, 1.0, int(rng.integers(0, 99))),
+                                          stop_ids=(5, 6, 7) if rng.random() < 0.5 else ()))
+        for i, r in enumerate(reqs):
+            s.submit(r)
+            if i % 3 == 2:
+                s.step()
+        s.run_until_idle()
+        assert s.idle()
+        check_against_alone(backend, s, reqs)
+        if s.prefix:
+            s.prefix.clear()
+        backend.cache.check_invariants()
+        assert backend.cache.free_pages() == pages and not backend.cache.requests, "pages or requests were lost"
+        ahead += backend.ahead_steps
+    assert ahead > 20, "no step was launched ahead"
+
+
+def test_a_stop_token_drops_the_row_of_the_step_launched_ahead():
+    backend = fb.FakeFeedbackBackend(32, 4, 64, 50)
+    s = Scheduler(backend, fb.sample_rows(50), SchedulerConfig(max_running=2, prefix_cache=False),
+                  sample_async=fb.sample_async(backend, 50))
+    want, _ = fb.expected_alone([1, 2, 3], 0, SamplingParams(0.0), (), 64, 50)
+    stop = want[4]                                        # ends at its 5th generated token
+    first = want.index(stop)
+    a = s.submit(GenerationRequest([1, 2, 3], 0, SamplingParams(0.0), stop_ids=(stop,)))
+    b = s.submit(GenerationRequest([9, 8, 7, 6], 20, SamplingParams(0.0)))
+    s.run_until_idle()
+    assert s.result(a).generated_tokens == want[:first + 1] and s.result(a).stopped_by_end_token
+    assert s.result(b).generated_tokens == fb.expected_alone([9, 8, 7, 6], 20, SamplingParams(0.0), (), 64, 50)[0]
+    assert backend.ahead_steps > 0
+    assert backend.cache.free_pages() == 32 and not backend.cache.requests
+
+
 def test_pages_run_out_youngest_is_preempted_and_recomputed():
     backend, s = make(10, page_size=4, step_tokens=64, max_running=3, prefix_cache=False)
     reqs = [GenerationRequest([1 + i] * 10, 30, SamplingParams(0.8, 0, 1.0, seed=i)) for i in range(3)]
