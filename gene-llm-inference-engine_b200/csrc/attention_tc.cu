@@ -13,6 +13,8 @@
 // Scores, maxima, sums and the output accumulator are 32-bit; P is rounded to bfloat16 as the
 // operand of P V. Two CTAs fit on an SM, so one CTA's softmax overlaps the other's MMAs.
 // Every mbarrier wait is bounded; on expiry a code goes to the status word and the CTA winds down.
+#include <type_traits>
+
 #include "common.cuh"
 #include "tma.cuh"
 
@@ -300,10 +302,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         // independent of which references were used.
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
-        auto tile_pass = [&](int key0, bool edge, float m_use, float& mx, float& sum) {
+        auto tile_pass = [&](int key0, auto edge_tag, float m_use, float& mx, float& sum) {
             // one pass over the tile's scores: running maximum of the raw scores, weights, their sum,
             // and the weights as bfloat16 into the K-major P tile; loads of the next 32 columns are
-            // in flight while the current ones are processed
+            // in flight while the current ones are processed. The masking of tiles that some row
+            // does not see whole is compiled into a pass of its own.
+            constexpr bool kEdge = decltype(edge_tag)::value;
             uint32_t buf[2][32];
             tmem_ld32(tmem_s + lane_addr, buf[0]);
             tmem_ld_wait();
@@ -315,7 +319,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
                     float v0 = __uint_as_float(sv[j]), v1 = __uint_as_float(sv[j + 1]);
-                    if (edge) {
+                    if (kEdge) {
                         const int key = key0 + c * 32 + j;
                         if (!(key >= row_lo && key <= row_pos)) v0 = -INFINITY;
                         if (!(key + 1 >= row_lo && key + 1 <= row_pos)) v1 = -INFINITY;
@@ -335,6 +339,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 if (c + 1 < kKeys / 32) tmem_ld_wait();
             }
         };
+        auto tile_pass_any = [&](int key0, bool edge, float m_use, float& mx, float& sum) {
+            if (edge) tile_pass(key0, std::true_type{}, m_use, mx, sum);
+            else tile_pass(key0, std::false_type{}, m_use, mx, sum);
+        };
         for (int i = 0; i < n_tiles; ++i) {
             const int key0 = (first_tile + i) * kKeys;
             if (!mbar_wait(smem_u32(&bars[4]), i & 1, abort_flag)) { ok = false; break; }
@@ -344,7 +352,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             tc_fence_after();
             const bool edge = key0 < lo_last || key0 + kKeys - 1 > pos_first;      // some row masks some key of this tile
             float mx = -INFINITY, sum = 0.f;
-            tile_pass(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum);
+            tile_pass_any(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum);
             const float m_tile = mx * scale_log2;
             const bool move = m_tile > m_ref + 8.0f;                     // also true for the first visible key (m_ref = -inf)
             if (__any_sync(0xffffffffu, move)) {
@@ -366,7 +374,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 m_ref = m_new;
                 mx = -INFINITY;
                 sum = 0.f;
-                tile_pass(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum);
+                tile_pass_any(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum);
             }
             l += sum;
             if (key0 < lo_first || key0 + kKeys - 1 > pos_last) {
