@@ -194,7 +194,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         // The whole warp looks up the tile's pages (lane b: box b), one round trip to the block table
-        // per tile, started before the wait for the free stage; lane 0 then issues the boxes.
+        // per tile, started before the wait for the free stage, and each lane requests its own box: one
+        // thread issuing all of a tile's copies in turn was late for the MMAs.
         const int* table = block_tables + static_cast<size_t>(req) * table_stride;
         const int box_rows = page_size < kKeys ? page_size : kKeys;
         const int boxes = kKeys / box_rows;                       // at most 16 (pages of 8)
@@ -217,17 +218,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_expect_tx(bar, static_cast<uint32_t>(__popc(valid_mask)) * 2u * box_rows * HD * 2u);
             }
-            for (int b = 0; b < boxes; ++b) {
-                const int page = __shfl_sync(0xffffffffu, page_lane, b);
-                if (lane == 0 && ((valid_mask >> b) & 1u)) {
-                    const int kb = key0 + b * box_rows;
-                    const int row = (page * Hkv + g) * page_size + kb % page_size;
+            __syncwarp();                                         // the expected bytes are set before any copy can complete
+            if (lane_valid) {                                     // every lane requests its own box
+                const int row = (page_lane * Hkv + g) * page_size + kb_lane % page_size;
 #pragma unroll
-                    for (int h = 0; h < C::kBlocks; ++h) {
-                        const uint32_t off = static_cast<uint32_t>(h * (kKeys * 128) + b * box_rows * 128);
-                        tma_load_2d(k_tile + off, &map_k, h * 64, row, bar);
-                        tma_load_2d(v_tile + off, &map_v, h * 64, row, bar);
-                    }
+                for (int h = 0; h < C::kBlocks; ++h) {
+                    const uint32_t off = static_cast<uint32_t>(h * (kKeys * 128) + lane * box_rows * 128);
+                    tma_load_2d(k_tile + off, &map_k, h * 64, row, bar);
+                    tma_load_2d(v_tile + off, &map_v, h * 64, row, bar);
                 }
             }
         }
@@ -237,12 +235,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             // Q is written by the softmax warps; their first arrival on "p full" (phase 0) also says Q is ready
             bool ok = mbar_wait(smem_u32(&bars[5]), 0, abort_flag);
             if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, 9); }
-            for (int i = 0; i < n_tiles && ok; ++i) {
+            // S(i + 1) goes to the tensor cores before P(i) V(i): the softmax warps have read S(i) by the
+            // time P(i) is full, so they can start on the next tile while O is still being updated.
+            auto issue_s = [&](int i) -> bool {
                 const int s = i % kStages;
-                if (!mbar_wait(smem_u32(&bars[s]), (i / kStages) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&bars[s]), (i / kStages) & 1, abort_flag)) return false;
                 tc_fence_after();
-                const uint32_t k_tile = smem_u32(kv_smem + s * 2 * C::kTileBytes), v_tile = k_tile + C::kTileBytes;
-                // S = Q K^T
+                const uint32_t k_tile = smem_u32(kv_smem + s * 2 * C::kTileBytes);
 #pragma unroll
                 for (int kb = 0; kb < C::kBlocks; ++kb) {
                     const uint64_t dq = desc_k_major(smem_u32(q_smem) + kb * (kRows * 128));
@@ -251,9 +250,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                     for (int k = 0; k < 4; ++k) umma(tmem_s, dq + 2 * k, dk + 2 * k, C::kIdescS, (kb > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&bars[4]));
-                // wait for P (and the rescaled O), then O += P V
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int i = 0; i < n_tiles && ok; ++i) {
+                const int s = i % kStages;
+                // wait for P(i) (and the rescaled O)
                 if (!mbar_wait(smem_u32(&bars[5]), (i + 1) & 1, abort_flag)) { ok = false; break; }
+                if (i + 1 < n_tiles && !issue_s(i + 1)) { ok = false; break; }
                 tc_fence_after();
+                const uint32_t v_tile = smem_u32(kv_smem + s * 2 * C::kTileBytes) + C::kTileBytes;
 #pragma unroll
                 for (int kb = 0; kb < kKeys / 64; ++kb) {
                     const uint64_t dp = desc_k_major(smem_u32(p_smem) + kb * (kRows * 128));
@@ -302,7 +308,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         // independent of which references were used.
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
-        auto tile_pass = [&](int key0, auto edge_tag, float m_use, float& mx, float& sum) {
+        auto tile_pass = [&](int key0, auto edge_tag, float m_use, float& mx, float& sum, int p_free_parity) {
             // one pass over the tile's scores: running maximum of the raw scores, weights, their sum,
             // and the weights as bfloat16 into the K-major P tile; loads of the next 32 columns are
             // in flight while the current ones are processed. The masking of tiles that some row
@@ -330,6 +336,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                     __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
                     packed[j >> 1] = *reinterpret_cast<uint32_t*>(&pb);
                 }
+                if (c == 0 && p_free_parity >= 0) {
+                    // P of the tile before is still being read by its MMAs (they were issued after this
+                    // tile's S): the first store waits for them; O may be touched from here on, too
+                    if (!mbar_wait(smem_u32(&bars[6]), static_cast<uint32_t>(p_free_parity), abort_flag)) ok = false;
+                    tc_fence_after();
+                }
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
                     const int chunk = (c & 1) * 4 + q4;                 // 16-byte chunk inside the 64-key block c / 2
@@ -339,20 +351,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 if (c + 1 < kKeys / 32) tmem_ld_wait();
             }
         };
-        auto tile_pass_any = [&](int key0, bool edge, float m_use, float& mx, float& sum) {
-            if (edge) tile_pass(key0, std::true_type{}, m_use, mx, sum);
-            else tile_pass(key0, std::false_type{}, m_use, mx, sum);
+        auto tile_pass_any = [&](int key0, bool edge, float m_use, float& mx, float& sum, int p_free_parity) {
+            if (edge) tile_pass(key0, std::true_type{}, m_use, mx, sum, p_free_parity);
+            else tile_pass(key0, std::false_type{}, m_use, mx, sum, p_free_parity);
         };
         for (int i = 0; i < n_tiles; ++i) {
             const int key0 = (first_tile + i) * kKeys;
             if (!mbar_wait(smem_u32(&bars[4]), i & 1, abort_flag)) { ok = false; break; }
-            // P of the previous tile must have been consumed; its MMAs were issued before this tile's
-            // S MMAs, so this wait returns at once
-            if (i > 0 && !mbar_wait(smem_u32(&bars[6]), (i - 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const bool edge = key0 < lo_last || key0 + kKeys - 1 > pos_first;      // some row masks some key of this tile
             float mx = -INFINITY, sum = 0.f;
-            tile_pass_any(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum);
+            tile_pass_any(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum, i > 0 ? ((i - 1) & 1) : -1);
+            if (!ok) break;
             const float m_tile = mx * scale_log2;
             const bool move = m_tile > m_ref + 8.0f;                     // also true for the first visible key (m_ref = -inf)
             if (__any_sync(0xffffffffu, move)) {
@@ -374,7 +384,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 m_ref = m_new;
                 mx = -INFINITY;
                 sum = 0.f;
-                tile_pass_any(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum);
+                tile_pass_any(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum, -1);
             }
             l += sum;
             if (key0 < lo_first || key0 + kKeys - 1 > pos_last) {
