@@ -471,35 +471,25 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const uint32_t k_tile = stages + s * Cfg::kStageBytes, v_tile = k_tile + Cfg::kTileBytes;
         const int key0 = pi.c0 + ptile * kTile;
         if (!waited && key0 + kTile > pi.pos) { pdl_wait(); waited = true; }      // the key written in this step
-        int my_box_page = 0;                   // lane b: the page of box b of this tile
-        {
-            const int kb = key0 + (lane < boxes ? lane : 0) * box_rows;
-            my_box_page = __shfl_sync(0xffffffffu, p_pages, ((kb - pi.c0) / page_size) & 31);
-        }
-        int box_pages[8];
-#pragma unroll
-        for (int b = 0; b < 8; ++b) box_pages[b] = __shfl_sync(0xffffffffu, my_box_page, b);
+        // lane b requests box b of this tile (keys and values): the copies of a tile are issued side by
+        // side instead of one after the other by a single lane
+        const int kb = key0 + (lane < boxes ? lane : 0) * box_rows;
+        const bool box_valid = lane < boxes && kb <= pi.pos && kb + box_rows - 1 >= pi.lo;
+        const int box_page = __shfl_sync(0xffffffffu, p_pages, ((kb - pi.c0) / page_size) & 31);
+        const unsigned valid_mask = __ballot_sync(0xffffffffu, box_valid);
+        const uint32_t bar = smem_addr(&bars[s]);
         if (lane == 0) {
-            int n_boxes = 0;
-            for (int b = 0; b < boxes; ++b) {
-                const int kb = key0 + b * box_rows;
-                if (kb <= pi.pos && kb + box_rows - 1 >= pi.lo) ++n_boxes;
-            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the stage was read and maybe zeroed by ordinary accesses
-            const uint32_t bar = smem_addr(&bars[s]);
-            att_expect_tx(bar, static_cast<uint32_t>(n_boxes) * 2u * box_rows * HD * 2u);
+            att_expect_tx(bar, static_cast<uint32_t>(__popc(valid_mask)) * 2u * box_rows * HD * 2u);
+        }
+        __syncwarp();
+        if (box_valid) {
+            const int row = (box_page * Hkv + pi.g) * page_size + kb % page_size;
 #pragma unroll
-            for (int b = 0; b < 8; ++b) {
-                const int kb = key0 + b * box_rows;
-                if (b < boxes && kb <= pi.pos && kb + box_rows - 1 >= pi.lo) {
-                    const int row = (box_pages[b] * Hkv + pi.g) * page_size + kb % page_size;
-#pragma unroll
-                    for (int h = 0; h < Cfg::kHalves; ++h) {
-                        const uint32_t off = static_cast<uint32_t>(h * (kTile * 128) + b * box_rows * (Cfg::kBoxCols * 2));
-                        att_tma_load(k_tile + off, &map_k, h * 64, row, bar);
-                        att_tma_load(v_tile + off, &map_v, h * 64, row, bar);
-                    }
-                }
+            for (int h = 0; h < Cfg::kHalves; ++h) {
+                const uint32_t off = static_cast<uint32_t>(h * (kTile * 128) + lane * box_rows * (Cfg::kBoxCols * 2));
+                att_tma_load(k_tile + off, &map_k, h * 64, row, bar);
+                att_tma_load(v_tile + off, &map_v, h * 64, row, bar);
             }
         }
         ++n_issued;
