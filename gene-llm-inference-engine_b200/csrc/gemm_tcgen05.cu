@@ -91,6 +91,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -131,12 +135,18 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     return d;
 }
 
-template <int BLOCK_Q>
+// TILED: the 128-row operand comes from a tile-by-tile copy of the matrix (see TcParams::p_tiles)
+// and a stage holds two 64-wide blocks of K, fetched with one bulk copy of 32 KB.
+template <int BLOCK_Q, bool TILED = false>
 struct TcConfig {
-    static constexpr int kStageBytesP = kBlockP * kBlockK * 2;
-    static constexpr int kStageBytesQ = BLOCK_Q * kBlockK * 2;
+    static constexpr int kKb = TILED ? 2 : 1;                  // 64-wide blocks of K per stage
+    static constexpr int kBlockBytesP = kBlockP * kBlockK * 2;
+    static constexpr int kBlockBytesQ = BLOCK_Q * kBlockK * 2;
+    static constexpr int kStageBytesP = kBlockBytesP * kKb;
+    static constexpr int kStageBytesQ = kBlockBytesQ * kKb;
     static constexpr int kStageBytes = kStageBytesP + kStageBytesQ;
-    static constexpr int kStages = (BLOCK_Q >= 256) ? 4 : (BLOCK_Q >= 128) ? 6 : 8;
+    static constexpr int kStages = TILED ? ((BLOCK_Q >= 128) ? 3 : (BLOCK_Q >= 64) ? 4 : 5)
+                                         : ((BLOCK_Q >= 256) ? 4 : (BLOCK_Q >= 128) ? 6 : 8);
     static constexpr int kTmemCols = BLOCK_Q < 32 ? 32 : BLOCK_Q;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
     // a cluster's split 0 also holds the partial tiles of the other splits, [split - 1][q][128 rows]
@@ -164,6 +174,9 @@ struct TcParams {
     int prefetch_p;          // P is a weight matrix no earlier kernel writes: its first tiles may be
                              // fetched before the kernel waits for the kernels it depends on
     int cluster;             // the splits of a tile are one cluster (dims 1 x 1 x splits): reduce in shared memory
+    const uint8_t* p_tiles;  // TILED kernels: the 128-row operand tile by tile, [row tile][K block][128][64] with the
+                             // 128-byte swizzle applied and K padded to a multiple of 128 (tile_weight in ops/kernels.py)
+    int tiles_kb;            // 64-wide blocks of K in a row of tiles
 };
 
 template <int BLOCK_Q>
@@ -195,10 +208,11 @@ __device__ __forceinline__ void store_row_chunk(const TcParams& p, int row_p, in
     }
 }
 
-template <int BLOCK_Q>
+template <int BLOCK_Q, bool TILED>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const TcParams p) {
-    using Cfg = TcConfig<BLOCK_Q>;
+    using Cfg = TcConfig<BLOCK_Q, TILED>;
+    constexpr int kKb = Cfg::kKb;
     constexpr int kStages = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -216,7 +230,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     const int total_kb = (p.K + kBlockK - 1) / kBlockK;
     const int kb_begin = split * p.k_blocks_per_split;
     const int kb_end = min(total_kb, kb_begin + p.k_blocks_per_split);
-    const int n_kb = max(0, kb_end - kb_begin);
+    const int n_blocks = max(0, kb_end - kb_begin);
+    const int n_kb = (n_blocks + kKb - 1) / kKb;                // stages of kKb blocks (the host keeps splits whole)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -245,15 +260,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             // this kernel waits for its predecessors, so the weight stream never pauses between
             // the kernels of a decode step; the activation tiles follow after the wait.
             const int early = p.prefetch_p ? min(n_kb, kStages) : 0;
+            auto load_p = [&](int i, uint32_t full) {          // stage i of this CTA: blocks kb_begin + i * kKb ..
+                const uint32_t dst = smem_u32(smem + (i % kStages) * Cfg::kStageBytes);
+                if (TILED)
+                    bulk_load(dst, p.p_tiles + (static_cast<size_t>(tile_p) * p.tiles_kb + kb_begin + i * kKb) * Cfg::kBlockBytesP,
+                              Cfg::kStageBytesP, full);
+                else
+                    tma_load_2d(dst, &map_p, (kb_begin + i) * kBlockK, tile_p * kBlockP, full);
+            };
+            auto load_q = [&](int i, uint32_t full) {
+                const uint32_t dst = smem_u32(smem + (i % kStages) * Cfg::kStageBytes + Cfg::kStageBytesP);
+#pragma unroll
+                for (int j = 0; j < kKb; ++j)
+                    tma_load_2d(dst + j * Cfg::kBlockBytesQ, &map_q, (kb_begin + i * kKb + j) * kBlockK, tile_q * BLOCK_Q, full);
+            };
             for (int i = 0; i < early; ++i) {
                 const uint32_t full = smem_u32(&bars[i]);
                 mbar_expect_tx(full, Cfg::kStageBytes);
-                tma_load_2d(smem_u32(smem + i * Cfg::kStageBytes), &map_p, (kb_begin + i) * kBlockK, tile_p * kBlockP, full);
+                load_p(i, full);
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int i = 0; i < early; ++i) {
-                tma_load_2d(smem_u32(smem + i * Cfg::kStageBytes + Cfg::kStageBytesP), &map_q, (kb_begin + i) * kBlockK,
-                            tile_q * BLOCK_Q, smem_u32(&bars[i]));
+                load_q(i, smem_u32(&bars[i]));
                 issued = i + 1;
             }
             for (int i = early; i < n_kb; ++i) {
@@ -265,10 +293,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 }
                 const uint32_t full = smem_u32(&bars[s]);
                 mbar_expect_tx(full, Cfg::kStageBytes);
-                uint8_t* stage = smem + s * Cfg::kStageBytes;
-                const int k0 = (kb_begin + i) * kBlockK;
-                tma_load_2d(smem_u32(stage), &map_p, k0, tile_p * kBlockP, full);
-                tma_load_2d(smem_u32(stage + Cfg::kStageBytesP), &map_q, k0, tile_q * BLOCK_Q, full);
+                load_p(i, full);
+                load_q(i, full);
                 issued = i + 1;
             }
             if (*abort_flag) {
@@ -295,12 +321,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 }
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes);
-                const uint64_t desc_p = umma_desc(a_addr);
-                const uint64_t desc_q = umma_desc(a_addr + Cfg::kStageBytesP);
 #pragma unroll
-                for (int k = 0; k < kBlockK / 16; ++k) {
-                    // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in the address field
-                    umma_bf16(tmem_base, desc_p + 2 * k, desc_q + 2 * k, Cfg::kIdesc, (i > 0 || k > 0) ? 1u : 0u);
+                for (int j = 0; j < kKb; ++j) {
+                    const uint64_t desc_p = umma_desc(a_addr + j * Cfg::kBlockBytesP);
+                    const uint64_t desc_q = umma_desc(a_addr + Cfg::kStageBytesP + j * Cfg::kBlockBytesQ);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 16; ++k) {
+                        // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in the address field
+                        umma_bf16(tmem_base, desc_p + 2 * k, desc_q + 2 * k, Cfg::kIdesc, (i > 0 || j > 0 || k > 0) ? 1u : 0u);
+                    }
                 }
                 umma_commit(smem_u32(&bars[kStages + s]));      // frees the stage once the MMAs have read it
             }
@@ -756,14 +785,14 @@ constexpr int kMaxClusterSplits = 8;           // the portable cluster size
 
 // How many clusters of `splits` CTAs of this kernel the device holds at once (0: none, or the
 // partial tiles do not fit into shared memory). Asked once per size.
-template <int BLOCK_Q>
+template <int BLOCK_Q, bool TILED>
 static int cluster_capacity(int splits) {
-    using Cfg = TcConfig<BLOCK_Q>;
+    using Cfg = TcConfig<BLOCK_Q, TILED>;
     static int cached[kMaxClusterSplits + 1] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
     if (splits < 2 || splits > kMaxClusterSplits || Cfg::smem_bytes(splits) > kMaxSmemPerBlock) return 0;
     if (cached[splits] >= 0) return cached[splits];
     int n = 0;
-    if (cudaFuncSetAttribute(gemm_tc_kernel<BLOCK_Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemPerBlock) == cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BLOCK_Q, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemPerBlock) == cudaSuccess) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(1, 1, splits);
         cfg.blockDim = dim3(kThreads);
@@ -775,28 +804,28 @@ static int cluster_capacity(int splits) {
         attr[0].val.clusterDim.z = splits;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BLOCK_Q>, &cfg) != cudaSuccess) n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BLOCK_Q, TILED>, &cfg) != cudaSuccess) n = 0;
     }
     cudaGetLastError();
     cached[splits] = n;
     return n;
 }
 
-template <int BLOCK_Q>
+template <int BLOCK_Q, bool TILED>
 static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, TcParams p, dim3 grid, cudaStream_t st) {
-    using Cfg = TcConfig<BLOCK_Q>;
+    using Cfg = TcConfig<BLOCK_Q, TILED>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BLOCK_Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemPerBlock);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BLOCK_Q, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemPerBlock);
         if (e != cudaSuccess) { set_error("gemm_tc: cannot reserve %d bytes of shared memory: %s", kMaxSmemPerBlock, cudaGetErrorString(e)); return 1; }
         configured = true;
     }
     // all clusters of the launch resident at once, or the workspace path: a second wave of clusters
     // would cost more than the reduce through global memory
     const long long tiles = static_cast<long long>(grid.x) * grid.y;
-    p.cluster = (p.splits > 1 && g_cluster_reduce && tiles <= cluster_capacity<BLOCK_Q>(p.splits)) ? 1 : 0;
+    p.cluster = (p.splits > 1 && g_cluster_reduce && tiles <= cluster_capacity<BLOCK_Q, TILED>(p.splits)) ? 1 : 0;
     if (!p.cluster) {
-        launch_kernel((gemm_tc_kernel<BLOCK_Q>), dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, mp, mq, p);
+        launch_kernel((gemm_tc_kernel<BLOCK_Q, TILED>), dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, mp, mq, p);
         return check_launch("gemm_tc");
     }
     cudaLaunchConfig_t cfg = {};
@@ -813,7 +842,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, TcParams p, d
     attr[1].val.clusterDim.z = p.splits;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BLOCK_Q>, mp, mq, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BLOCK_Q, TILED>, mp, mq, p);
     if (e != cudaSuccess) { set_error("gemm_tc: cluster launch failed: %s", cudaGetErrorString(e)); return 1; }
     return check_launch("gemm_tc");
 }
@@ -829,6 +858,8 @@ using namespace gi;
 //   swap = 1: weights on the 128-row side, block_q >= tokens on the narrow side.
 //   splits > 1 (swap only): K is cut into `splits` ranges; workspace must hold
 //   tiles * splits * 128 * block_q floats and counters one zeroed word per tile.
+//   w_tiles (swap only, may be null): W once more in the tile-by-tile layout of TcParams::p_tiles;
+//   the weights are then fetched with bulk copies, two 64-wide blocks of K to a stage.
 // Switches the cluster reduce of split products on or off (on by default); returns the old value.
 extern "C" int gi_gemm_tc_set_cluster(int on) {
     const int old = g_cluster_reduce;
@@ -838,12 +869,12 @@ extern "C" int gi_gemm_tc_set_cluster(int on) {
 
 // Clusters of `splits` CTAs the device holds at once for the kernel of this block_q (0: the
 // workspace path is used).
-extern "C" int gi_gemm_tc_cluster_capacity(int block_q, int splits) {
+extern "C" int gi_gemm_tc_cluster_capacity(int block_q, int splits, int tiled) {
     switch (block_q) {
-        case 16: return cluster_capacity<16>(splits);
-        case 32: return cluster_capacity<32>(splits);
-        case 64: return cluster_capacity<64>(splits);
-        case 128: return cluster_capacity<128>(splits);
+        case 16: return tiled ? cluster_capacity<16, true>(splits) : cluster_capacity<16, false>(splits);
+        case 32: return tiled ? cluster_capacity<32, true>(splits) : cluster_capacity<32, false>(splits);
+        case 64: return tiled ? cluster_capacity<64, true>(splits) : cluster_capacity<64, false>(splits);
+        case 128: return tiled ? cluster_capacity<128, true>(splits) : cluster_capacity<128, false>(splits);
         default: return 0;
     }
 }
@@ -851,7 +882,7 @@ extern "C" int gi_gemm_tc_cluster_capacity(int block_q, int splits) {
 extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int accumulate, int M, int N, int K,
                           long long lda, long long ldw, long long ldc, int swap, int block_q, int splits,
                           void* workspace, long long workspace_floats, void* counters, int n_counters, void* status,
-                          void* stream) {
+                          const void* w_tiles, void* stream) {
     if (M == 0 || N == 0) return 0;
     GI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: sizes must be positive (M=%d, N=%d, K=%d)", M, N, K);
     GI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
@@ -876,6 +907,13 @@ extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
     p.status = static_cast<int*>(status);
     const int total_kb = (K + kBlockK - 1) / kBlockK;
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
+    const bool tiled = swap && w_tiles != nullptr && block_q <= 128;
+    p.p_tiles = tiled ? static_cast<const uint8_t*>(w_tiles) : nullptr;
+    p.tiles_kb = (total_kb + 1) / 2 * 2;
+    if (tiled) {
+        GI_REQUIRE(reinterpret_cast<uintptr_t>(w_tiles) % 16 == 0, "gemm_tc: the tiled weights must be 16-byte aligned");
+        p.k_blocks_per_split = (p.k_blocks_per_split + 1) / 2 * 2;      // a stage's two blocks belong to one split
+    }
 
     CUtensorMap mp, mq;
     p.prefetch_p = swap ? 1 : 0;
@@ -897,11 +935,11 @@ extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (block_q) {
-        case 16: return launch_tc<16>(mp, mq, p, grid, st);
-        case 32: return launch_tc<32>(mp, mq, p, grid, st);
-        case 64: return launch_tc<64>(mp, mq, p, grid, st);
-        case 128: return launch_tc<128>(mp, mq, p, grid, st);
-        default: return launch_tc<256>(mp, mq, p, grid, st);
+        case 16: return tiled ? launch_tc<16, true>(mp, mq, p, grid, st) : launch_tc<16, false>(mp, mq, p, grid, st);
+        case 32: return tiled ? launch_tc<32, true>(mp, mq, p, grid, st) : launch_tc<32, false>(mp, mq, p, grid, st);
+        case 64: return tiled ? launch_tc<64, true>(mp, mq, p, grid, st) : launch_tc<64, false>(mp, mq, p, grid, st);
+        case 128: return tiled ? launch_tc<128, true>(mp, mq, p, grid, st) : launch_tc<128, false>(mp, mq, p, grid, st);
+        default: return launch_tc<256, false>(mp, mq, p, grid, st);
     }
 }
 

@@ -22,12 +22,16 @@ from .step import StepEngine
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_seq_len: Optional[int] = None, page_size: int = 16, kv_pages: Optional[int] = None,
-                 max_running: int = 8, step_tokens: int = 2048, prefill_chunk: int = 0, prefix_cache: bool = True):
+                 max_running: int = 8, step_tokens: int = 2048, prefill_chunk: int = 0, prefix_cache: bool = True,
+                 decode_weight_copy: bool = True):
         """``model_dir``: folder with config.json and model.safetensors. ``dtype``: "bfloat16"
         (serving kernels) or "float32" (everything in true 32-bit). ``max_seq_len`` lowers the
         context length. ``kv_pages``: pages of ``page_size`` positions in the pool (default: room
-        for ``max_running`` full contexts, within 80 % of the free device memory)."""
-        self.model = load_model(model_dir, dtype=dtype, device=device, max_position=max_seq_len)
+        for ``max_running`` full contexts, within 80 % of the free device memory).
+        ``decode_weight_copy`` (bfloat16): a second copy of the matrices laid out for decode steps, which
+        then stream the weights faster; False saves that memory."""
+        self.model = load_model(model_dir, dtype=dtype, device=device, max_position=max_seq_len,
+                                weight_tiles=decode_weight_copy)
         context = self.model.max_position
         if kv_pages is None:
             per_request = (context + page_size - 1) // page_size

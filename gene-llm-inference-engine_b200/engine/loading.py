@@ -23,13 +23,16 @@ def parse_dtype(name) -> torch.dtype:
         raise ValueError(f"unknown dtype '{name}' (bfloat16 or float32)") from None
 
 
-def load_model(model_dir: str, dtype="bfloat16", device="cuda:0", max_position: Optional[int] = None) -> DecoderModel:
+def load_model(model_dir: str, dtype="bfloat16", device="cuda:0", max_position: Optional[int] = None,
+               weight_tiles: bool = True) -> DecoderModel:
     """Reads config.json (the registry picks the architecture) and model.safetensors, and builds
     the model on the device. ``dtype`` float32 runs everything in true 32-bit; bfloat16 weights of
-    the file are then widened exactly. ``max_position`` may lower the context length."""
+    the file are then widened exactly. ``max_position`` may lower the context length.
+    ``weight_tiles`` (bfloat16 only): keep a second, tile-by-tile copy of each matrix, from which
+    decode steps stream the weights faster (it doubles the memory of the matrices)."""
     if not torch.cuda.is_available():
         raise RuntimeError("no CUDA device: this engine runs on the GPU only")
     arch, cfg, params = load_model_folder(model_dir)
-    model = DecoderModel(cfg.model_spec(), params, parse_dtype(dtype), torch.device(device), max_position)
+    model = DecoderModel(cfg.model_spec(), params, parse_dtype(dtype), torch.device(device), max_position, weight_tiles)
     model.config = cfg
     return model

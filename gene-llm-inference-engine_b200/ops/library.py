@@ -30,7 +30,7 @@ _SIGNATURES = {
     "gi_gemm_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                      c_int, c_void_p],
     "gi_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
-                   c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p],
+                   c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
     "gi_gemm_tc_persistent": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                               c_int, c_void_p, c_void_p],
     "gi_gemm_tc_status": [c_void_p, c_void_p, c_void_p],
@@ -41,7 +41,7 @@ _SIGNATURES = {
                              c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p, c_void_p],
     "gi_attention_prefill_rows": [c_int, c_int],
     "gi_gemm_tc_set_cluster": [c_int],
-    "gi_gemm_tc_cluster_capacity": [c_int, c_int],
+    "gi_gemm_tc_cluster_capacity": [c_int, c_int, c_int],
     "gi_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                 c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p, c_void_p],
     "gi_attention_prefill_tc_supported": [c_int, c_int, c_int, c_int],

@@ -40,8 +40,8 @@ class AttentionMixer:
                              f"({qkv_rows}, {self.hidden_size})")
         if tuple(weights["w_o"].shape) != (self.hidden_size, self.num_heads * self.head_dim):
             raise ValueError(f"attention: w_o has shape {tuple(weights['w_o'].shape)}")
-        self.w_qkv = Linear(weights["w_qkv"], build.compute_dtype, build.device)
-        self.w_o = Linear(weights["w_o"], build.compute_dtype, build.device)
+        self.w_qkv = Linear(weights["w_qkv"], build.compute_dtype, build.device, tiles=build.weight_tiles)
+        self.w_o = Linear(weights["w_o"], build.compute_dtype, build.device, tiles=build.weight_tiles)
         self.dtype = build.compute_dtype
         # bfloat16 with a head size the tensor-core kernels are built for; else the general kernel
         self.fast = self.dtype is torch.bfloat16 and kernels.attention_fast_supported(

@@ -26,8 +26,8 @@ class SwiGLUFeedForward:
             raise ValueError(f"swiglu: w_gate_up has shape {tuple(weights['w_gate_up'].shape)}, expected ({2 * I}, {D})")
         if tuple(weights["w_down"].shape) != (D, I):
             raise ValueError(f"swiglu: w_down has shape {tuple(weights['w_down'].shape)}, expected ({D}, {I})")
-        self.w_gate_up = Linear(weights["w_gate_up"], build.compute_dtype, build.device)
-        self.w_down = Linear(weights["w_down"], build.compute_dtype, build.device)
+        self.w_gate_up = Linear(weights["w_gate_up"], build.compute_dtype, build.device, tiles=build.weight_tiles)
+        self.w_down = Linear(weights["w_down"], build.compute_dtype, build.device, tiles=build.weight_tiles)
         self.dtype = build.compute_dtype
 
     def forward(self, ctx, xn: torch.Tensor, x: torch.Tensor) -> None:

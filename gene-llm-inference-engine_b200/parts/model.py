@@ -26,7 +26,7 @@ class LayerRun:
 
 class DecoderModel:
     def __init__(self, spec: ModelSpec, params: Dict[str, torch.Tensor], compute_dtype: torch.dtype,
-                 device: torch.device, max_position: Optional[int] = None):
+                 device: torch.device, max_position: Optional[int] = None, weight_tiles: bool = True):
         spec.validate()
         if compute_dtype not in (torch.float32, torch.bfloat16):
             raise ValueError("compute dtype must be float32 or bfloat16")
@@ -36,7 +36,8 @@ class DecoderModel:
         self.hidden_size = spec.hidden_size
         self.vocab_size = spec.vocab_size
         self.max_position = min(spec.max_position, max_position) if max_position else spec.max_position
-        build = BuildContext(device=device, compute_dtype=compute_dtype, max_position=self.max_position)
+        build = BuildContext(device=device, compute_dtype=compute_dtype, max_position=self.max_position,
+                             weight_tiles=weight_tiles)
 
         emb = params["embedding.weight"]
         if tuple(emb.shape) != (spec.vocab_size, spec.hidden_size):
@@ -53,12 +54,9 @@ class DecoderModel:
                      for e in spec.schedule]
         self.final_norm = build_part(NORMS, "norm", spec.final_norm, sub_weights(params, "final_norm."), build)
         if spec.tie_word_embeddings:
-            self.head = Linear.__new__(Linear)
-            self.head.out_features, self.head.in_features = spec.vocab_size, spec.hidden_size
-            self.head.compute_dtype = compute_dtype
-            self.head.weight = self.embedding                      # one copy on the device
+            self.head = Linear.over(self.embedding, tiles=weight_tiles)   # the table itself, not a second row-major copy
         else:
-            self.head = Linear(params["head.weight"], compute_dtype, device)
+            self.head = Linear(params["head.weight"], compute_dtype, device, tiles=weight_tiles)
             if (self.head.out_features, self.head.in_features) != (spec.vocab_size, spec.hidden_size):
                 raise ValueError("head.weight has the wrong shape")
 
@@ -81,7 +79,9 @@ class DecoderModel:
         return out
 
     def weight_bytes(self) -> int:
-        """Bytes of distinct weight tensors on the device (a tied head counts once)."""
+        """Bytes of distinct weight tensors on the device (a tied head counts once; the tile-by-tile
+        copies that few-token products read in place of the row-major matrices are not counted: a step
+        reads one or the other)."""
         seen, total = set(), 0
 
         def visit(obj):
@@ -92,7 +92,7 @@ class DecoderModel:
                     total += obj.numel() * obj.element_size()
             elif hasattr(obj, "__dict__"):
                 for k, v in vars(obj).items():
-                    if k in ("cos", "sin"):
+                    if k in ("cos", "sin", "weight_tiles"):
                         continue
                     visit(v)
             elif isinstance(obj, (list, tuple)):

@@ -24,6 +24,7 @@ class BuildContext:
     device: torch.device
     compute_dtype: torch.dtype       # torch.float32 (true 32-bit path) or torch.bfloat16
     max_position: int                # context length the engine is built for
+    weight_tiles: bool = True        # bfloat16: keep a second, tile-by-tile copy of each matrix for few-token products
 
 
 def _register(table: Dict[str, Callable], kind: str):

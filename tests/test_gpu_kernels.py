@@ -346,6 +346,36 @@ def test_gemm_tensor_cores(M, N, K_, plan, c_dtype):
     K().gemm_tc(a, w, auto)                            # the plan the engine would pick
     close(auto, want, c_dtype, "gemm_tc auto plan", f32_tol=2e-6 * max(1, K_ / 64), bf16_tol=1e-2)
     assert K().gemm_tc_status(torch.device(DEV)) == 0
+    if plan[0]:
+        # few tokens: the same product with the weights read from their tile-by-tile copy (bulk
+        # copies, two blocks of K to a stage); zero padding of the copy must not leak either
+        tiles = K().tile_weight(w)
+        guard2 = torch.full((M + 2, N), -1024.0, dtype=dt(c_dtype), device=DEV)
+        tiled = guard2[1:M + 1]
+        tiled.fill_(float("nan"))
+        K().gemm_tc(a, w, tiled, plan=plan, w_tiles=tiles)
+        close(tiled, want, c_dtype, "gemm_tc tiled", f32_tol=2e-6 * max(1, K_ / 64), bf16_tol=1e-2)
+        assert float(guard2[0].float().min()) == -1024.0 == float(guard2[-1].float().max()), "wrote outside the output"
+        auto2 = torch.empty((M, N), dtype=dt(c_dtype), device=DEV)
+        K().gemm_tc(a, w, auto2, w_tiles=tiles)
+        close(auto2, want, c_dtype, "gemm_tc tiled auto plan", f32_tol=2e-6 * max(1, K_ / 64), bf16_tol=1e-2)
+        if c_dtype == "float32":
+            acc2 = base.clone()
+            K().gemm_tc(a, w, acc2, accumulate=True, plan=plan, w_tiles=tiles)
+            close(acc2, want + base.cpu().double(), "float32", "gemm_tc tiled accumulate", f32_tol=2e-6 * max(1, K_ / 64))
+        assert K().gemm_tc_status(torch.device(DEV)) == 0
+
+
+def test_tile_weight_layout():
+    """Element (r, k) of tile (i, j) lies at r * 64 + ((k // 8) ^ (r % 8)) * 8 + k % 8 of the tile."""
+    g = torch.Generator().manual_seed(3)
+    w = torch.randn(200, 136, generator=g).to(torch.bfloat16).to(DEV)
+    wp = torch.zeros(256, 256, dtype=torch.bfloat16)           # rows and columns padded to multiples of 128
+    wp[:200, :136] = w.cpu()
+    assert K().tile_weight(w).numel() == 256 * 256
+    t = K().tile_weight(w).view(2, 4, 128 * 64).cpu()
+    for (i, j, r, k) in [(0, 0, 0, 0), (0, 0, 5, 9), (1, 2, 71, 7), (0, 1, 127, 63), (1, 0, 3, 40), (1, 3, 100, 1)]:
+        assert t[i, j, r * 64 + (((k // 8) ^ (r % 8)) * 8) + k % 8] == wp[i * 128 + r, j * 64 + k]
 
 
 def test_gemm_tensor_cores_refuses_what_tma_cannot_address():
