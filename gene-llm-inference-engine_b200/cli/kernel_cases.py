@@ -4,7 +4,7 @@
 
 Cases at the Llama-3.2-1B layer sizes (random data, sizes larger than L2 where bandwidth matters):
   gemm_prefill       the four products of a layer for T tokens (tensor cores, persistent kernel)
-  gemm_decode        the same products for B tokens (weights on the 128-row side, split over K)
+  gemm_decode        the same products for B tokens (weights on the 128-row side, read tile by tile, split over K)
   attention_decode   B single tokens, each over a context of C cached positions
   attention_prefill  one prompt of T tokens, with the mma.sync kernel and with the tcgen05 kernel
   decode_step        R whole decode steps of B requests at context C through the step function
@@ -52,9 +52,12 @@ def gemm_case(tokens, repeat, dev, kernels):
         if name == "head" and tokens > 128:
             continue
         ws = _weights(n, k, dev)
+        # few tokens: the engine's Linear reads the tile-by-tile copy of the weights
+        tiles = [kernels.tile_weight(w) if tokens <= 128 else None for w in ws]
         a = torch.randn(tokens, k, device=dev).bfloat16()
         out = torch.zeros(tokens, n, device=dev)
-        _time(f"gemm {name} [{tokens}x{k}] x [{n}x{k}]^T", lambda i: kernels.gemm_tc(a, ws[i % len(ws)], out, acc), repeat,
+        _time(f"gemm {name} [{tokens}x{k}] x [{n}x{k}]^T",
+              lambda i: kernels.gemm_tc(a, ws[i % len(ws)], out, acc, w_tiles=tiles[i % len(ws)]), repeat,
               nbytes=n * k * 2, flops=2 * tokens * n * k)
     if tokens > 128:
         ws = _weights(2 * I, D, dev)
