@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine at the Llama-3.2-1B shape with random weights.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 1b|3b|8b] [--layers L]
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 and context 8192, timed on
 the device over exactly K decode steps (one step = one token for every request of the batch);
@@ -33,6 +33,12 @@ LLAMA_1B = {
                      "original_max_position_embeddings": 8192},
     "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
 }
+# The other two shapes the baseline names (not the default run): --shape 3b | 8b, usually with --layers.
+LLAMA_3B = dict(LLAMA_1B, hidden_size=3072, num_hidden_layers=28, num_attention_heads=24, head_dim=128)
+LLAMA_8B = dict(LLAMA_1B, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
+                head_dim=128, tie_word_embeddings=False,
+                rope_scaling=dict(LLAMA_1B["rope_scaling"], factor=8.0))
+SHAPES = {"1b": ("Llama-3.2-1B", LLAMA_1B), "3b": ("Llama-3.2-3B", LLAMA_3B), "8b": ("Llama-3.1-8B", LLAMA_8B)}
 CONTEXT = 8192
 PAGE = 16
 PREFILL_TOKENS = 2048
@@ -91,7 +97,8 @@ class ClockSampler:
 def model_folder(config, seed=1):
     """The random-weights model folder (made once per box under the temporary directory)."""
     from geneinfer_b200.weights import write_random_model
-    tag = f"geneinfer_bench_{config['num_hidden_layers']}x{config['hidden_size']}_{seed}_{os.getuid()}"
+    tag = (f"geneinfer_bench_{config['num_hidden_layers']}x{config['hidden_size']}x{config['intermediate_size']}_"
+           f"{int(config['tie_word_embeddings'])}_{seed}_{os.getuid()}")
     path = os.path.join(tempfile.gettempdir(), tag)
     if not (os.path.isfile(os.path.join(path, "model.safetensors")) and os.path.isfile(os.path.join(path, "done"))):
         t0 = time.time()
@@ -223,7 +230,8 @@ def time_prefill(engine, tokens, warmup, vocab):
 def run_ours(args):
     import torch
     from geneinfer_b200 import Engine
-    cfg = dict(LLAMA_1B)
+    shape_name, shape = SHAPES[args.shape]
+    cfg = dict(shape)
     layers_full = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -261,17 +269,18 @@ def run_ours(args):
 
     value = batch / (ms_step * 1e-3)
     line = {
-        "metric": "decode tok/s at batch 8, context 8192 (Llama-3.2-1B shape, random bf16 weights)",
+        "metric": f"decode tok/s at batch 8, context 8192 ({shape_name} shape, random bf16 weights)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights N(0,0.02), random token ids, random cache contents",
         "impl": "ours",
         "config": {
-            "model": "Llama-3.2-1B shape", "global_batch": batch, "seq_len": CONTEXT, "parallelism": "single GPU",
+            "model": f"{shape_name} shape", "global_batch": batch, "seq_len": CONTEXT, "parallelism": "single GPU",
             "layers": cfg["num_hidden_layers"], "layers_of_named_config": layers_full, "hidden": cfg["hidden_size"],
             "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-            "intermediate": cfg["intermediate_size"], "vocab": vocab, "tied_head": True, "page_size": PAGE,
-            "rope": "theta 500000, llama3 32/1/4/8192", "rms_norm_eps": cfg["rms_norm_eps"],
+            "intermediate": cfg["intermediate_size"], "vocab": vocab, "tied_head": cfg["tie_word_embeddings"], "page_size": PAGE,
+            "rope": f"theta 500000, llama3 {cfg['rope_scaling']['factor']:g}/1/4/8192", "rms_norm_eps": cfg["rms_norm_eps"],
+            "decode_weight_copy": True,
             "l2": "step inputs (weights + cache) are larger than L2", "peaks": pk["source"],
         },
         "e2e": {"value": round(batch / (ms_e2e * 1e-3), 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
@@ -304,6 +313,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0 = all)")
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="1b", help="layer sizes (the default is the baseline's third configuration)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

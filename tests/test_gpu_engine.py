@@ -10,7 +10,7 @@ import trace_tools as tt
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-CASES = ["a", "b", "c"]
+CASES = ["a", "b", "c", "d"]
 
 
 def _play(case, dtype, steps, page_size=16):

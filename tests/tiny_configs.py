@@ -1,4 +1,6 @@
-"""The tiny configurations the tests run: two Llama shapes that differ in every size and option."""
+"""The tiny configurations the tests run: Llama shapes that differ in every size and option (A and B
+are the two named by the baseline; C and D have the head sizes 64 and 128 of the 1B and the 3B / 8B
+shapes, for which the tensor-core attention kernels are built)."""
 import os
 import sys
 
@@ -52,3 +54,14 @@ TINY_C = {   # head size 64 (the tcgen05 prefill attention and the fused gate/up
     "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
 }
 SHARP_C = {"seed": 31, "dtype": "bfloat16", "std": 0.12, "norm_mean": 1.0, "norm_std": 0.1}
+
+TINY_D = {   # head size 128 as in the 3B and 8B shapes, 4:2 heads, untied head, three layers
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_act": "silu",
+    "hidden_size": 256, "intermediate_size": 328, "num_hidden_layers": 3, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 333, "max_position_embeddings": 384,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 96},
+    "rms_norm_eps": 2e-6, "tie_word_embeddings": False,
+}
+SHARP_D = {"seed": 41, "dtype": "bfloat16", "std": 0.1, "norm_mean": 1.0, "norm_std": 0.1}
