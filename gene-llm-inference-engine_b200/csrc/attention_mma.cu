@@ -672,8 +672,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     pdl_prologue();
     extern __shared__ __align__(128) uint8_t smem[];
     const int G = H / Hkv;
-    const int g = blockIdx.y;
-    const int t0 = work[blockIdx.x * 3], n_tok = work[blockIdx.x * 3 + 1], req = work[blockIdx.x * 3 + 2];
+    const int g = blockIdx.x;          // heads vary fastest: the longest work items of every head start first
+    const int t0 = work[blockIdx.y * 3], n_tok = work[blockIdx.y * 3 + 1], req = work[blockIdx.y * 3 + 2];
     const int n_rows = n_tok * G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* table = block_tables + static_cast<size_t>(req) * table_stride;
@@ -802,7 +802,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __
     uint64_t* empty = full + kStages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = H / Hkv;
-    const int g = blockIdx.y;
+    const int g = blockIdx.x;          // heads vary fastest: the longest work items of every head start first
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -814,7 +814,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __
     __syncthreads();
     pdl_prologue();
 
-    const int t0 = work[blockIdx.x * 3], n_tok = work[blockIdx.x * 3 + 1], req = work[blockIdx.x * 3 + 2];
+    const int t0 = work[blockIdx.y * 3], n_tok = work[blockIdx.y * 3 + 1], req = work[blockIdx.y * 3 + 2];
     const int n_rows = n_tok * G;
     const int* table = block_tables + static_cast<size_t>(req) * table_stride;
     const int pos_first = positions[t0], pos_last = pos_first + n_tok - 1;
@@ -1020,7 +1020,7 @@ static int launch_prefill(const void* q, const void* kc, const void* vc, void* o
         if (e != cudaSuccess) { set_error("attention_prefill: %s", cudaGetErrorString(e)); return 1; }
         configured = true;
     }
-    dim3 grid(n_work, Hkv);
+    dim3 grid(Hkv, n_work);
     launch_kernel((attention_prefill_kernel<HD>), dim3(grid), dim3(kAttThreads), bytes, st, 
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc),
         static_cast<__nv_bfloat16*>(out), work, positions, tables, table_stride, H, Hkv, page_size, scale * kLog2e, window);
@@ -1045,7 +1045,7 @@ static int launch_prefill_tma(const void* q, const void* kc, const void* vc, voi
                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "attention_prefill")) return 1;
     if (make_tensor_map_2d(&mv, vc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_total, HD, HD, box_rows, Cfg::kBoxCols,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "attention_prefill")) return 1;
-    dim3 grid(n_work, Hkv);
+    dim3 grid(Hkv, n_work);
     launch_kernel((attention_prefill_tma_kernel<HD>), dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, mk, mv,
                   static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), work, positions, tables,
                   table_stride, H, Hkv, page_size, scale * kLog2e, window, status);
@@ -1117,7 +1117,7 @@ extern "C" int gi_attention_prefill(const void* q, const void* k_cache, const vo
                                     void* status, void* stream) {
     if (n_work == 0) return 0;
     GI_REQUIRE(gi_attention_fast_supported(hd, H, Hkv), "attention_prefill: head size %d with %d/%d heads is not built", hd, H, Hkv);
-    GI_REQUIRE(Hkv <= 65535, "attention_prefill: grid too large");
+    GI_REQUIRE(n_work <= 65535, "attention_prefill: %d work items exceed the grid limit 65535", n_work);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (gi_attention_prefill_rows(page_size, hd) == 128 && status != nullptr) {
 #define GI_PREFILL_TMA(HD) return launch_prefill_tma<HD>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, \

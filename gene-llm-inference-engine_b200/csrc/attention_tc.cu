@@ -165,7 +165,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = H / Hkv;
-    const int g = blockIdx.y;
+    const int g = blockIdx.x;          // heads vary fastest: the longest work items of every head start first
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&bars[s]), 1); mbar_init(smem_u32(&bars[2 + s]), 1); }
@@ -183,7 +183,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + kKeys;
     pdl_prologue();
 
-    const int t0 = work[blockIdx.x * 3], n_tok = work[blockIdx.x * 3 + 1], req = work[blockIdx.x * 3 + 2];
+    const int t0 = work[blockIdx.y * 3], n_tok = work[blockIdx.y * 3 + 1], req = work[blockIdx.y * 3 + 2];
     const int n_rows = n_tok * G;
     const int pos_first = positions[t0], pos_last = pos_first + n_tok - 1;
     const int lo_first = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
@@ -456,7 +456,7 @@ static int launch(const void* q, const void* kc, const void* vc, void* out, cons
                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "attention_prefill_tc")) return 1;
     if (make_tensor_map_2d(&mv, vc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_total, HD, HD, box_rows, 64,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "attention_prefill_tc")) return 1;
-    dim3 grid(n_work, Hkv);
+    dim3 grid(Hkv, n_work);
     launch_kernel((attention_prefill_tc_kernel<HD>), dim3(grid), dim3(kThreads), C::kSmemBytes, st, mk, mv,
                   static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), work, positions, tables,
                   table_stride, H, Hkv, page_size, scale * kLog2e, window, status);
@@ -484,7 +484,7 @@ extern "C" int gi_attention_prefill_tc(const void* q, const void* k_cache, const
     if (n_work == 0) return 0;
     GI_REQUIRE(gi_attention_prefill_tc_supported(hd, H, Hkv, page_size), "attention_prefill_tc: shape not supported");
     GI_REQUIRE(status != nullptr, "attention_prefill_tc: a status word is required");
-    GI_REQUIRE(Hkv <= 65535, "attention_prefill_tc: grid too large");
+    GI_REQUIRE(n_work <= 65535, "attention_prefill_tc: %d work items exceed the grid limit 65535", n_work);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (hd == 64)
         return atc::launch<64>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv,
