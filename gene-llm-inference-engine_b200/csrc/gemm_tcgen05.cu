@@ -446,13 +446,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     __threadfence();
 #pragma unroll 1
                     for (int c = 0; c < kChunks; ++c) {
+                        // four splits' values are requested together (64 loads in flight), then added
+                        // in split order: one split after the other would wait for memory 4 times as often
                         float v[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                        for (int s = 0; s < p.splits; ++s) {
-                            const float* part = ws_tile + static_cast<size_t>(s) * BLOCK_Q * kBlockP;
+                        for (int s0 = 0; s0 < p.splits; s0 += 4) {
+                            float part[4][16];
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) v[j] += __ldcg(&part[(c * 16 + j) * kBlockP + row_in_tile]);
+                            for (int ds = 0; ds < 4; ++ds) {
+                                const float* src = ws_tile + static_cast<size_t>(s0 + ds) * BLOCK_Q * kBlockP;
+#pragma unroll
+                                for (int j = 0; j < 16; ++j)
+                                    part[ds][j] = (s0 + ds < p.splits) ? __ldcg(&src[(c * 16 + j) * kBlockP + row_in_tile]) : 0.f;
+                            }
+#pragma unroll
+                            for (int ds = 0; ds < 4; ++ds)
+                                if (s0 + ds < p.splits) {
+#pragma unroll
+                                    for (int j = 0; j < 16; ++j) v[j] += part[ds][j];
+                                }
                         }
                         store_row_chunk<BLOCK_Q>(p, row_p, tile_q * BLOCK_Q + c * 16, v);
                     }
