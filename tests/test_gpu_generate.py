@@ -103,6 +103,18 @@ def test_greedy_and_sampled_requests_in_one_batch_with_steps_launched_ahead():
     assert engine.steps.cache.free_pages() == 16 and not engine.steps.cache.requests
 
 
+def test_decoding_without_the_tiled_weight_copy_gives_the_same_tokens():
+    """The tile-by-tile copy of the weights changes how decode steps fetch them, not what they compute."""
+    from geneinfer_b200 import Engine
+    prompts = [tc.random_tokens(n, 500, 70 + n) for n in (9, 40, 3)]
+    with_copy = Engine(gf.model_dir("c"), dtype="bfloat16", max_running=3, kv_pages=24, prefix_cache=False)
+    without = Engine(gf.model_dir("c"), dtype="bfloat16", max_running=3, kv_pages=24, prefix_cache=False,
+                     decode_weight_copy=False)
+    assert with_copy.model.head.weight_tiles is not None and without.model.head.weight_tiles is None
+    assert with_copy.model.weight_bytes() == without.model.weight_bytes()
+    assert with_copy.generate(prompts, 12) == without.generate(prompts, 12)
+
+
 def test_prefix_cache_gives_the_same_tokens():
     from geneinfer_b200 import Engine
     common = tc.random_tokens(40, 256, 9)
