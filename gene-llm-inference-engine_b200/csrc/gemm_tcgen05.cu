@@ -208,6 +208,16 @@ __device__ __forceinline__ void store_row_chunk(const TcParams& p, int row_p, in
     }
 }
 
+// The same for a chunk whose old values were read earlier (32-bit C, accumulate).
+__device__ __forceinline__ void store_row_chunk_old(const TcParams& p, int row_p, int q0, const float* v, const float* old) {
+    if (row_p >= p.rows_p) return;
+    float* c = static_cast<float*>(p.C) + static_cast<long long>(row_p) * p.stride_p + static_cast<long long>(q0) * p.stride_q;
+    const int n = min(16, p.rows_q - q0);
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+        if (j < n) c[j * p.stride_q] = old[j] + v[j];
+}
+
 template <int BLOCK_Q, bool TILED>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const TcParams p) {
@@ -341,6 +351,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         const int lane_group = warp & 3;                        // the TMEM lanes this warp may read
         const int row_in_tile = lane_group * 32 + lane;
         const int row_p = tile_p * kBlockP + row_in_tile;
+        // A tile of 16 columns that this CTA itself will add into C: the old values are requested
+        // now, while the products run, instead of after them.
+        const bool early_old = BLOCK_Q == 16 && p.accumulate && !p.c_bf16 && row_p < p.rows_p &&
+                               (p.splits == 1 || (p.cluster && split == 0));
+        float old_c[16];
+        if (early_old) {
+            const float* c = static_cast<const float*>(p.C) + static_cast<long long>(row_p) * p.stride_p +
+                             static_cast<long long>(tile_q * BLOCK_Q) * p.stride_q;
+            const int n = min(16, p.rows_q - tile_q * BLOCK_Q);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) old_c[j] = (j < n) ? __ldcg(c + j * p.stride_q) : 0.f;
+        }
         bool have = n_kb > 0;
         if (have && !mbar_wait(smem_u32(&bars[2 * kStages]), 0, abort_flag)) {
             if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, kErrEpilogueWait); }
@@ -397,7 +419,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
                             for (int j = 0; j < 16; ++j) v[j] += part[(c * 16 + j) * kBlockP + row_in_tile];
                         }
-                        store_row_chunk<BLOCK_Q>(p, row_p, tile_q * BLOCK_Q + c * 16, v);
+                        if (early_old) store_row_chunk_old(p, row_p, tile_q * BLOCK_Q, v, old_c);
+                        else store_row_chunk<BLOCK_Q>(p, row_p, tile_q * BLOCK_Q + c * 16, v);
                     }
                 }
             }
@@ -416,7 +439,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = 0.f;
                     }
-                    store_row_chunk<BLOCK_Q>(p, row_p, tile_q * BLOCK_Q + c * 16, v);
+                    if (early_old) store_row_chunk_old(p, row_p, tile_q * BLOCK_Q, v, old_c);
+                    else store_row_chunk<BLOCK_Q>(p, row_p, tile_q * BLOCK_Q + c * 16, v);
                 }
             } else {
                 // partial tile -> workspace [tile][split][q][128 rows]; the last CTA of the tile sums all splits
