@@ -827,7 +827,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __
     if (warp == Cfg::kWarps) {
         // ---------------------------------------------------------------- producer warp
         // All lanes look up the tile's pages at once (lane b: box b), before the wait for the free
-        // stage; lane 0 issues the boxes.
+        // stage; then every lane requests its own box (one lane issuing them in turn is slow).
         for (int i = 0; i < n_tiles; ++i) {
             const int s = i % kStages;
             const int key0 = (first_tile + i) * kTile;
@@ -847,17 +847,14 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 att_expect_tx(bar, static_cast<uint32_t>(__popc(valid_mask)) * 2u * box_rows * HD * 2u);
             }
-            for (int b = 0; b < boxes; ++b) {
-                const int page = __shfl_sync(0xffffffffu, page_lane, b);
-                if (lane == 0 && ((valid_mask >> b) & 1u)) {
-                    const int kb = key0 + b * box_rows;
-                    const int row = (page * Hkv + g) * page_size + kb % page_size;
+            __syncwarp();                                         // the expected bytes are set before any copy can complete
+            if (lane_valid) {                                     // every lane requests its own box
+                const int row = (page_lane * Hkv + g) * page_size + kb_lane % page_size;
 #pragma unroll
-                    for (int h = 0; h < Cfg::kHalves; ++h) {
-                        const uint32_t off = static_cast<uint32_t>(h * (kTile * 128) + b * box_rows * (Cfg::kBoxCols * 2));
-                        att_tma_load(k_tile + off, &map_k, h * 64, row, bar);
-                        att_tma_load(v_tile + off, &map_v, h * 64, row, bar);
-                    }
+                for (int h = 0; h < Cfg::kHalves; ++h) {
+                    const uint32_t off = static_cast<uint32_t>(h * (kTile * 128) + lane * box_rows * (Cfg::kBoxCols * 2));
+                    att_tma_load(k_tile + off, &map_k, h * 64, row, bar);
+                    att_tma_load(v_tile + off, &map_v, h * 64, row, bar);
                 }
             }
         }
