@@ -448,7 +448,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
     // ---- producer cursor: the next tile to request
     DecodeItem pi;
-    int pw = blockIdx.x * Cfg::kWarps + warp, ptile = 0, n_issued = 0;
+    // A CTA's warps take neighbouring items (neighbouring chunks of one request lie next to each other
+    // in memory); when there are fewer items than warps, each CTA takes only its share so that all SMs work.
+    const int per_cta = total < static_cast<int>(gridDim.x) * Cfg::kWarps ? (total + gridDim.x - 1) / gridDim.x : Cfg::kWarps;
+    const int first_item = warp < per_cta ? static_cast<int>(blockIdx.x) * per_cta + warp : total;
+    int pw = first_item, ptile = 0, n_issued = 0;
     int p_pages = 0;                           // lane i: the page of the chunk's i-th page-sized run of keys
     const int pages_per_chunk = kChunkKeys / page_size > 0 ? kChunkKeys / page_size : 1;
     auto p_seek = [&]() {
@@ -511,7 +515,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     bool failed = false;
     LaneOffsets<HD, kTile, true> off;
     off.init(lane);
-    for (int cw = blockIdx.x * Cfg::kWarps + warp; cw < total && !failed; cw += stride) {
+    for (int cw = first_item; cw < total && !failed; cw += stride) {
         item_at(cw, ci);
         float* my_o = part_o + ((static_cast<size_t>(ci.idx) * H + ci.g * G) * max_chunks + ci.chunk) * HD;
         float* my_ml = part_ml + ((static_cast<size_t>(ci.idx) * H + ci.g * G) * max_chunks + ci.chunk) * 2;
@@ -994,8 +998,7 @@ static int launch_decode_tma(const void* q, const void* kc, const void* vc, void
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int items = n_rows * Hkv * n_chunks;
-    int grid = (items + Cfg::kWarps - 1) / Cfg::kWarps;
-    if (grid > sms) grid = sms;
+    int grid = items < sms ? items : sms;           // few items: fewer per CTA rather than fewer CTAs
     launch_kernel((attention_decode_tma_kernel<HD>), dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, mk, mv,
                   static_cast<const __nv_bfloat16*>(q), rows, n_rows, row_req, positions, tables, table_stride, H, Hkv,
                   page_size, scale * kLog2e, window, part_o, part_ml, max_chunks, n_chunks, status);
