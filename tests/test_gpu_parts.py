@@ -314,3 +314,152 @@ def test_toy_architecture_with_a_stateful_mixer(tmp_path):
         tt.compare(got, plain, 5e-5, "toy model")
         engine.cache.check_invariants()
         assert engine.cache.slots.free_count == 4 and all(g.pool.free_count == g.pool.n_pages for g in engine.cache.groups)
+
+
+# ------------------------------------------------------------------------- a second toy architecture
+def _register_toy_routed():
+    """A feed-forward with routing (router logits in 32-bit, the best of three experts per token,
+    each expert a small gated unit) and a position encoding of its own (angles that grow with the
+    square root of the position), entered through the public registries like the first toy."""
+    from geneinfer_b200.config import (Architecture, LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture)
+    from geneinfer_b200.parts import FEED_FORWARDS, register_feed_forward, register_position_encoding
+    from geneinfer_b200.weights.plan import TensorRule, WeightPlan
+    if "toy_best_of_three" in FEED_FORWARDS:
+        return
+
+    @register_position_encoding("toy_sqrt_angles")
+    class SqrtAngles:
+        applies = "qk_before_store"
+        interleaved = False
+
+        def __init__(self, params, weights, build):
+            half = params["head_dim"] // 2
+            pos = np.sqrt(np.arange(build.max_position, dtype=np.float64))[:, None]
+            ang = pos * (np.arange(half, dtype=np.float64)[None] + 1.0) * params["step"]
+            self.cos = torch.from_numpy(np.cos(ang).astype(np.float32)).to(build.device).contiguous()
+            self.sin = torch.from_numpy(np.sin(ang).astype(np.float32)).to(build.device).contiguous()
+
+    @register_feed_forward("toy_best_of_three")
+    class BestOfThree:
+        def __init__(self, params, weights, build):
+            self.D, self.I, self.E = params["hidden_size"], params["intermediate_size"], 3
+            dev = build.device
+            self.router = weights["router"].to(device=dev, dtype=torch.float32)          # [E, D]
+            self.gate_up = weights["gate_up"].to(device=dev, dtype=torch.float32)        # [E, 2I, D]
+            self.down = weights["down"].to(device=dev, dtype=torch.float32)              # [E, D, I]
+
+        def forward(self, ctx, xn, x):
+            xf = xn.float()
+            best = (xf @ self.router.T).argmax(dim=-1)                                   # routing in 32-bit
+            for e in range(self.E):
+                rows = (best == e).nonzero(as_tuple=True)[0]
+                if rows.numel():
+                    gu = xf[rows] @ self.gate_up[e].T
+                    g, u = gu[:, :self.I], gu[:, self.I:]
+                    x[rows] += (g * torch.sigmoid(g) * u) @ self.down[e].T
+
+    class Toy2Config:
+        architecture = "ToyRoutedForCausalLM"
+
+        def __init__(self, j):
+            self.hidden, self.layers, self.vocab, self.max_pos, self.step = j["hidden"], j["layers"], j["vocab"], j["max_pos"], j["step"]
+
+        @classmethod
+        def from_json(cls, j):
+            return cls(j)
+
+        def model_spec(self):
+            D = self.hidden
+            norm = PartSpec("rmsnorm", {"size": D, "eps": 3e-6})
+            pos = PartSpec("toy_sqrt_angles", {"head_dim": 16, "step": self.step})
+            att = PartSpec("attention", {"hidden_size": D, "num_heads": 3, "num_kv_heads": 3, "head_dim": 16,
+                                         "scale": 0.3, "window": None, "position": pos})
+            routed = PartSpec("toy_best_of_three", {"hidden_size": D, "intermediate_size": 24})
+            dense = PartSpec("swiglu", {"hidden_size": D, "intermediate_size": 40})
+            layers = [LayerSpec(att, routed if i % 2 == 0 else dense, norm, norm) for i in range(self.layers)]
+            return ModelSpec("ToyRoutedForCausalLM", D, self.vocab, self.max_pos, layers,
+                             [ScheduleEntry(i) for i in range(self.layers)], norm, True)
+
+    def plan(cfg):
+        D = cfg.hidden
+        rules = [TensorRule("emb", (cfg.vocab, D)), TensorRule("norm", (D,), "vector")]
+        for i in range(cfg.layers):
+            rules += [TensorRule(f"l{i}.n1", (D,), "vector"), TensorRule(f"l{i}.n2", (D,), "vector"),
+                      TensorRule(f"l{i}.qkv", (144, D)), TensorRule(f"l{i}.o", (D, 48))]
+            if i % 2 == 0:
+                rules += [TensorRule(f"l{i}.router", (3, D))] + [TensorRule(f"l{i}.e{e}.gu", (48, D)) for e in range(3)] + \
+                         [TensorRule(f"l{i}.e{e}.down", (D, 24)) for e in range(3)]
+            else:
+                rules += [TensorRule(f"l{i}.gu", (80, D)), TensorRule(f"l{i}.down", (D, 40))]
+
+        def assemble(t):
+            out = {"embedding.weight": t["emb"], "final_norm.weight": t["norm"], "head.weight": t["emb"]}
+            for i in range(cfg.layers):
+                q = f"layers.{i}."
+                out[q + "mixer_norm.weight"], out[q + "feed_forward_norm.weight"] = t[f"l{i}.n1"], t[f"l{i}.n2"]
+                out[q + "mixer.w_qkv"], out[q + "mixer.w_o"] = t[f"l{i}.qkv"], t[f"l{i}.o"]
+                if i % 2 == 0:
+                    out[q + "feed_forward.router"] = t[f"l{i}.router"]
+                    out[q + "feed_forward.gate_up"] = torch.stack([t[f"l{i}.e{e}.gu"] for e in range(3)])
+                    out[q + "feed_forward.down"] = torch.stack([t[f"l{i}.e{e}.down"] for e in range(3)])
+                else:
+                    out[q + "feed_forward.w_gate_up"], out[q + "feed_forward.w_down"] = t[f"l{i}.gu"], t[f"l{i}.down"]
+            return out
+        return WeightPlan(rules, [], assemble)
+
+    register_architecture(Architecture("ToyRoutedForCausalLM", ("toy_routed",), Toy2Config, plan))
+
+
+def _toy_routed_plain(w, cfg, toks):
+    D, T = cfg["hidden"], len(toks)
+    x = w["emb"][torch.tensor(toks)].float()
+    ang = np.sqrt(np.arange(T, dtype=np.float64))[:, None] * (np.arange(8, dtype=np.float64)[None] + 1.0) * cfg["step"]
+    c, s_ = torch.from_numpy(np.cos(ang).astype(np.float32))[:, None], torch.from_numpy(np.sin(ang).astype(np.float32))[:, None]
+
+    def rot(v):                                             # half-split pairs (k, k + 8)
+        a, b = v[..., :8], v[..., 8:]
+        return torch.cat([a * c - b * s_, a * s_ + b * c], dim=-1)
+    routes = []
+    for i in range(cfg["layers"]):
+        xn = pm.plain_rmsnorm(x, w[f"l{i}.n1"], 3e-6)
+        qkv = xn @ w[f"l{i}.qkv"].T
+        q, k, v = rot(qkv[:, :48].reshape(T, 3, 16)), rot(qkv[:, 48:96].reshape(T, 3, 16)), qkv[:, 96:].reshape(T, 3, 16)
+        x = x + pm.plain_attention(q, k, v, 0.3).reshape(T, 48) @ w[f"l{i}.o"].T
+        xn = pm.plain_rmsnorm(x, w[f"l{i}.n2"], 3e-6)
+        if i % 2 == 0:
+            best = (xn @ w[f"l{i}.router"].T).argmax(dim=-1)
+            routes.append(best)
+            y = torch.zeros_like(x)
+            for t in range(T):
+                e = int(best[t])
+                gu = xn[t] @ w[f"l{i}.e{e}.gu"].T
+                y[t] = pm.plain_swiglu(gu[None, :24], gu[None, 24:])[0] @ w[f"l{i}.e{e}.down"].T
+            x = x + y
+        else:
+            gu = xn @ w[f"l{i}.gu"].T
+            x = x + pm.plain_swiglu(gu[:, :40], gu[:, 40:]) @ w[f"l{i}.down"].T
+    return (pm.plain_rmsnorm(x, w["norm"], 3e-6) @ w["emb"].T).numpy(), routes
+
+
+def test_toy_architecture_with_a_routed_feed_forward_and_its_own_position_encoding(tmp_path):
+    _register_toy_routed()
+    from geneinfer_b200.engine.loading import load_model
+    from geneinfer_b200.engine.step import StepEngine
+    from geneinfer_b200.weights import write_random_model
+    cfg = {"architectures": ["ToyRoutedForCausalLM"], "model_type": "toy_routed", "hidden": 40, "layers": 3, "vocab": 70,
+           "max_pos": 80, "step": 0.37}
+    d = write_random_model(cfg, 5, str(tmp_path / "toy_routed"), "float32", std=0.2, norm_std=0.1)
+    model = load_model(d, dtype="float32")
+    reqs = {f"t{i}": tc.random_tokens(n, 70, 300 + i) for i, n in enumerate([40, 80, 9, 55])}
+    w = pm.read_safetensors_f32(os.path.join(d, "model.safetensors"))
+    plain, used = {}, set()
+    for rid, toks in reqs.items():
+        plain[rid], routes = _toy_routed_plain(w, cfg, toks)
+        used |= {int(e) for r in routes for e in r}
+    assert used == {0, 1, 2}, "the test's tokens do not reach every expert"
+    for steps in (tt.trace_whole(reqs), tt.trace_portions(reqs), tt.trace_mixed(reqs, seed=6, tail=8)):
+        engine = StepEngine(model, page_size=8, n_pages=4 * 10, max_requests=4, max_step_tokens=128)
+        got = tt.run_in_process(engine, steps)
+        tt.compare(got, plain, 5e-5, "toy routed model")
+        engine.cache.check_invariants()
+        assert all(g.pool.free_count == g.pool.n_pages for g in engine.cache.groups)
