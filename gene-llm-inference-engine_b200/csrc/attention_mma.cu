@@ -1,19 +1,26 @@
 // Paged causal attention in bfloat16 on the tensor cores (mma.sync m16n8k16, 32-bit accumulators
-// and 32-bit online softmax), in two kernels that share their warp-level code:
+// and 32-bit online softmax). The kernels share their warp-level code (warp_tile_step):
 //
-//   attention_decode   single decoded tokens deep in a context. The context is cut into chunks of
-//                      kChunkKeys positions (a fixed length, so a row's arithmetic does not depend on
-//                      the batch); one CTA takes one chunk of one (request, key/value head), its four
-//                      warps a quarter each, with the query heads that share the key/value head packed
-//                      as rows of the 16-row tile. Partial (max, sum, output) per chunk go to a
-//                      workspace and attention_combine merges them in chunk order.
-//   attention_prefill  portions of prompts. One CTA takes 64 query rows = (tokens x heads of one
-//                      key/value group) and walks the keys in tiles of 64 through a two-stage
-//                      cp.async pipeline; the four warps own 16 rows each.
+//   attention_decode_tma   single decoded tokens deep in a context (the kernel decoding uses). The
+//                          context is cut into chunks of kChunkKeys positions, a fixed length, so that
+//                          a row's arithmetic does not depend on the batch; an item is one chunk of one
+//                          (token, key/value head), with the query heads that share the key/value head
+//                          packed as rows of the 16-row tile. One persistent CTA per SM; each of its
+//                          warps walks its own items with its own ring of 32-key tiles that TMA fills
+//                          (a box per page and head, each lane requesting its own). Partial (max, sum,
+//                          output) per chunk go to a workspace and attention_combine merges them in
+//                          chunk order.
+//   attention_decode       the same for page sizes that TMA boxes cannot tile: one CTA per chunk, four
+//                          warps a quarter each, cp.async.
+//   attention_prefill_tma  portions of prompts at head sizes the tcgen05 kernel (attention_tc.cu) is
+//                          not built for: 128 query rows = (tokens x heads of one key/value group) per
+//                          CTA, eight consumer warps of 16 rows and a TMA producer warp, 64-key tiles.
+//   attention_prefill      the same with 64 rows, four warps and cp.async, for other page sizes.
 //
 // Keys and values come from pages [pages, Hkv, page_size, head_dim] through the request's block
-// table. Rows of a tile that lie outside every query's range are zero-filled on load, so stale or
-// unwritten page contents (tests fill them with NaN) can never reach a result.
+// table. Rows of a tile that lie outside every query's range are zero-filled (on load, or in shared
+// memory after a TMA box brought a whole page), so stale or unwritten page contents (tests fill
+// them with NaN) can never reach a result.
 // Head sizes 16, 32, 64 and 128 are built; other sizes use the general kernel.
 #include "common.cuh"
 #include "tma.cuh"
@@ -22,7 +29,7 @@ namespace gi {
 
 constexpr int kAttThreads = 128;
 constexpr int kTileKeys = 64;
-constexpr int kChunkKeys = 256;          // decode: keys per CTA (4 warps x 64)
+constexpr int kChunkKeys = 256;          // decode: keys per item
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }

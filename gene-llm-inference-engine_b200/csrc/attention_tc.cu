@@ -2,10 +2,12 @@
 //
 // One CTA takes 128 query rows (tokens x the query heads of one key/value group) and walks the keys
 // in tiles of 128 over the request's pages:
-//   warp 0      TMA producer: one box per page and head for K and for V into a two-stage ring;
+//   warp 0      TMA producer: one box per page and head for K and for V into a two-stage ring, each
+//               lane requesting its own box;
 //   warp 1      allocates tensor memory and issues the MMAs: S = Q K^T (both operands K-major in
 //               shared memory, S in tensor memory) and O += P V (P from shared memory, V as an
-//               MN-major operand straight from the page layout [keys, head_dim]);
+//               MN-major operand straight from the page layout [keys, head_dim]); S of the next tile
+//               is issued before P V of the current one, so the softmax warps never wait for P V;
 //   warps 2..5  softmax: thread r owns row r of the tile, which is lane r of tensor memory, so row
 //               maximum and row sum need no exchange between threads. They read S with tcgen05.ld,
 //               scale O by the correction factor in tensor memory, write P = exp2(S - m) as bfloat16
