@@ -2,10 +2,12 @@
 // accumulation in tensor memory.
 //
 // One CTA computes a 128 x BLOCK_Q tile. Both operands are K-major, so each is fetched by TMA as
-// [rows, 64] boxes with the 128-byte swizzle that tcgen05.mma reads directly. Three roles:
-//   warp 0      producer: one lane issues the TMA loads of a pipeline of kStages stages;
-//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (4 x K=16 per stage) and
-//               commits each stage back to the producer, and the finished tile to the epilogue;
+// [rows, 64] boxes with the 128-byte swizzle that tcgen05.mma reads directly (TILED kernels fetch
+// the weights from a copy that is laid out tile by tile already: one untiled bulk copy of 32 KB
+// brings two 64-wide blocks of K). Three roles:
+//   warp 0      producer: one lane issues the loads of a pipeline of kStages stages;
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (4 x K=16 per 64 columns of K)
+//               and commits each stage back to the producer, and the finished tile to the epilogue;
 //   warps 2..5  epilogue: tcgen05.ld of the accumulators (one lane = one row of the tile), then
 //               store / accumulate into C in 32-bit, or round to bfloat16.
 // The 128-row operand "P" and the BLOCK_Q-row operand "Q" can be either matrix: for many tokens P
