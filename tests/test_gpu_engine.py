@@ -89,15 +89,18 @@ def test_long_decoding_and_first_tokens(dtype):
     tt.compare(got, gf.plain_logits(case, dtype), gf.tolerance(dtype, case), f"long decode {dtype}")
 
 
-@pytest.mark.parametrize("page_size", [8, 64])
-def test_other_page_sizes(page_size):
-    case, dtype = "a", "float32"
+@pytest.mark.parametrize("case,dtype,page_size", [("a", "float32", 8), ("a", "float32", 64), ("c", "bfloat16", 8),
+                                                  ("c", "bfloat16", 32), ("c", "bfloat16", 64), ("d", "bfloat16", 128),
+                                                  ("b", "bfloat16", 24)])
+def test_other_page_sizes(case, dtype, page_size):
+    """Pages smaller than, equal to and larger than the kernels' key tiles (the TMA boxes follow the
+    page size), and a page size that TMA boxes cannot tile (24: the cp.async kernels)."""
     reqs = gf.requests(case)
     steps = tt.trace_mixed(reqs, seed=3)
     max_tokens = tt.max_tokens_of(steps, reqs, unit=max(64, page_size))
     engine = gf.make_engine(case, dtype, n_pages=max_tokens // page_size, page_size=page_size)
     got = tt.run_in_process(engine, steps)
-    tt.compare(got, gf.plain_logits(case, dtype), gf.TOL_F32, f"page size {page_size}")
+    tt.compare(got, gf.plain_logits(case, dtype), gf.tolerance(dtype, case), f"page size {page_size}")
 
 
 def test_step_refuses_bad_input_and_leaves_state_unchanged():
