@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine at the Llama-3.2-1B shape with random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 1b|3b|8b] [--layers L]
+    python bench.py --scenario mixed|prefix [--shape ...]      (continuous batching / shared prefixes, see run_scenario)
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 and context 8192, timed on
 the device over exactly K decode steps (one step = one token for every request of the batch);
@@ -297,6 +298,79 @@ def run_ours(args):
     return 0
 
 
+def run_scenario(args):
+    """Two workloads through the entry point, beside the default run: ``mixed`` (32 requests with
+    prompts of 128 to 4096 random ids and 256 generated tokens each, admitted together, prompts cut
+    into portions beside decoding requests) and ``prefix`` (64 requests with 2,048-token prompts of
+    which the first 1,024 are one of four shared prefixes, 512 generated tokens each, with the
+    prefix cache on and off). Prints one JSON line."""
+    import numpy as np
+    import torch
+    from geneinfer_b200 import Engine, SamplingParams
+    shape_name, shape = SHAPES[args.shape]
+    cfg = dict(shape)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    folder = model_folder(cfg)
+    vocab = cfg["vocab_size"]
+    rng = np.random.default_rng(11)
+
+    def ids(n):
+        return [int(t) for t in rng.integers(0, vocab, n)]
+
+    if args.scenario == "mixed":
+        n_req, new, running = 32, 256, 32
+        prompts = [ids(int(n)) for n in rng.integers(128, 4097, n_req)]
+        variants = [("prefix_cache_on", True)]
+    else:
+        n_req, new, running = 64, 512, 64
+        prefixes = [ids(1024) for _ in range(4)]
+        prompts = [prefixes[i % 4] + ids(1024) for i in range(n_req)]
+        variants = [("prefix_cache_on", True), ("prefix_cache_off", False)]
+    longest = max(len(p) for p in prompts) + new
+    pages = sum((len(p) + new + PAGE - 1) // PAGE + 1 for p in prompts)
+    out = {"metric": f"{args.scenario} workload, generated tok/s ({shape_name} shape, random bf16 weights)", "impl": "ours",
+           "n_gpus": 1, "dtype": "bf16", "data": "synthetic: seeded random weights and token ids",
+           "config": {"model": f"{shape_name} shape", "layers": cfg["num_hidden_layers"], "requests": n_req,
+                      "prompt_tokens": sum(len(p) for p in prompts), "generated_per_request": new, "max_running": running,
+                      "step_tokens": 2048, "page_size": PAGE}}
+    for name, cache_on in variants:
+        llm = Engine(folder, dtype="bfloat16", max_seq_len=longest, page_size=PAGE, kv_pages=pages, max_running=running,
+                     step_tokens=2048, prefix_cache=cache_on)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        if args.scenario == "prefix":
+            # the first request of each prefix arrives first; the others once its prompt is in the cache
+            rids = [llm.submit(p, len(p) + new - 1, SamplingParams(0.0)) for p in prompts[:4]]
+            while any(llm.result(r).first_token_step < 0 for r in rids):
+                llm.step()
+            rids += [llm.submit(p, len(p) + new - 1, SamplingParams(0.0)) for p in prompts[4:]]
+        else:
+            rids = [llm.submit(p, len(p) + new - 1, SamplingParams(0.0)) for p in prompts]
+        llm.run_until_idle()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        res = [llm.result(r) for r in rids]
+        bad = [r.error or len(r.generated_tokens) for r in res if r.error or len(r.generated_tokens) != new]
+        if bad:
+            raise RuntimeError(f"scenario {args.scenario}: requests did not finish as expected: {bad[:4]}")
+        st = llm.stats
+        out[name] = {"seconds": round(dt, 3), "generated_tok_s": round(n_req * new / dt, 1),
+                     "all_tok_s": round((sum(len(p) for p in prompts) + n_req * new) / dt, 1), "steps": st.steps,
+                     "preemptions": st.preemptions, "prefix_hits": st.prefix_hits, "cached_positions": st.prefix_tokens,
+                     "evicted_pages": st.evicted_pages, "max_tokens_in_step": st.max_tokens_in_step}
+        llm.clear_prefix_cache()
+        llm.steps.cache.check_invariants()
+        if llm.steps.cache.free_pages() != pages:
+            raise RuntimeError("scenario: pages were lost")
+        del llm
+        torch.cuda.empty_cache()
+    out["value"] = out[variants[0][0]]["generated_tok_s"]
+    out["unit"] = "tok/s"
+    print(json.dumps(out), flush=True)
+    return 0
+
+
 def run_reference(args):
     # The reference is a CMake project without setup.py or pyproject.toml:
     # `pip install --no-index --target baseline/_ref <reference>` answers "not installable".
@@ -314,6 +388,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0 = all)")
     ap.add_argument("--shape", choices=sorted(SHAPES), default="1b", help="layer sizes (the default is the baseline's third configuration)")
+    ap.add_argument("--scenario", choices=["mixed", "prefix"], default="", help="a workload through the scheduler instead of the default run")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -321,6 +396,8 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.scenario:
+        return run_scenario(args)
     return run_ours(args)
 
 
