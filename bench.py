@@ -208,18 +208,21 @@ def time_decode_e2e(llm, batch, context, steps, warmup, vocab):
     return wall_ms / steps, h2d, d2h
 
 
-def time_prefill(engine, tokens, warmup, vocab):
+def time_prefill(engine, tokens, warmup, vocab, portions=1):
+    """One prompt of ``tokens`` ids in ``portions`` equal steps; the median of three, in ms."""
     import torch
     from geneinfer_b200.engine.step import StepEntry
     g = torch.Generator().manual_seed(7)
     times = []
+    n = tokens // portions
     for i in range(warmup + 3):
         prompt = torch.randint(0, vocab, (tokens,), generator=g).tolist()
         engine.open("p")
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        engine.step([StepEntry("p", prompt, [tokens - 1])])
+        for c in range(portions):
+            engine.step([StepEntry("p", prompt[c * n:(c + 1) * n], [n - 1] if c == portions - 1 else [])])
         end.record()
         torch.cuda.synchronize()
         if i >= warmup:
@@ -254,13 +257,16 @@ def run_ours(args):
     clock_record = clocks.stop()
     ms_e2e, h2d, d2h = time_decode_e2e(llm, batch, CONTEXT, args.steps, args.warmup, vocab)
     ms_prefill = time_prefill(llm.steps, PREFILL_TOKENS, max(1, args.warmup), vocab)
+    ms_prefill_4 = time_prefill(llm.steps, PREFILL_TOKENS, 1, vocab, portions=4)
+    ms_short, _ = time_decode_device(llm.steps, batch, 128, max(4, args.steps // 2), args.warmup, vocab)
     bytes_step = step_bytes(model, cfg, batch, CONTEXT)
     achieved = bytes_step / (ms_step * 1e-3) / 1e9
     flops = prefill_flops(cfg, PREFILL_TOKENS)
     del llm
     torch.cuda.empty_cache()
 
-    points = {}
+    points = {"decode_b8_context128": round(batch / (ms_short * 1e-3), 1),
+              "prefill_2048_in_4_portions": round(PREFILL_TOKENS / (ms_prefill_4 * 1e-3), 1)}
     for b in (1, 64):
         e = make(b)
         ms_b, _ = time_decode_device(e.steps, b, CONTEXT, max(4, args.steps // 2), args.warmup, vocab)

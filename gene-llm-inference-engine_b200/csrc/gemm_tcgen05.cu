@@ -551,6 +551,9 @@ struct TcPersistentParams {
     int tiles_p, tiles_q;
     int up_row_offset;           // SwiGLU: row of the first up channel in the weight (= I)
     int* status;
+    int splits;                  // K is cut into this many ranges, each an accumulator tile of its own whose result is
+    int kb_per_split;            //   stored split_rows rows further down in the output (a workspace; the ranges are
+    int split_rows;              //   added up, in order, by reduce_splits_kernel): few tiles still fill the GPU
 };
 
 constexpr int kPersistentThreads = 64 + 2 * 128;     // producer warp, MMA warp, two epilogue groups of four warps
@@ -570,8 +573,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_kb = (p.K + kBlockK - 1) / kBlockK;
-    const int n_tiles = p.tiles_p * p.tiles_q;
+    const int total_kb = (p.K + kBlockK - 1) / kBlockK;
+    const int out_tiles = p.tiles_p * p.tiles_q;
+    const int n_tiles = out_tiles * p.splits;
+    // work item t: output tile t % out_tiles, range t / out_tiles of K
+    auto kb_first = [&](int t) { return (t / out_tiles) * p.kb_per_split; };
+    auto kb_count = [&](int t) { return min(total_kb, kb_first(t) + p.kb_per_split) - kb_first(t); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -597,7 +604,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
         if (lane == 0) {
             int it = 0, issued_ok = 1;
             for (int t = blockIdx.x; t < n_tiles && issued_ok; t += gridDim.x) {
-                const int tile_p = t % p.tiles_p, tile_q = t / p.tiles_p;
+                const int tile_p = (t % out_tiles) % p.tiles_p, tile_q = (t % out_tiles) / p.tiles_p;
+                const int kb0 = kb_first(t), n_kb = kb_count(t);
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = it % kStages;
                     if (!mbar_wait(smem_u32(&bars[kStages + s]), ((it / kStages) & 1) ^ 1, abort_flag)) {
@@ -608,7 +616,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                     const uint32_t full = smem_u32(&bars[s]);
                     mbar_expect_tx(full, Cfg::kStageBytes);
                     uint8_t* stage = smem + s * Cfg::kStageBytes;
-                    const int k0 = kb * kBlockK;
+                    const int k0 = (kb0 + kb) * kBlockK;
                     tma_load_2d(smem_u32(stage), &map_p, k0, tile_p * kBlockP, full);
                     if (EPI == kEpiSwiGLU) {
                         const int n0 = tile_q * (BLOCK_Q / 2);
@@ -642,6 +650,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                 }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * BLOCK_Q;
+                const int n_kb = kb_count(t);
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = it % kStages;
                     if (!mbar_wait(smem_u32(&bars[s]), (it / kStages) & 1, abort_flag)) {
@@ -677,7 +686,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
         int j = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++j) {
-            const int tile_p = t % p.tiles_p, tile_q = t / p.tiles_p;
+            const int tile_p = (t % out_tiles) % p.tiles_p, tile_q = (t % out_tiles) / p.tiles_p;
+            const int out_row = tile_p * kBlockP + (t / out_tiles) * p.split_rows;
             const int buf = j & 1;
             if (ok && !mbar_wait(smem_u32(&bars[2 * kStages + buf]), (j >> 1) & 1, abort_flag)) {
                 if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, kErrEpilogueWait); }
@@ -741,8 +751,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                 group_sync();
                 if (leader) {
                     const int col = (EPI == kEpiSwiGLU) ? tile_q * (BLOCK_Q / 2) + c * 64 : tile_q * BLOCK_Q + c * 32;
-                    if (EPI == kEpiAddF32) tma_reduce_add_2d(&map_c, smem_u32(stg), col, tile_p * kBlockP);
-                    else tma_store_2d(&map_c, smem_u32(stg), col, tile_p * kBlockP);
+                    if (EPI == kEpiAddF32) tma_reduce_add_2d(&map_c, smem_u32(stg), col, out_row);
+                    else tma_store_2d(&map_c, smem_u32(stg), col, out_row);
                     bulk_commit();
                 }
             }
@@ -812,7 +822,7 @@ static int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, const
         if (e != cudaSuccess) { set_error("gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::kSmemBytes, cudaGetErrorString(e)); return 1; }
         configured = true;
     }
-    const int tiles = p.tiles_p * p.tiles_q;
+    const int tiles = p.tiles_p * p.tiles_q * p.splits;
     const int grid = tiles < sm_count() ? tiles : sm_count();
     launch_kernel((gemm_tc_persistent_kernel<BLOCK_Q, EPI>), dim3(grid), dim3(kPersistentThreads), Cfg::kSmemBytes, st, mp, mq, mc, p);
     return check_launch("gemm_tc_persistent");
@@ -990,12 +1000,35 @@ extern "C" int gi_gemm_tc_status(const void* status, void* stream, int* out) {
     return 0;
 }
 
+// C[m, n] (+)= ws[0][m][n] + ws[1][m][n] + ... in this order: the ranges of K of a split product.
+__global__ void reduce_splits_kernel(const float* __restrict__ ws, float* __restrict__ C, int M, int N4, long long ldc,
+                                     long long split_stride, int splits, int accumulate) {
+    pdl_prologue();
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= static_cast<long long>(M) * N4) return;
+    const int m = static_cast<int>(i / N4), n4 = static_cast<int>(i % N4);
+    float4* c = reinterpret_cast<float4*>(C + static_cast<long long>(m) * ldc) + n4;
+    const float4* w = reinterpret_cast<const float4*>(ws + static_cast<long long>(m) * N4 * 4) + n4;
+    float4 part[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+        part[s] = s < splits ? __ldcg(w + static_cast<long long>(s) * split_stride / 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 v = accumulate ? *c : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+        if (s < splits) { v.x += part[s].x; v.y += part[s].y; v.z += part[s].z; v.w += part[s].w; }
+    *c = v;
+}
+
 // Many tokens, one persistent CTA per SM. epilogue 0: C[M,N] = A W^T (32-bit); 1: C += A W^T (32-bit);
 // 2: W is [2N, K] = [gate; up] and C[M,N] = silu(A Wgate^T) * (A Wup^T) as bfloat16.
 // block_q: 256 or 128 accumulator columns per tile.
+// splits > 1 (epilogues 0 and 1, N a multiple of 4, at most 8): K is cut into ranges whose tiles are work
+// items of their own; their results go to `workspace` (splits x ceil(M / 128) x 128 x N floats) and a
+// second kernel adds them up in order into C. Few output tiles (a few hundred tokens) then still fill the GPU.
 extern "C" int gi_gemm_tc_persistent(const void* A, const void* W, void* C, int epilogue, int M, int N, int K,
                                      long long lda, long long ldw, long long ldc, int block_q, void* status,
-                                     void* stream) {
+                                     int splits, void* workspace, long long workspace_floats, void* stream) {
     if (M == 0 || N == 0) return 0;
     GI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: sizes must be positive (M=%d, N=%d, K=%d)", M, N, K);
     GI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
@@ -1012,10 +1045,33 @@ extern "C" int gi_gemm_tc_persistent(const void* A, const void* W, void* C, int 
     p.tiles_p = (M + kBlockP - 1) / kBlockP;
     p.up_row_offset = N;
     p.status = static_cast<int*>(status);
+    const int total_kb = (K + kBlockK - 1) / kBlockK;
+    p.splits = 1; p.kb_per_split = total_kb; p.split_rows = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
     CUtensorMap mp, mq, mc;
     if (make_map(&mp, A, M, K, lda, kBlockP)) return 1;
-    if (make_out_map(&mc, C, M, N, ldc, bf16_out)) return 1;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool split = splits > 1;
+    if (split) {
+        GI_REQUIRE(epilogue != kEpiSwiGLU && N % 4 == 0 && splits <= 8, "gemm_tc: a split over K needs a 32-bit output, N %% 4 == 0 and at most 8 ranges");
+        p.kb_per_split = (total_kb + splits - 1) / splits;
+        splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;             // every range holds at least one block
+        p.splits = splits;
+        p.split_rows = p.tiles_p * kBlockP;
+        const long long need = static_cast<long long>(splits) * p.split_rows * N;
+        GI_REQUIRE(workspace != nullptr && need <= workspace_floats, "gemm_tc: the workspace of %lld floats is too small for %lld", workspace_floats, need);
+        if (make_out_map(&mc, workspace, splits * p.split_rows, N, N, false)) return 1;
+    } else if (make_out_map(&mc, C, M, N, ldc, bf16_out)) {
+        return 1;
+    }
+    const int run_epilogue = split ? static_cast<int>(kEpiStoreF32) : epilogue;
+    auto finish = [&](int rc) -> int {
+        if (rc != 0 || !split) return rc;
+        const long long n = static_cast<long long>(M) * (N / 4);
+        launch_kernel((reduce_splits_kernel), dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, st,
+                      static_cast<const float*>(workspace), static_cast<float*>(C), M, N / 4, ldc,
+                      static_cast<long long>(p.split_rows) * N, splits, epilogue == kEpiAddF32 ? 1 : 0);
+        return check_launch("gemm_tc reduce");
+    };
     if (epilogue == kEpiSwiGLU) {
         p.tiles_q = (N + block_q / 2 - 1) / (block_q / 2);
         if (make_map(&mq, W, 2 * N, K, ldw, block_q / 2)) return 1;
@@ -1025,9 +1081,9 @@ extern "C" int gi_gemm_tc_persistent(const void* A, const void* W, void* C, int 
     p.tiles_q = (N + block_q - 1) / block_q;
     if (make_map(&mq, W, N, K, ldw, block_q)) return 1;
     if (block_q == 256) {
-        if (epilogue == kEpiAddF32) return launch_persistent<256, kEpiAddF32>(mp, mq, mc, p, st);
-        return launch_persistent<256, kEpiStoreF32>(mp, mq, mc, p, st);
+        if (run_epilogue == kEpiAddF32) return launch_persistent<256, kEpiAddF32>(mp, mq, mc, p, st);
+        return finish(launch_persistent<256, kEpiStoreF32>(mp, mq, mc, p, st));
     }
-    if (epilogue == kEpiAddF32) return launch_persistent<128, kEpiAddF32>(mp, mq, mc, p, st);
-    return launch_persistent<128, kEpiStoreF32>(mp, mq, mc, p, st);
+    if (run_epilogue == kEpiAddF32) return launch_persistent<128, kEpiAddF32>(mp, mq, mc, p, st);
+    return finish(launch_persistent<128, kEpiStoreF32>(mp, mq, mc, p, st));
 }

@@ -279,7 +279,17 @@ def gemm_tc_plan(M: int, N: int, K: int):
         while tiles * (splits + 1) <= 112 and k_blocks // (splits + 1) >= 4 and splits < 8:
             splits += 1
         return True, block_q, splits
-    return False, (256 if N >= 256 else 128 if N > 64 else 64), 1
+    block_q = 256 if N >= 256 else 128 if N > 64 else 64
+    splits = 1
+    if block_q >= 128 and N % 4 == 0:
+        # many tokens but few output tiles (a prompt portion of a few hundred tokens, a narrow matrix):
+        # K is cut as well so that about as many work items as SMs exist, each with at least 8 steps of 64
+        tiles = ((M + 127) // 128) * ((N + block_q - 1) // block_q)
+        k_blocks = (K + 63) // 64
+        splits = max(1, min(8, 148 // tiles, k_blocks // 8))
+        if splits < 3 and k_blocks < 64:
+            splits = 1           # measured: two ranges of a short K cost more (a second kernel adds them) than they save
+    return False, block_q, splits
 
 
 _cluster_splits_cache = {}
@@ -333,9 +343,15 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     st = _tc_state(a.device)
     if not swap and out.dtype is torch.float32 and N % 4 == 0 and block_q >= 128:
         # many tokens, 32-bit output: the persistent kernel (epilogue overlapped, TMA stores)
+        need = splits * ((M + 127) // 128 * 128) * N
+        if splits > 1 and need > st.workspace.numel():
+            splits = 1
         check(lib().gi_gemm_tc_persistent(_dev(a, "a", torch.bfloat16), _dev(w, "w", torch.bfloat16),
                                           _dev(out, "out", torch.float32), 1 if accumulate else 0, M, N, K, K, K, N,
-                                          block_q, st.status.data_ptr(), _stream()), "gemm_tc")
+                                          block_q, st.status.data_ptr(), splits, st.workspace.data_ptr(),
+                                          st.workspace.numel(), _stream()), "gemm_tc")
+        if splits > 1:
+            count_launches(1)     # the kernel that adds the ranges up
         return
     check(lib().gi_gemm_tc(_dev(a, "a", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"),
                            dtype_code(out.dtype), int(accumulate), M, N, K, K, K, N, int(swap), block_q, splits,
@@ -359,7 +375,7 @@ def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> 
     st = _tc_state(a.device)
     check(lib().gi_gemm_tc_persistent(_dev(a, "a", torch.bfloat16), _dev(w_gate_up, "w_gate_up", torch.bfloat16),
                                       _dev(out, "out", torch.bfloat16), 2, M, I, K, K, K, I, 256,
-                                      st.status.data_ptr(), _stream()), "gemm_swiglu")
+                                      st.status.data_ptr(), 1, 0, 0, _stream()), "gemm_swiglu")
 
 
 def gemm_tc_status(device: torch.device) -> int:

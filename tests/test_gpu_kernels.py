@@ -455,6 +455,34 @@ def test_gemm_persistent_many_tiles(M, N, K_, block_q):
     assert K().gemm_tc_status(torch.device(DEV)) == 0
 
 
+@pytest.mark.parametrize("M,N,K_,block_q,splits", [(512, 2048, 2048, 256, 4), (300, 520, 1032, 256, 3), (130, 256, 520, 256, 2),
+                                                   (256, 2048, 8192, 256, 8), (517, 384, 1600, 128, 5), (200, 260, 136, 256, 8)])
+def test_gemm_persistent_split_over_k(M, N, K_, block_q, splits):
+    """Few output tiles: K is cut into ranges that are work items of their own, added up in order by
+    a second kernel; a last range that is shorter, more ranges asked for than blocks exist."""
+    g = torch.Generator().manual_seed(19)
+    a = torch.randn(M, K_, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(N, K_, generator=g).to(torch.bfloat16).to(DEV)
+    want = a.float().cpu().double() @ w.float().cpu().double().T
+    guard = torch.full((M + 2, N), -1024.0, device=DEV)
+    out = guard[1:M + 1]
+    out.fill_(float("nan"))
+    K().gemm_tc(a, w, out, plan=(False, block_q, splits))
+    close(out, want, "float32", "persistent split store", f32_tol=2e-6 * max(1, K_ / 64))
+    assert float(guard[0].min()) == -1024.0 == float(guard[-1].max()), "wrote outside the output"
+    base = torch.randn(M, N, generator=g).to(DEV)
+    acc = base.clone()
+    K().gemm_tc(a, w, acc, accumulate=True, plan=(False, block_q, splits))
+    close(acc, want + base.cpu().double(), "float32", "persistent split add", f32_tol=2e-6 * max(1, K_ / 64))
+    again = base.clone()
+    K().gemm_tc(a, w, again, accumulate=True, plan=(False, block_q, splits))
+    assert torch.equal(again, acc), "two runs differ"
+    auto = torch.empty(M, N, device=DEV)
+    K().gemm_tc(a, w, auto)
+    close(auto, want, "float32", "persistent auto plan", f32_tol=2e-6 * max(1, K_ / 64))
+    assert K().gemm_tc_status(torch.device(DEV)) == 0
+
+
 @pytest.mark.parametrize("H,Hkv,hd,ps", [(8, 2, 64, 16), (32, 8, 64, 16), (3, 1, 64, 8), (8, 2, 128, 32), (5, 5, 64, 16), (4, 4, 128, 128)])
 def test_attention_tcgen05_prefill(H, Hkv, hd, ps):
     """The tcgen05 prefill kernel: whole prompts of several key tiles, a portion deep in a context
