@@ -266,30 +266,46 @@ def _tc_state(device: torch.device) -> _TensorCoreState:
     return _tc_states[key]
 
 
-def gemm_tc_plan(M: int, N: int, K: int):
-    """(swap, block_q, splits) for a product of these sizes. Few tokens put the weights on the
-    128-row side and split K until the grid fills the GPU; the choice depends on the sizes only."""
-    if M <= 128:
-        block_q = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
-        tiles = (N + 127) // 128
-        k_blocks = (K + 63) // 64
-        # split K until about 100 CTAs stream weights, keeping at least 4 steps of 64 per CTA
-        # (measured on B200 at the Llama-3.2-1B widths: 4 splits for 24 tiles, 6..8 for 16, 1 for 128)
-        splits = 1
-        while tiles * (splits + 1) <= 112 and k_blocks // (splits + 1) >= 4 and splits < 8:
-            splits += 1
-        return True, block_q, splits
+def _persistent_plan(M: int, N: int, K: int):
     block_q = 256 if N >= 256 else 128 if N > 64 else 64
     splits = 1
     if block_q >= 128 and N % 4 == 0:
-        # many tokens but few output tiles (a prompt portion of a few hundred tokens, a narrow matrix):
-        # K is cut as well so that about as many work items as SMs exist, each with at least 8 steps of 64
+        # few output tiles (a prompt portion of a few hundred tokens, a narrow matrix): K is cut as well
+        # so that about as many work items as SMs exist, each with at least 8 steps of 64
         tiles = ((M + 127) // 128) * ((N + block_q - 1) // block_q)
         k_blocks = (K + 63) // 64
         splits = max(1, min(8, 148 // tiles, k_blocks // 8))
         if splits < 3 and k_blocks < 64:
             splits = 1           # measured: two ranges of a short K cost more (a second kernel adds them) than they save
     return False, block_q, splits
+
+
+def gemm_tc_plan(M: int, N: int, K: int):
+    """(swap, block_q, splits) for a product of these sizes; the choice depends on the sizes only.
+    Few tokens put the weights on the 128-row side (the tokens are the N of the MMA) and split K until
+    the grid fills the GPU. Many tokens put the tokens on the 128-row side, one persistent CTA per SM,
+    K cut into ranges when the output has few tiles. Between 33 and 128 tokens a narrow matrix (one
+    that the first form would split) is faster in the second form, whose ranges are added up by a
+    kernel of their own instead of by one CTA per tile (measured at the Llama-3.2-1B widths: the O
+    product of 128 tokens 25 -> 10.5 us, the down product 30 -> 17 us)."""
+    if M <= 128:
+        swap, block_q, splits = _swap_plan(M, N, K)
+        if M > 32 and N >= 256 and N % 4 == 0 and (splits >= 6 or (M > 64 and splits > 1)):
+            return _persistent_plan(M, N, K)
+        return swap, block_q, splits
+    return _persistent_plan(M, N, K)
+
+
+def _swap_plan(M: int, N: int, K: int):
+    block_q = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+    tiles = (N + 127) // 128
+    k_blocks = (K + 63) // 64
+    # split K until about 100 CTAs stream weights, keeping at least 4 steps of 64 per CTA
+    # (measured on B200 at the Llama-3.2-1B widths: 4 splits for 24 tiles, 6..8 for 16, 1 for 128)
+    splits = 1
+    while tiles * (splits + 1) <= 112 and k_blocks // (splits + 1) >= 4 and splits < 8:
+        splits += 1
+    return True, block_q, splits
 
 
 _cluster_splits_cache = {}
@@ -338,10 +354,16 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     if w.shape[1] != K or out.shape != (M, N):
         raise KernelError(f"gemm: shapes do not agree (a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)})")
     swap, block_q, splits = plan or gemm_tc_plan(M, N, K)
-    if plan is None and splits > 1:
+    persistent = not swap and out.dtype is torch.float32 and N % 4 == 0 and block_q >= 128
+    if not swap and not persistent:
+        if plan is None and M <= 128:
+            swap, block_q, splits = _swap_plan(M, N, K)      # the persistent kernel cannot write this output
+        else:
+            splits = 1
+    if plan is None and swap and splits > 1:
         splits = gemm_tc_cluster_splits(block_q, (N + 127) // 128, splits, w_tiles is not None and block_q <= 128)
     st = _tc_state(a.device)
-    if not swap and out.dtype is torch.float32 and N % 4 == 0 and block_q >= 128:
+    if persistent:
         # many tokens, 32-bit output: the persistent kernel (epilogue overlapped, TMA stores)
         need = splits * ((M + 127) // 128 * 128) * N
         if splits > 1 and need > st.workspace.numel():
