@@ -162,6 +162,25 @@ struct TcConfig {
                                        (static_cast<uint32_t>(kBlockP >> 4) << 24);
 };
 
+// Rotation of query and key heads and the store of keys and values into the request's pages, done
+// by the epilogue of the product that makes [q; k; v] (the rows of W are H query heads, Hkv key heads,
+// Hkv value heads of hd features each): q goes to q_out [tokens, H * hd], k and v of token t to its
+// page (block_tables[row_req[t]][pos / page_size]) in caches of [pages, Hkv, page_size, hd]; all
+// bfloat16. cos/sin: tables [max position, rot_half] in 32-bit (null: no rotation).
+struct RopeStoreParams {
+    const int* positions;
+    const int* row_req;
+    const int* block_tables;
+    int table_stride;
+    const float* cos_t;
+    const float* sin_t;
+    int rot_half, interleaved;
+    __nv_bfloat16* q_out;
+    __nv_bfloat16* k_cache;
+    __nv_bfloat16* v_cache;
+    int H, Hkv, hd, page_size, write_kv;
+};
+
 struct TcParams {
     void* C;
     int c_bf16;              // 0: C is float, 1: C is bfloat16
@@ -179,6 +198,8 @@ struct TcParams {
     const uint8_t* p_tiles;  // TILED kernels: the 128-row operand tile by tile, [row tile][K block][128][64] with the
                              // 128-byte swizzle applied and K padded to a multiple of 128 (tile_weight in ops/kernels.py)
     int tiles_kb;            // 64-wide blocks of K in a row of tiles
+    int rope_on;             // the product is [q; k; v] (weights on the 128-row side): the CTA that holds a tile's sum
+    RopeStoreParams rope;    //   rotates it and stores queries, keys and values instead of writing C
 };
 
 template <int BLOCK_Q>
@@ -365,6 +386,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 16; ++j) old_c[j] = (j < n) ? __ldcg(c + j * p.stride_q) : 0.f;
         }
+        // Rotation and store: thread j < BLOCK_Q looks up the position and the page row of token j of the
+        // tile now, while the products run.
+        int tok_pos = 0;
+        long long tok_base = -1;
+        if (p.rope_on && row_in_tile < BLOCK_Q) {
+            const int tok = tile_q * BLOCK_Q + row_in_tile;
+            if (tok < p.rows_q) {
+                tok_pos = p.rope.positions[tok];
+                if (p.rope.write_kv) {
+                    const int page = p.rope.block_tables[static_cast<size_t>(p.rope.row_req[tok]) * p.rope.table_stride + tok_pos / p.rope.page_size];
+                    tok_base = (static_cast<long long>(page) * p.rope.Hkv * p.rope.page_size + (tok_pos % p.rope.page_size)) * p.rope.hd;
+                }
+            }
+        }
+        // The pipeline's stages are free once the accumulator is complete: the finished tile is laid
+        // there as [token][128 rows] so that a thread can read its rotation partner's value.
+        float* xch = reinterpret_cast<float*>(smem);
+        bool emitted = false;
+        auto emit = [&](int c, const float* v) {          // the final values of columns c * 16 .. of this thread's row
+            if (p.rope_on) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) xch[(c * 16 + j) * kBlockP + row_in_tile] = v[j];
+                emitted = true;
+            } else {
+                store_row_chunk<BLOCK_Q>(p, row_p, tile_q * BLOCK_Q + c * 16, v);
+            }
+        };
         bool have = n_kb > 0;
         if (have && !mbar_wait(smem_u32(&bars[2 * kStages]), 0, abort_flag)) {
             if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, kErrEpilogueWait); }
@@ -422,7 +470,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                             for (int j = 0; j < 16; ++j) v[j] += part[(c * 16 + j) * kBlockP + row_in_tile];
                         }
                         if (early_old) store_row_chunk_old(p, row_p, tile_q * BLOCK_Q, v, old_c);
-                        else store_row_chunk<BLOCK_Q>(p, row_p, tile_q * BLOCK_Q + c * 16, v);
+                        else emit(c, v);
                     }
                 }
             }
@@ -442,7 +490,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                         for (int j = 0; j < 16; ++j) v[j] = 0.f;
                     }
                     if (early_old) store_row_chunk_old(p, row_p, tile_q * BLOCK_Q, v, old_c);
-                    else store_row_chunk<BLOCK_Q>(p, row_p, tile_q * BLOCK_Q + c * 16, v);
+                    else emit(c, v);
                 }
             } else {
                 // partial tile -> workspace [tile][split][q][128 rows]; the last CTA of the tile sums all splits
@@ -493,8 +541,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                                     for (int j = 0; j < 16; ++j) v[j] += part[ds][j];
                                 }
                         }
-                        store_row_chunk<BLOCK_Q>(p, row_p, tile_q * BLOCK_Q + c * 16, v);
+                        emit(c, v);
                     }
+                }
+            }
+        }
+        if (p.rope_on) {
+            const RopeStoreParams& rp = p.rope;
+            int* tpos = reinterpret_cast<int*>(xch + BLOCK_Q * kBlockP);
+            long long* tbase = reinterpret_cast<long long*>(tpos + BLOCK_Q);
+            if (row_in_tile < BLOCK_Q) { tpos[row_in_tile] = tok_pos; tbase[row_in_tile] = tok_base; }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (emitted && row_p < p.rows_p) {
+                // this thread's row is feature d of one head; its partner in a rotated pair lies in the same tile
+                const int hd = rp.hd, head = row_p / hd, d = row_p - head * hd;
+                const bool is_q = head < rp.H, is_k = !is_q && head < rp.H + rp.Hkv;
+                const int rh = rp.cos_t ? rp.rot_half : 0;
+                const bool rotate = (is_q || is_k) && d < 2 * rh;
+                int partner = row_in_tile, ci = 0;
+                bool first = true;                       // first member of the pair: a c - b s; second: a s + b c
+                if (rotate) {
+                    if (rp.interleaved) { first = (d & 1) == 0; partner = row_in_tile ^ 1; ci = d >> 1; }
+                    else { first = d < rh; partner = first ? row_in_tile + rh : row_in_tile - rh; ci = first ? d : d - rh; }
+                }
+                const int n_tok = min(BLOCK_Q, p.rows_q - tile_q * BLOCK_Q);
+                const size_t kv_head = static_cast<size_t>(is_q ? 0 : (is_k ? head - rp.H : head - rp.H - rp.Hkv)) * rp.page_size * hd + d;
+                __nv_bfloat16* cache = is_k ? rp.k_cache : rp.v_cache;
+#pragma unroll 4
+                for (int j = 0; j < n_tok; ++j) {
+                    float out = xch[j * kBlockP + row_in_tile];
+                    if (rotate) {
+                        const float other = xch[j * kBlockP + partner];
+                        const size_t at = static_cast<size_t>(tpos[j]) * rh + ci;
+                        const float ck = __ldg(rp.cos_t + at), sk = __ldg(rp.sin_t + at);
+                        out = first ? out * ck - other * sk : other * sk + out * ck;
+                    }
+                    if (is_q) rp.q_out[(static_cast<size_t>(tile_q * BLOCK_Q + j) * rp.H + head) * hd + d] = __float2bfloat16_rn(out);
+                    else if (tbase[j] >= 0) cache[tbase[j] + kv_head] = __float2bfloat16_rn(out);
                 }
             }
         }
@@ -514,7 +597,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 // Epilogues: store 32-bit, add to 32-bit, or SwiGLU: the tile's first half of columns are gate
 // channels and the second half the matching up channels (two TMA loads per stage from the
 // [gate; up] weight), and silu(gate) * up is stored as bfloat16.
-enum TcEpilogue : int { kEpiStoreF32 = 0, kEpiAddF32 = 1, kEpiSwiGLU = 2 };
+enum TcEpilogue : int { kEpiStoreF32 = 0, kEpiAddF32 = 1, kEpiSwiGLU = 2, kEpiRopeStore = 3 };
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -554,6 +637,7 @@ struct TcPersistentParams {
     int splits;                  // K is cut into this many ranges, each an accumulator tile of its own whose result is
     int kb_per_split;            //   stored split_rows rows further down in the output (a workspace; the ranges are
     int split_rows;              //   added up, in order, by reduce_splits_kernel): few tiles still fill the GPU
+    RopeStoreParams rope;        // epilogue kEpiRopeStore
 };
 
 constexpr int kPersistentThreads = 64 + 2 * 128;     // producer warp, MMA warp, two epilogue groups of four warps
@@ -689,6 +773,33 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
             const int tile_p = (t % out_tiles) % p.tiles_p, tile_q = (t % out_tiles) / p.tiles_p;
             const int out_row = tile_p * kBlockP + (t / out_tiles) * p.split_rows;
             const int buf = j & 1;
+            // Rotation and store: the token's position, its page row and the first cos/sin values are
+            // requested now, while the tile's products still run.
+            int rope_token = 0;
+            size_t rope_kv_base = 0;
+            const float *rope_cs = nullptr, *rope_sn = nullptr;
+            float4 rope_c[4], rope_s[4];
+            if constexpr (EPI == kEpiRopeStore) {
+                const RopeStoreParams& rp = p.rope;
+                rope_token = out_row + row;
+                int pos = 0;
+                if (rope_token < p.rows_p) {
+                    pos = rp.positions[rope_token];
+                    if (rp.write_kv) {
+                        const int page = rp.block_tables[static_cast<size_t>(rp.row_req[rope_token]) * rp.table_stride + pos / rp.page_size];
+                        rope_kv_base = (static_cast<size_t>(page) * rp.Hkv * rp.page_size + (pos % rp.page_size)) * rp.hd;
+                    }
+                }
+                if (rp.cos_t) {
+                    rope_cs = rp.cos_t + static_cast<size_t>(pos) * (rp.hd >> 1);
+                    rope_sn = rp.sin_t + static_cast<size_t>(pos) * (rp.hd >> 1);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        rope_c[q4] = __ldg(reinterpret_cast<const float4*>(rope_cs) + q4);
+                        rope_s[q4] = __ldg(reinterpret_cast<const float4*>(rope_sn) + q4);
+                    }
+                }
+            }
             if (ok && !mbar_wait(smem_u32(&bars[2 * kStages + buf]), (j >> 1) & 1, abort_flag)) {
                 if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, kErrEpilogueWait); }
             }
@@ -698,6 +809,73 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
             if (!ok) break;
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + buf * BLOCK_Q + lane_addr;
+            if constexpr (EPI == kEpiRopeStore) {
+                // A thread holds one token's row of the tile: whole heads (BLOCK_Q is a multiple of the head
+                // size), so both members of a rotated pair (d, d + hd/2) are its own. 16 pairs at a time:
+                // their cos/sin are read once and serve all heads of the tile that this group takes.
+                const RopeStoreParams& rp = p.rope;
+                const int hd = rp.hd, half = hd >> 1;
+                const int heads_per_tile = BLOCK_Q / hd;
+                if (group >= heads_per_tile) {
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf]));
+                }
+                const bool valid = rope_token < p.rows_p;
+                for (int j = 0; j < half; j += 16) {
+                    if (j > 0 && rope_cs != nullptr) {
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            rope_c[q4] = __ldg(reinterpret_cast<const float4*>(rope_cs + j) + q4);
+                            rope_s[q4] = __ldg(reinterpret_cast<const float4*>(rope_sn + j) + q4);
+                        }
+                    }
+                    const bool last_j = j + 16 >= half;
+                    for (int hh = group; hh < heads_per_tile; hh += 2) {
+                        const int head = tile_q * heads_per_tile + hh;
+                        __nv_bfloat16* dst = nullptr;
+                        if (valid) {
+                            if (head < rp.H) dst = rp.q_out + (static_cast<size_t>(rope_token) * rp.H + head) * hd;
+                            else if (!rp.write_kv) dst = nullptr;
+                            else if (head < rp.H + rp.Hkv) dst = rp.k_cache + rope_kv_base + static_cast<size_t>(head - rp.H) * rp.page_size * hd;
+                            else if (head < rp.H + 2 * rp.Hkv) dst = rp.v_cache + rope_kv_base + static_cast<size_t>(head - rp.H - rp.Hkv) * rp.page_size * hd;
+                        }
+                        const bool rotate = rope_cs != nullptr && head < rp.H + rp.Hkv;
+                        uint32_t lo[16], hi[16];
+                        tmem_ld_x16(tmem_d + hh * hd + j, lo);
+                        tmem_ld_x16(tmem_d + hh * hd + half + j, hi);
+                        tmem_ld_wait();
+                        if (last_j && hh + 2 >= heads_per_tile) { tc_fence_before(); mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf])); }
+                        if (dst == nullptr) continue;
+                        uint32_t oa[8], ob[8];
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            const float cc[4] = {rope_c[q4].x, rope_c[q4].y, rope_c[q4].z, rope_c[q4].w};
+                            const float ss[4] = {rope_s[q4].x, rope_s[q4].y, rope_s[q4].z, rope_s[q4].w};
+                            float ra[4], rb[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float a = __uint_as_float(lo[q4 * 4 + e]), b = __uint_as_float(hi[q4 * 4 + e]);
+                                ra[e] = rotate ? a * cc[e] - b * ss[e] : a;
+                                rb[e] = rotate ? a * ss[e] + b * cc[e] : b;
+                            }
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                __nv_bfloat162 pa = __floats2bfloat162_rn(ra[2 * e], ra[2 * e + 1]);
+                                __nv_bfloat162 pb = __floats2bfloat162_rn(rb[2 * e], rb[2 * e + 1]);
+                                oa[q4 * 2 + e] = *reinterpret_cast<uint32_t*>(&pa);
+                                ob[q4 * 2 + e] = *reinterpret_cast<uint32_t*>(&pb);
+                            }
+                        }
+                        uint4* da = reinterpret_cast<uint4*>(dst + j);
+                        uint4* db = reinterpret_cast<uint4*>(dst + half + j);
+                        da[0] = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+                        da[1] = make_uint4(oa[4], oa[5], oa[6], oa[7]);
+                        db[0] = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+                        db[1] = make_uint4(ob[4], ob[5], ob[6], ob[7]);
+                    }
+                }
+                continue;
+            }
             constexpr int kChunks = (EPI == kEpiSwiGLU) ? BLOCK_Q / 128 : BLOCK_Q / 32;   // TMA stores per tile
             if (group >= kChunks) {                               // a tile with a single chunk: this group has nothing to read
                 tc_fence_before();
@@ -928,10 +1106,10 @@ extern "C" int gi_gemm_tc_cluster_capacity(int block_q, int splits, int tiled) {
     }
 }
 
-extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int accumulate, int M, int N, int K,
-                          long long lda, long long ldw, long long ldc, int swap, int block_q, int splits,
-                          void* workspace, long long workspace_floats, void* counters, int n_counters, void* status,
-                          const void* w_tiles, void* stream) {
+static int run_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int accumulate, int M, int N, int K,
+                       long long lda, long long ldw, long long ldc, int swap, int block_q, int splits,
+                       void* workspace, long long workspace_floats, void* counters, int n_counters, void* status,
+                       const void* w_tiles, const RopeStoreParams* rope, void* stream) {
     if (M == 0 || N == 0) return 0;
     GI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: sizes must be positive (M=%d, N=%d, K=%d)", M, N, K);
     GI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
@@ -945,7 +1123,12 @@ extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
     GI_REQUIRE(splits >= 1, "gemm_tc: splits must be >= 1");
     GI_REQUIRE(status != nullptr, "gemm_tc: a status word is required");
 
-    TcParams p;
+    TcParams p = {};
+    if (rope) {
+        GI_REQUIRE(swap && block_q <= 128 && !accumulate, "gemm_tc rope: needs the weights on the 128-row side");
+        p.rope_on = 1;
+        p.rope = *rope;
+    }
     p.C = C;
     p.c_bf16 = c_dtype == kBF16;
     p.accumulate = accumulate;
@@ -990,6 +1173,36 @@ extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
         case 128: return tiled ? launch_tc<128, true>(mp, mq, p, grid, st) : launch_tc<128, false>(mp, mq, p, grid, st);
         default: return launch_tc<256, false>(mp, mq, p, grid, st);
     }
+}
+
+extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int accumulate, int M, int N, int K,
+                          long long lda, long long ldw, long long ldc, int swap, int block_q, int splits,
+                          void* workspace, long long workspace_floats, void* counters, int n_counters, void* status,
+                          const void* w_tiles, void* stream) {
+    return run_gemm_tc(A, W, C, c_dtype, accumulate, M, N, K, lda, ldw, ldc, swap, block_q, splits, workspace,
+                       workspace_floats, counters, n_counters, status, w_tiles, nullptr, stream);
+}
+
+// The [q; k; v] product of few tokens (at most block_q <= 128, weights on the 128-row side) with rotation
+// and page store done by the CTA that holds a tile's sum (RopeStoreParams). The head size must divide 128
+// so that both members of a rotated pair lie in one tile; any rotary size and pairing.
+extern "C" int gi_gemm_tc_rope(const void* A, const void* W, int M, int K, long long lda, long long ldw, int block_q,
+                               int splits, void* workspace, long long workspace_floats, void* counters, int n_counters,
+                               void* status, const void* w_tiles, const int* positions, const int* row_req,
+                               const int* block_tables, int table_stride, const float* cos_t, const float* sin_t,
+                               int rot_half, int interleaved, void* q_out, void* k_cache, void* v_cache, int H, int Hkv,
+                               int hd, int page_size, int write_kv, void* stream) {
+    GI_REQUIRE(H > 0 && Hkv > 0 && hd > 0 && page_size > 0, "gemm_tc rope: sizes must be positive");
+    GI_REQUIRE(kBlockP % hd == 0, "gemm_tc rope: the head size %d does not divide %d", hd, kBlockP);
+    GI_REQUIRE(M <= block_q || block_q == 128, "gemm_tc rope: block_q=%d is too small for %d tokens", block_q, M);
+    GI_REQUIRE(cos_t == nullptr || (sin_t != nullptr && rot_half > 0 && 2 * rot_half <= hd),
+               "gemm_tc rope: rotary size %d does not fit the head size %d", 2 * rot_half, hd);
+    RopeStoreParams rope{positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved,
+                         static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
+                         static_cast<__nv_bfloat16*>(v_cache), H, Hkv, hd, page_size, write_kv};
+    const int N = (H + 2 * Hkv) * hd;
+    return run_gemm_tc(A, W, nullptr, kF32, 0, M, N, K, lda, ldw, N, 1, block_q, splits, workspace, workspace_floats,
+                       counters, n_counters, status, w_tiles, &rope, stream);
 }
 
 // Reads the status word (synchronises the stream): 0 = no bounded wait ever gave up.
@@ -1040,7 +1253,7 @@ extern "C" int gi_gemm_tc_persistent(const void* A, const void* W, void* C, int 
                (reinterpret_cast<uintptr_t>(C) % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
     GI_REQUIRE(block_q == 128 || block_q == 256, "gemm_tc: block_q=%d is not 128 or 256", block_q);
     GI_REQUIRE(status != nullptr, "gemm_tc: a status word is required");
-    TcPersistentParams p;
+    TcPersistentParams p = {};
     p.rows_p = M; p.rows_q = N; p.K = K;
     p.tiles_p = (M + kBlockP - 1) / kBlockP;
     p.up_row_offset = N;
@@ -1086,4 +1299,42 @@ extern "C" int gi_gemm_tc_persistent(const void* A, const void* W, void* C, int 
     }
     if (run_epilogue == kEpiAddF32) return launch_persistent<128, kEpiAddF32>(mp, mq, mc, p, st);
     return finish(launch_persistent<128, kEpiStoreF32>(mp, mq, mc, p, st));
+}
+
+// The [q; k; v] product of many tokens with rotation and page store in its epilogue (RopeStoreParams):
+// A [M, K] bfloat16 activations, W [(H + 2 Hkv) * hd, K]; nothing else is written. Head sizes 32, 64, 128
+// with the whole head rotated (rot_half = hd / 2) in the half-split pairing, or no rotation at all.
+extern "C" int gi_gemm_tc_persistent_rope(const void* A, const void* W, int M, int K, long long lda, long long ldw,
+                                          const int* positions, const int* row_req, const int* block_tables,
+                                          int table_stride, const float* cos_t, const float* sin_t, int rot_half,
+                                          int interleaved, void* q_out, void* k_cache, void* v_cache, int H, int Hkv,
+                                          int hd, int page_size, int write_kv, void* status, void* stream) {
+    if (M == 0) return 0;
+    GI_REQUIRE(M > 0 && K > 0 && H > 0 && Hkv > 0 && page_size > 0, "gemm_tc rope: sizes must be positive");
+    GI_REQUIRE(hd == 32 || hd == 64 || hd == 128, "gemm_tc rope: head size %d is not 32, 64 or 128", hd);
+    GI_REQUIRE(cos_t == nullptr || (sin_t != nullptr && !interleaved && rot_half * 2 == hd),
+               "gemm_tc rope: only whole heads in the half-split pairing are rotated here (rot_half=%d, hd=%d, interleaved=%d)",
+               rot_half, hd, interleaved);
+    GI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
+               "gemm_tc: K=%d and the row strides (%lld, %lld) must be multiples of 8 (16-byte rows for TMA)", K, lda, ldw);
+    GI_REQUIRE((reinterpret_cast<uintptr_t>(A) % 16 == 0) && (reinterpret_cast<uintptr_t>(W) % 16 == 0) &&
+               (reinterpret_cast<uintptr_t>(q_out) % 16 == 0) && (reinterpret_cast<uintptr_t>(k_cache) % 16 == 0) &&
+               (reinterpret_cast<uintptr_t>(v_cache) % 16 == 0) &&
+               (cos_t == nullptr || (reinterpret_cast<uintptr_t>(cos_t) % 16 == 0 && reinterpret_cast<uintptr_t>(sin_t) % 16 == 0)),
+               "gemm_tc rope: operands must be 16-byte aligned");
+    GI_REQUIRE(status != nullptr, "gemm_tc: a status word is required");
+    const int N = (H + 2 * Hkv) * hd;
+    TcPersistentParams p = {};
+    p.rows_p = M; p.rows_q = N; p.K = K;
+    p.tiles_p = (M + kBlockP - 1) / kBlockP;
+    p.tiles_q = (N + 255) / 256;
+    p.up_row_offset = 0;
+    p.status = static_cast<int*>(status);
+    p.splits = 1; p.kb_per_split = (K + kBlockK - 1) / kBlockK; p.split_rows = 0;
+    p.rope = RopeStoreParams{positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved,
+                             static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
+                             static_cast<__nv_bfloat16*>(v_cache), H, Hkv, hd, page_size, write_kv};
+    CUtensorMap mp, mq;
+    if (make_map(&mp, A, M, K, lda, kBlockP) || make_map(&mq, W, N, K, ldw, 256)) return 1;
+    return launch_persistent<256, kEpiRopeStore>(mp, mq, mp /* no TMA store */, p, static_cast<cudaStream_t>(stream));
 }

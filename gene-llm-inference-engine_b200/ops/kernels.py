@@ -400,6 +400,65 @@ def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> 
                                       st.status.data_ptr(), 1, 0, 0, _stream()), "gemm_swiglu")
 
 
+_ROPE_FEW_TOKENS = 64      # up to here the few-token product (weights on the 128-row side) does the rotation
+
+
+def gemm_rope_store_supported(M: int, K: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                              cos: Optional[torch.Tensor], interleaved: bool) -> bool:
+    """Whether the [q; k; v] product of M tokens can rotate and store in its own epilogue. Few tokens: the
+    head size must divide 128 (both members of a pair in one tile of weight rows), any rotation. Many
+    tokens: head sizes 32, 64, 128, whole heads rotated in the half-split pairing (or no rotation), and
+    enough output tiles that K is not cut into ranges. Between the two, and otherwise, the product and
+    the rope+store kernel run one after the other."""
+    if K % 8:
+        return False
+    if M <= _ROPE_FEW_TOKENS:
+        return 128 % head_dim == 0
+    if head_dim not in (32, 64, 128) or not (cos is None or (not interleaved and 2 * cos.shape[1] == head_dim)):
+        return False
+    N = (num_heads + 2 * num_kv_heads) * head_dim
+    return M > 128 and _persistent_plan(M, N, K)[2] == 1
+
+
+def gemm_rope_store(a: torch.Tensor, w_qkv: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor,
+                    block_tables: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                    interleaved: bool, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, write_kv: bool = True,
+                    w_tiles: Optional[torch.Tensor] = None) -> None:
+    """``rope_store`` of ``a @ w_qkv^T`` in one tensor-core kernel: the product's epilogue rotates the
+    query and key heads and writes queries to ``q_out`` and keys/values into the pages; the
+    [T, (H+2Hkv)*hd] intermediate never exists in memory. All operands bfloat16."""
+    M, K = a.shape
+    N = (num_heads + 2 * num_kv_heads) * head_dim
+    if w_qkv.shape != (N, K):
+        raise KernelError("gemm_rope_store: the weight must be [(H+2Hkv)*hd, K]")
+    if q_out.shape != (M, num_heads * head_dim):
+        raise KernelError("gemm_rope_store: q_out must be [T, H*hd]")
+    if k_cache.shape[1:] != (num_kv_heads, page_size, head_dim) or v_cache.shape != k_cache.shape:
+        raise KernelError("gemm_rope_store: the cache must be [pages, Hkv, page_size, hd]")
+    if cos is not None and (sin is None or sin.shape != cos.shape):
+        raise KernelError("gemm_rope_store: cos and sin tables must have one shape")
+    if not gemm_rope_store_supported(M, K, num_heads, num_kv_heads, head_dim, cos, interleaved):
+        raise KernelError(f"gemm_rope_store: not built for {M} tokens, head size {head_dim} and this rotation")
+    st = _tc_state(a.device)
+    rope_args = (_dev(positions, "positions", torch.int32), _dev(row_req, "row_req", torch.int32),
+                 _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1], _opt(cos, "cos", torch.float32),
+                 _opt(sin, "sin", torch.float32), 0 if cos is None else cos.shape[1], int(interleaved),
+                 _dev(q_out, "q_out", torch.bfloat16), _dev(k_cache, "k_cache", torch.bfloat16),
+                 _dev(v_cache, "v_cache", torch.bfloat16), num_heads, num_kv_heads, head_dim, page_size, int(write_kv))
+    if M <= _ROPE_FEW_TOKENS:
+        _, block_q, splits = _swap_plan(M, N, K)
+        if splits > 1:
+            splits = gemm_tc_cluster_splits(block_q, (N + 127) // 128, splits, w_tiles is not None)
+        check(lib().gi_gemm_tc_rope(_dev(a, "a", torch.bfloat16), _dev(w_qkv, "w_qkv", torch.bfloat16), M, K, K, K, block_q,
+                                    splits, st.workspace.data_ptr(), st.workspace.numel(), st.counters.data_ptr(),
+                                    st.counters.numel(), st.status.data_ptr(), _opt(w_tiles, "w_tiles", torch.bfloat16),
+                                    *rope_args, _stream()), "gemm_rope_store")
+    else:
+        check(lib().gi_gemm_tc_persistent_rope(_dev(a, "a", torch.bfloat16), _dev(w_qkv, "w_qkv", torch.bfloat16), M, K, K, K,
+                                               *rope_args, st.status.data_ptr(), _stream()), "gemm_rope_store")
+
+
 def gemm_tc_status(device: torch.device) -> int:
     """0 when no bounded wait of a tensor-core kernel ever gave up on this device (synchronises)."""
     import ctypes

@@ -33,6 +33,12 @@ _SIGNATURES = {
                    c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
     "gi_gemm_tc_persistent": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                               c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p],
+    "gi_gemm_tc_persistent_rope": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
+                                   c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                   c_int, c_int, c_int, c_void_p, c_void_p],
+    "gi_gemm_tc_rope": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_void_p, c_longlong,
+                        c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                        c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "gi_gemm_tc_status": [c_void_p, c_void_p, c_void_p],
     "gi_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                             c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_longlong,

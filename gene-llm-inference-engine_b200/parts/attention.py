@@ -79,12 +79,19 @@ class AttentionMixer:
         H, Hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         k_cache, v_cache = ctx.pages(run.cache_layer)
         tables = ctx.block_tables(run.cache_layer)
-        qkv = ctx.scratch("qkv", (T, (H + 2 * Hkv) * hd), torch.float32)
-        self.w_qkv.forward(xn, qkv)
         q = ctx.scratch("q", (T, H * hd), self.dtype)
-        kernels.rope_store(qkv, ctx.positions, ctx.row_req, tables, self.position.cos, self.position.sin,
-                           self.position.interleaved, q, k_cache, v_cache, H, Hkv, hd, ctx.page_size,
-                           write_kv=run.writes_cache)
+        if self.dtype is torch.bfloat16 and kernels.gemm_rope_store_supported(
+                T, self.hidden_size, H, Hkv, hd, self.position.cos, self.position.interleaved):
+            # rotation and page store in the epilogue of the product
+            kernels.gemm_rope_store(xn, self.w_qkv.weight, ctx.positions, ctx.row_req, tables, self.position.cos,
+                                    self.position.sin, self.position.interleaved, q, k_cache, v_cache, H, Hkv, hd,
+                                    ctx.page_size, write_kv=run.writes_cache, w_tiles=self.w_qkv.weight_tiles)
+        else:
+            qkv = ctx.scratch("qkv", (T, (H + 2 * Hkv) * hd), torch.float32)
+            self.w_qkv.forward(xn, qkv)
+            kernels.rope_store(qkv, ctx.positions, ctx.row_req, tables, self.position.cos, self.position.sin,
+                               self.position.interleaved, q, k_cache, v_cache, H, Hkv, hd, ctx.page_size,
+                               write_kv=run.writes_cache)
         att = ctx.scratch("att", (T, H * hd), self.dtype)
         if self.fast:
             # tensor-core kernels: single decoded tokens split their context over many CTAs,

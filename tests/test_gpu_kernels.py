@@ -508,3 +508,64 @@ def test_attention_tcgen05_window(window):
                                 spike=(0, ctx - 1 - window), fast=True, tcgen05=True)
     close(got, want, "bfloat16", f"window {window}", bf16_tol=1e-2)
     assert float(want[-1].abs().mean()) < 2.0 and float(want[-2].abs().mean()) > 2.0
+
+
+@pytest.mark.parametrize("T,H,Hkv,hd,ps,D,rotated", [(300, 5, 1, 64, 16, 192, True), (131, 2, 2, 128, 8, 264, True),
+                                                     (257, 3, 3, 32, 16, 128, True), (200, 4, 2, 64, 32, 256, False),
+                                                     (8, 5, 1, 64, 16, 192, True), (3, 2, 2, 128, 8, 264, True),
+                                                     (40, 6, 2, 32, 16, 128, True), (60, 4, 4, 16, 16, 136, True),
+                                                     (17, 3, 1, 64, 16, 200, False)])
+def test_gemm_rope_store_fused(T, H, Hkv, hd, ps, D, rotated):
+    """The [q; k; v] product with rotation and page store in its epilogue against the product followed by
+    the rope+store kernel (and that against exact arithmetic): requests whose rows cross page edges,
+    pages in a shuffled order, widths and token counts that fill no tile, untouched pages stay NaN."""
+    g = torch.Generator().manual_seed(T + hd)
+    n_req = 3
+    lens = [T // 2, 1, T - T // 2 - 1]
+    first = [ps - 2, 3 * ps - 1, 5]
+    max_pos = max(f + n for f, n in zip(first, lens)) + 1
+    a = (torch.randn(T, D, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn((H + 2 * Hkv) * hd, D, generator=g) / math.sqrt(D)).to(torch.bfloat16).to(DEV)
+    cos = sin = None
+    if rotated:
+        freq = 1.0 / (10000.0 ** (np.arange(hd // 2, dtype=np.float64) * 2 / hd))
+        ang = np.arange(max_pos, dtype=np.float64)[:, None] * freq[None]
+        cos = torch.from_numpy(np.cos(ang).astype(np.float32)).to(DEV)
+        sin = torch.from_numpy(np.sin(ang).astype(np.float32)).to(DEV)
+    pages_per = [(first[r] + lens[r] + ps - 1) // ps for r in range(n_req)]
+    n_pages = sum(pages_per) + 3
+    perm = torch.randperm(n_pages, generator=g).int()
+    tables = torch.full((n_req, max(pages_per)), -1, dtype=torch.int32)
+    used = 0
+    for r in range(n_req):
+        for i in range(pages_per[r]):
+            tables[r, i] = perm[used]
+            used += 1
+    positions = torch.cat([torch.arange(first[r], first[r] + lens[r]) for r in range(n_req)]).int().to(DEV)
+    row_req = torch.cat([torch.full((lens[r],), r) for r in range(n_req)]).int().to(DEV)
+    tables = tables.to(DEV)
+    assert K().gemm_rope_store_supported(T, D, H, Hkv, hd, cos, False)
+    kc, vc = _paged("bfloat16", n_pages, Hkv, ps, hd)
+    q = torch.full((T, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    w_tiles = K().tile_weight(w)
+    K().gemm_rope_store(a, w, positions, row_req, tables, cos, sin, False, q, kc, vc, H, Hkv, hd, ps, w_tiles=w_tiles)
+    # the same in two kernels
+    qkv = torch.empty(T, (H + 2 * Hkv) * hd, dtype=torch.float32, device=DEV)
+    K().gemm_tc(a, w, qkv, w_tiles=w_tiles)
+    kc2, vc2 = _paged("bfloat16", n_pages, Hkv, ps, hd)
+    q2 = torch.full_like(q, float("nan"))
+    K().rope_store(qkv, positions, row_req, tables, cos, sin, False, q2, kc2, vc2, H, Hkv, hd, ps)
+    assert K().gemm_tc_status(q.device) == 0
+    for got, want, what in ((q, q2, "q"), (kc, kc2, "k pages"), (vc, vc2, "v pages")):
+        got, want = got.float().cpu(), want.float().cpu()
+        assert torch.equal(torch.isnan(got), torch.isnan(want)), f"{what}: other places were written"
+        got, want = torch.nan_to_num(got), torch.nan_to_num(want)
+        err = (got - want).abs().max().item()
+        assert err <= 2.0 ** -7 * want.abs().max().item(), f"{what}: differs from the two-kernel path by {err}"   # one bfloat16 step
+        assert (got != want).float().mean().item() < 0.02, f"{what}: too many values round differently"
+    # no write without write_kv
+    kc3, vc3 = _paged("bfloat16", n_pages, Hkv, ps, hd)
+    K().gemm_rope_store(a, w, positions, row_req, tables, cos, sin, False, q, kc3, vc3, H, Hkv, hd, ps, write_kv=False,
+                        w_tiles=w_tiles)
+    assert torch.isnan(kc3.float()).all() and torch.isnan(vc3.float()).all()
+    assert torch.equal(torch.nan_to_num(q.float()), torch.nan_to_num(q.float())) and not torch.isnan(q.float()).any()
