@@ -397,7 +397,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const int* __restrict__ row_req, const int* __restrict__ positions,
                             const int* __restrict__ block_tables, int table_stride, int H, int Hkv, int page_size,
                             float scale_log2, int window, float* __restrict__ part_o, float* __restrict__ part_ml,
-                            int max_chunks, int n_chunks, int* status) {
+                            int max_chunks, int n_chunks, __nv_bfloat16* __restrict__ out, int* status) {
     using Cfg = DecodeTma<HD>;
     constexpr int kTile = Cfg::kTile, kStages = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -583,6 +583,20 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             if (pw < total) issue();
         }
         if (failed) break;
+        if (ci.lo / kChunkKeys == ci.pos / kChunkKeys) {
+            // all keys of this token lie in this one chunk: the result is final and is written as the
+            // merge kernel would write it (which skips such tokens, or is not launched at all)
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int row = r0 + 8 * r;
+                if (row >= G) continue;
+                __nv_bfloat16* dst = out + (static_cast<size_t>(ci.t) * H + ci.g * G + row) * HD + (lane & 3) * 2;
+#pragma unroll
+                for (int n = 0; n < HD / 8; ++n)
+                    *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) = __floats2bfloat162_rn(o[n][2 * r] / l[r], o[n][2 * r + 1] / l[r]);
+            }
+            continue;
+        }
         // the chunk's partial result: unnormalised output, running maximum (log2 domain) and sum
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -613,7 +627,7 @@ constexpr int kCombineMaxDims = 4;                 // head dims per lane: the he
 __global__ void __launch_bounds__(kCombineWarps * 32)
 attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                          const int* __restrict__ rows, const int* __restrict__ positions,
-                         __nv_bfloat16* __restrict__ out, int H, int HD, int max_chunks, int window) {
+                         __nv_bfloat16* __restrict__ out, int H, int HD, int max_chunks, int window, int skip_single) {
     __shared__ float s_acc[kCombineWarps][kCombineMaxDims * 32];
     __shared__ float s_l[kCombineWarps];
     const int h = blockIdx.x, idx = blockIdx.y;
@@ -623,6 +637,7 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int first = lo / kChunkKeys, last = pos / kChunkKeys;
     pdl_prologue();
+    if (skip_single && first == last) return;        // the attention kernel wrote this token's result itself
     const float* ml = part_ml + (static_cast<size_t>(idx) * H + h) * max_chunks * 2;
     const float* po = part_o + (static_cast<size_t>(idx) * H + h) * max_chunks * HD;
     float M = -INFINITY;
@@ -978,7 +993,7 @@ static int launch_decode(const void* q, const void* kc, const void* vc, void* ou
     if (check_launch("attention_decode")) return 1;
     dim3 grid2(H, n_rows);
     launch_kernel((attention_combine_kernel), dim3(grid2), dim3(kCombineWarps * 32), 0, st, part_o, part_ml, rows, positions,
-                                                                   static_cast<__nv_bfloat16*>(out), H, HD, max_chunks, window);
+                                                                   static_cast<__nv_bfloat16*>(out), H, HD, max_chunks, window, 0);
     return check_launch("attention_combine");
 }
 
@@ -1008,11 +1023,12 @@ static int launch_decode_tma(const void* q, const void* kc, const void* vc, void
     int grid = items < sms ? items : sms;           // few items: fewer per CTA rather than fewer CTAs
     launch_kernel((attention_decode_tma_kernel<HD>), dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, mk, mv,
                   static_cast<const __nv_bfloat16*>(q), rows, n_rows, row_req, positions, tables, table_stride, H, Hkv,
-                  page_size, scale * kLog2e, window, part_o, part_ml, max_chunks, n_chunks, status);
+                  page_size, scale * kLog2e, window, part_o, part_ml, max_chunks, n_chunks, static_cast<__nv_bfloat16*>(out), status);
     if (check_launch("attention_decode_tma")) return 1;
+    if (n_chunks == 1) return 0;                     // every token's keys lie in one chunk: nothing to merge
     dim3 grid2(H, n_rows);
     launch_kernel((attention_combine_kernel), dim3(grid2), dim3(kCombineWarps * 32), 0, st, part_o, part_ml, rows, positions,
-                  static_cast<__nv_bfloat16*>(out), H, HD, max_chunks, window);
+                  static_cast<__nv_bfloat16*>(out), H, HD, max_chunks, window, 1);
     return check_launch("attention_combine");
 }
 

@@ -68,12 +68,14 @@ class StepContext:
         self._cache: Dict = {}
         self.all_single = all(s.length == 1 for s in segments)
         self.max_context = max((s.first_position + s.length for s in segments), default=0)
-        # longest context among requests that bring a single token, rounded up to 1024 positions:
+        # longest context among requests that bring a single token, rounded up to 1024 positions
+        # (to 256 below that: one chunk of the decode attention, which then needs no merge kernel):
         # the grid of the decode attention depends on it, and a coarse value keeps the set of
         # distinct step shapes (and of captured graphs) small; chunks beyond a row's own
         # position exit at once
         longest = max((s.first_position + 1 for s in segments if s.length == 1), default=0)
-        self.longest_single = min(engine.model.max_position, (longest + 1023) // 1024 * 1024)
+        rounded = 256 if longest <= 256 else (longest + 1023) // 1024 * 1024
+        self.longest_single = min(engine.model.max_position, rounded)
 
     def pages(self, layer: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """(keys, values) of a layer, each [pages, Hkv, page_size, head_dim]."""

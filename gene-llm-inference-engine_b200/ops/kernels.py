@@ -186,8 +186,9 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         block_tables.shape[1], num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
         _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), max_chunks, n_chunks,
         k_cache.shape[0], _tc_state(q.device).status.data_ptr(), _stream()), "attention_decode")
-    global _launches
-    _launches += 1            # the combine kernel
+    tma = page_size % 8 == 0 and (32 % page_size == 0 or page_size % 32 == 0)
+    if n_chunks > 1 or not tma:
+        count_launches(1)     # the kernel that merges the chunks (not needed when every context is one chunk)
 
 
 def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,

@@ -152,7 +152,7 @@ def test_rope_store(dtype, H, Hkv, hd, ps, interleaved, rot):
 
 
 def _run_fast_attention(q_all, kc, vc, out, row_req, positions, tables, q_lens, ctx_lens, H, Hkv, hd, ps, scale, window,
-                        tcgen05=False):
+                        tcgen05=False, decode_chunks=None):
     """The tensor-core kernels: single tokens through the decode kernel, portions through prefill."""
     kern = K()
     G = H // Hkv
@@ -168,7 +168,7 @@ def _run_fast_attention(q_all, kc, vc, out, row_req, positions, tables, q_lens, 
     if decode_rows:
         chunk = kern.attention_chunk_keys()
         max_chunks = (max(ctx_lens) + chunk - 1) // chunk + 2
-        n_chunks = (max(ctx_lens[r] for r, n in enumerate(q_lens) if n == 1) + chunk - 1) // chunk
+        n_chunks = decode_chunks or (max(ctx_lens[r] for r, n in enumerate(q_lens) if n == 1) + chunk - 1) // chunk
         part_o = torch.full((len(decode_rows) * H * max_chunks * hd,), float("nan"), device=DEV)
         part_ml = torch.full((len(decode_rows) * H * max_chunks * 2,), float("nan"), device=DEV)
         kern.attention_decode(q_all, kc, vc, out, torch.tensor(decode_rows, dtype=torch.int32, device=DEV), row_req,
@@ -178,7 +178,8 @@ def _run_fast_attention(q_all, kc, vc, out, row_req, positions, tables, q_lens, 
         fn(q_all, kc, vc, out, torch.tensor(work, dtype=torch.int32, device=DEV), positions, tables, H, Hkv, hd, ps, scale, window)
 
 
-def _attention_case(dtype, H, Hkv, hd, ps, ctx_lens, q_lens, window, seed, spike=None, fast=False, tcgen05=False):
+def _attention_case(dtype, H, Hkv, hd, ps, ctx_lens, q_lens, window, seed, spike=None, fast=False, tcgen05=False,
+                    decode_chunks=None):
     """Requests with ``ctx_lens`` cached positions of which the last ``q_lens`` are this step's
     queries. Pages are scattered and unused pages hold NaN. ``spike`` = (request, key position):
     that key is made to match every query of the request strongly."""
@@ -219,7 +220,8 @@ def _attention_case(dtype, H, Hkv, hd, ps, ctx_lens, q_lens, window, seed, spike
     rr = torch.tensor(row_req, dtype=torch.int32, device=DEV)
     pp = torch.tensor(positions, dtype=torch.int32, device=DEV)
     if fast:
-        _run_fast_attention(q_all, kc, vc, out, rr, pp, tables.to(DEV), q_lens, ctx_lens, H, Hkv, hd, ps, scale, window, tcgen05)
+        _run_fast_attention(q_all, kc, vc, out, rr, pp, tables.to(DEV), q_lens, ctx_lens, H, Hkv, hd, ps, scale, window, tcgen05,
+                            decode_chunks)
     else:
         K().attention_generic(q_all, kc, vc, out, rr, pp, tables.to(DEV), H, Hkv, hd, ps, scale, window)
     want = []
@@ -394,6 +396,25 @@ def test_attention_tensor_cores_mixed_rows(H, Hkv, hd, ps):
     got, want = _attention_case("bfloat16", H, Hkv, hd, ps, ctx_lens=[150, 700, 3 * ps + 1, 1, 256, 257, 64, 65],
                                 q_lens=[150, 1, ps + 2, 1, 1, 1, 1, 1], window=None, seed=6, fast=True)
     close(got, want, "bfloat16", "attention (tensor cores)", bf16_tol=1e-2)
+
+
+@pytest.mark.parametrize("H,Hkv,hd,ps", [(8, 2, 64, 16), (4, 4, 128, 32), (6, 2, 32, 8), (5, 5, 64, 4)])
+@pytest.mark.parametrize("decode_chunks", [1, 3])
+def test_attention_decode_contexts_of_one_chunk(H, Hkv, hd, ps, decode_chunks):
+    """Single tokens whose keys all lie in one chunk are written by the attention kernel itself: with one
+    chunk in the launch no merge kernel runs, with more (the engine rounds the longest context up, or
+    another request is longer) the merge kernel leaves them alone. Both give the same bits."""
+    outs = []
+    for chunks in (decode_chunks, 1):
+        got, want = _attention_case("bfloat16", H, Hkv, hd, ps, ctx_lens=[100, 256, 1, 37, 255], q_lens=[1, 1, 1, 1, 1],
+                                    window=None, seed=21, fast=True, decode_chunks=chunks)
+        close(got, want, "bfloat16", "attention of short contexts", bf16_tol=1e-2)
+        outs.append(got)
+    assert torch.equal(outs[0], outs[1])
+    # a window that lies inside one chunk of a long context is final too
+    got, want = _attention_case("bfloat16", H, Hkv, hd, ps, ctx_lens=[700, 520, 300], q_lens=[1, 1, 1], window=40, seed=22,
+                                fast=True)
+    close(got, want, "bfloat16", "attention of a short window", bf16_tol=1e-2)
 
 
 @pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 255, 256, 511, 597])
