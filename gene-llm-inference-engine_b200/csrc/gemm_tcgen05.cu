@@ -622,9 +622,10 @@ struct TcPersistentConfig {
     static constexpr int kStageBytesP = kBlockP * kBlockK * 2;
     static constexpr int kStageBytesQ = BLOCK_Q * kBlockK * 2;
     static constexpr int kStageBytes = kStageBytesP + kStageBytesQ;
-    static constexpr int kStages = (BLOCK_Q >= 256) ? 4 : 6;
+    static constexpr int kStages = (BLOCK_Q >= 192) ? 4 : 6;
     static constexpr int kStagingBytes = kBlockP * 128;          // 128 rows x 128 bytes, two of them
-    static constexpr int kTmemCols = 2 * BLOCK_Q;
+    static constexpr int kAccStride = (BLOCK_Q > 128) ? 256 : BLOCK_Q;   // columns between the two accumulators
+    static constexpr int kTmemCols = 2 * kAccStride;                     // a power of two
     static constexpr int kSmemBytes = kStages * kStageBytes + 2 * kStagingBytes + 1024 + 256;
     static constexpr uint32_t kIdesc = TcConfig<BLOCK_Q>::kIdesc;
 };
@@ -733,7 +734,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                     break;
                 }
                 tc_fence_after();
-                const uint32_t tmem_d = tmem_base + buf * BLOCK_Q;
+                const uint32_t tmem_d = tmem_base + buf * Cfg::kAccStride;
                 const int n_kb = kb_count(t);
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = it % kStages;
@@ -808,7 +809,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
             group_sync();
             if (!ok) break;
             tc_fence_after();
-            const uint32_t tmem_d = tmem_base + buf * BLOCK_Q + lane_addr;
+            const uint32_t tmem_d = tmem_base + buf * Cfg::kAccStride + lane_addr;
             if constexpr (EPI == kEpiRopeStore) {
                 // A thread holds one token's row of the tile: whole heads (BLOCK_Q is a multiple of the head
                 // size), so both members of a rotated pair (d, d + hd/2) are its own. 16 pairs at a time:
@@ -1327,7 +1328,15 @@ extern "C" int gi_gemm_tc_persistent_rope(const void* A, const void* W, int M, i
     TcPersistentParams p = {};
     p.rows_p = M; p.rows_q = N; p.K = K;
     p.tiles_p = (M + kBlockP - 1) / kBlockP;
-    p.tiles_q = (N + 255) / 256;
+    // 256 or 192 accumulator columns per tile: whichever needs fewer column-rounds of the GPU (rounds of
+    // tiles over the SMs x tile width); with 3072 outputs and 2048 tokens 192 tiles of 256 are 2 rounds
+    // of 256, 256 tiles of 192 are 2 rounds of 192
+    auto rounds_cost = [&](int bq) {
+        const long long tiles = static_cast<long long>(p.tiles_p) * ((N + bq - 1) / bq);
+        return (tiles + sm_count() - 1) / sm_count() * bq;
+    };
+    const int block_q = (192 % hd == 0 && rounds_cost(192) < rounds_cost(256)) ? 192 : 256;
+    p.tiles_q = (N + block_q - 1) / block_q;
     p.up_row_offset = 0;
     p.status = static_cast<int*>(status);
     p.splits = 1; p.kb_per_split = (K + kBlockK - 1) / kBlockK; p.split_rows = 0;
@@ -1335,6 +1344,8 @@ extern "C" int gi_gemm_tc_persistent_rope(const void* A, const void* W, int M, i
                              static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
                              static_cast<__nv_bfloat16*>(v_cache), H, Hkv, hd, page_size, write_kv};
     CUtensorMap mp, mq;
-    if (make_map(&mp, A, M, K, lda, kBlockP) || make_map(&mq, W, N, K, ldw, 256)) return 1;
-    return launch_persistent<256, kEpiRopeStore>(mp, mq, mp /* no TMA store */, p, static_cast<cudaStream_t>(stream));
+    if (make_map(&mp, A, M, K, lda, kBlockP) || make_map(&mq, W, N, K, ldw, block_q)) return 1;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (block_q == 192) return launch_persistent<192, kEpiRopeStore>(mp, mq, mp /* no TMA store */, p, st);
+    return launch_persistent<256, kEpiRopeStore>(mp, mq, mp /* no TMA store */, p, st);
 }

@@ -401,7 +401,8 @@ def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> 
                                       st.status.data_ptr(), 1, 0, 0, _stream()), "gemm_swiglu")
 
 
-_ROPE_FEW_TOKENS = 64      # up to here the few-token product (weights on the 128-row side) does the rotation
+_ROPE_FEW_TOKENS = 32      # up to here the few-token product (weights on the 128-row side) does the rotation: measured
+                           # in whole decode steps, 2.4 % faster at 16 tokens, even at 32, 1.7 % slower at 64
 
 
 def gemm_rope_store_supported(M: int, K: int, num_heads: int, num_kv_heads: int, head_dim: int,

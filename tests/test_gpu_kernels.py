@@ -536,7 +536,7 @@ def test_attention_tcgen05_window(window):
                                                      (8, 5, 1, 64, 16, 192, True), (3, 2, 2, 128, 8, 264, True),
                                                      (40, 6, 2, 32, 16, 128, True), (60, 4, 4, 16, 16, 136, True),
                                                      (17, 3, 1, 64, 16, 200, False)])
-def test_gemm_rope_store_fused(T, H, Hkv, hd, ps, D, rotated):
+def test_gemm_rope_store_fused(T, H, Hkv, hd, ps, D, rotated, monkeypatch):
     """The [q; k; v] product with rotation and page store in its epilogue against the product followed by
     the rope+store kernel (and that against exact arithmetic): requests whose rows cross page edges,
     pages in a shuffled order, widths and token counts that fill no tile, untouched pages stay NaN."""
@@ -565,6 +565,7 @@ def test_gemm_rope_store_fused(T, H, Hkv, hd, ps, D, rotated):
     positions = torch.cat([torch.arange(first[r], first[r] + lens[r]) for r in range(n_req)]).int().to(DEV)
     row_req = torch.cat([torch.full((lens[r],), r) for r in range(n_req)]).int().to(DEV)
     tables = tables.to(DEV)
+    monkeypatch.setattr(K(), "_ROPE_FEW_TOKENS", 64)      # the few-token form is built for up to 128 tokens; cover its wider tiles too
     assert K().gemm_rope_store_supported(T, D, H, Hkv, hd, cos, False)
     kc, vc = _paged("bfloat16", n_pages, Hkv, ps, hd)
     q = torch.full((T, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
