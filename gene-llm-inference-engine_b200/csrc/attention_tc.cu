@@ -2,12 +2,14 @@
 //
 // One CTA takes 128 query rows (tokens x the query heads of one key/value group) and walks the keys
 // in tiles of 128 over the request's pages:
-//   warp 0      TMA producer: one box per page and head for K and for V into a two-stage ring, each
-//               lane requesting its own box;
+//   warp 0      TMA producer: one box per page and head, each lane requesting its own box; keys and
+//               values have two-place rings and barriers of their own (a key tile is free once its S
+//               product is done, a value tile only after P V), and keys run one tile ahead of values;
 //   warp 1      allocates tensor memory and issues the MMAs: S = Q K^T (both operands K-major in
 //               shared memory, S in tensor memory) and O += P V (P from shared memory, V as an
 //               MN-major operand straight from the page layout [keys, head_dim]); S of the next tile
-//               is issued before P V of the current one, so the softmax warps never wait for P V;
+//               is issued as soon as the softmax warps have the current scores in registers, before
+//               P V of the current tile;
 //   warps 2..5  softmax: thread r owns row r of the tile, which is lane r of tensor memory, so row
 //               maximum and row sum need no exchange between threads. They read S with tcgen05.ld,
 //               scale O by the correction factor in tensor memory, write P = exp2(S - m) as bfloat16
@@ -136,7 +138,7 @@ struct Cfg {
     static constexpr int kQBytes = kRows * HD * 2;
     static constexpr int kTileBytes = kKeys * HD * 2;              // one K or V tile
     static constexpr int kPBytes = kRows * kKeys * 2;
-    static constexpr int kSmemBytes = kQBytes + kStages * 2 * kTileBytes + kPBytes + 128;   // two CTAs fit in an SM's 228 KB
+    static constexpr int kSmemBytes = kQBytes + kStages * 2 * kTileBytes + kPBytes + 256;   // two CTAs fit in an SM's 228 KB
     static constexpr int kTmemCols = 256;                          // S: 128 columns, O: HD columns
     // D f32, A and B bf16, M = 128
     static constexpr uint32_t kIdescS = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kKeys >> 3) << 17) | (8u << 24);
@@ -161,8 +163,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     uint8_t* kv_smem = q_smem + C::kQBytes;                        // stage s: K at s * 2 * tile, V after it
     uint8_t* p_smem = kv_smem + kStages * 2 * C::kTileBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + C::kPBytes);
-    // bars: [0,2) kv full, [2,4) kv empty, 4 s full, 5 p full, 6 o done
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    // Keys and values have rings and barriers of their own: a key tile is free again when its S product is
+    // done (early in the tile's softmax), a value tile only after P V, so the keys of tile i + 1 are
+    // requested more than a tile's time before their product is issued.
+    constexpr int kKFull = 0, kVFull = 2, kKEmpty = 4, kVEmpty = 6, kSFull = 8, kPFull = 9, kODone = 10, kSRead = 11;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -170,10 +175,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int g = blockIdx.x;          // heads vary fastest: the longest work items of every head start first
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&bars[s]), 1); mbar_init(smem_u32(&bars[2 + s]), 1); }
-        mbar_init(smem_u32(&bars[4]), 1);
-        mbar_init(smem_u32(&bars[5]), 128);
-        mbar_init(smem_u32(&bars[6]), 1);
+        for (int b = 0; b < 8; ++b) mbar_init(smem_u32(&bars[b]), 1);
+        mbar_init(smem_u32(&bars[kSFull]), 1);
+        mbar_init(smem_u32(&bars[kPFull]), 128);
+        mbar_init(smem_u32(&bars[kODone]), 1);
+        mbar_init(smem_u32(&bars[kSRead]), 128);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -201,7 +207,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const int* table = block_tables + static_cast<size_t>(req) * table_stride;
         const int box_rows = page_size < kKeys ? page_size : kKeys;
         const int boxes = kKeys / box_rows;                       // at most 16 (pages of 8)
-        for (int i = 0; i < n_tiles; ++i) {
+        // one tile of keys or of values: false when a wait gave up
+        auto load_tile = [&](int i, bool values) -> bool {
             const int s = i % kStages;
             const int key0 = (first_tile + i) * kKeys;
             const int kb_lane = key0 + lane * box_rows;
@@ -209,16 +216,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             const int page_lane = lane_valid ? table[kb_lane / page_size] : 0;
             const unsigned valid_mask = __ballot_sync(0xffffffffu, lane_valid);
             bool ok = true;
-            if (lane == 0 && i >= kStages && !mbar_wait(smem_u32(&bars[2 + s]), ((i / kStages) - 1) & 1, abort_flag)) {
+            if (lane == 0 && i >= kStages &&
+                !mbar_wait(smem_u32(&bars[(values ? kVEmpty : kKEmpty) + s]), ((i / kStages) - 1) & 1, abort_flag)) {
                 if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, 8); }
                 ok = false;
             }
-            if (!__shfl_sync(0xffffffffu, ok ? 1 : 0, 0)) break;
-            const uint32_t k_tile = smem_u32(kv_smem + s * 2 * C::kTileBytes), v_tile = k_tile + C::kTileBytes;
-            const uint32_t bar = smem_u32(&bars[s]);
+            if (!__shfl_sync(0xffffffffu, ok ? 1 : 0, 0)) return false;
+            const uint32_t tile = smem_u32(kv_smem + s * 2 * C::kTileBytes) + (values ? C::kTileBytes : 0);
+            const uint32_t bar = smem_u32(&bars[(values ? kVFull : kKFull) + s]);
             if (lane == 0) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_expect_tx(bar, static_cast<uint32_t>(__popc(valid_mask)) * 2u * box_rows * HD * 2u);
+                mbar_expect_tx(bar, static_cast<uint32_t>(__popc(valid_mask)) * box_rows * HD * 2u);
             }
             __syncwarp();                                         // the expected bytes are set before any copy can complete
             if (lane_valid) {                                     // every lane requests its own box
@@ -226,22 +234,29 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
                 for (int h = 0; h < C::kBlocks; ++h) {
                     const uint32_t off = static_cast<uint32_t>(h * (kKeys * 128) + lane * box_rows * 128);
-                    tma_load_2d(k_tile + off, &map_k, h * 64, row, bar);
-                    tma_load_2d(v_tile + off, &map_v, h * 64, row, bar);
+                    tma_load_2d(tile + off, values ? &map_v : &map_k, h * 64, row, bar);
                 }
             }
+            return true;
+        };
+        // keys run one tile ahead of values: K(0); K(1), V(0); K(2), V(1); ... in the order in which
+        // their places become free (K(i) after S(i - 2), V(i - 1) after P V(i - 3))
+        for (int n = 0; n <= n_tiles; ++n) {
+            if (n < n_tiles && !load_tile(n, false)) break;
+            if (n >= 1 && !load_tile(n - 1, true)) break;
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             // Q is written by the softmax warps; their first arrival on "p full" (phase 0) also says Q is ready
-            bool ok = mbar_wait(smem_u32(&bars[5]), 0, abort_flag);
+            bool ok = mbar_wait(smem_u32(&bars[kPFull]), 0, abort_flag);
             if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, 9); }
-            // S(i + 1) goes to the tensor cores before P(i) V(i): the softmax warps have read S(i) by the
-            // time P(i) is full, so they can start on the next tile while O is still being updated.
+            // S(i + 1) goes to the tensor cores as soon as the softmax warps have read S(i) into registers
+            // ("s read": three quarters into their pass over the tile), well before P(i) is full and
+            // P(i) V(i) can be issued: the softmax warps find the next scores ready when they finish a tile.
             auto issue_s = [&](int i) -> bool {
                 const int s = i % kStages;
-                if (!mbar_wait(smem_u32(&bars[s]), (i / kStages) & 1, abort_flag)) return false;
+                if (!mbar_wait(smem_u32(&bars[kKFull + s]), (i / kStages) & 1, abort_flag)) return false;
                 tc_fence_after();
                 const uint32_t k_tile = smem_u32(kv_smem + s * 2 * C::kTileBytes);
 #pragma unroll
@@ -251,15 +266,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
                     for (int k = 0; k < 4; ++k) umma(tmem_s, dq + 2 * k, dk + 2 * k, C::kIdescS, (kb > 0 || k > 0) ? 1u : 0u);
                 }
-                umma_commit(smem_u32(&bars[4]));
+                umma_commit(smem_u32(&bars[kSFull]));
+                umma_commit(smem_u32(&bars[kKEmpty + s]));     // the key tile may be refilled
                 return true;
             };
             if (ok) ok = issue_s(0);
             for (int i = 0; i < n_tiles && ok; ++i) {
                 const int s = i % kStages;
-                // wait for P(i) (and the rescaled O)
-                if (!mbar_wait(smem_u32(&bars[5]), (i + 1) & 1, abort_flag)) { ok = false; break; }
-                if (i + 1 < n_tiles && !issue_s(i + 1)) { ok = false; break; }
+                if (i + 1 < n_tiles) {
+                    if (!mbar_wait(smem_u32(&bars[kSRead]), i & 1, abort_flag)) { ok = false; break; }
+                    if (!issue_s(i + 1)) { ok = false; break; }
+                }
+                // wait for P(i) (and the rescaled O) and for the values
+                if (!mbar_wait(smem_u32(&bars[kPFull]), (i + 1) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&bars[kVFull + s]), (i / kStages) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t v_tile = smem_u32(kv_smem + s * 2 * C::kTileBytes) + C::kTileBytes;
 #pragma unroll
@@ -275,8 +295,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                         }
                     }
                 }
-                umma_commit(smem_u32(&bars[2 + s]));        // the stage may be refilled
-                umma_commit(smem_u32(&bars[6]));            // O holds the sum up to this tile; P may be overwritten
+                umma_commit(smem_u32(&bars[kVEmpty + s]));  // the value tile may be refilled
+                umma_commit(smem_u32(&bars[kODone]));       // O holds the sum up to this tile; P may be overwritten
             }
             if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, 10); }
         }
@@ -299,7 +319,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 *reinterpret_cast<uint4*>(q_smem + (c >> 3) * (kRows * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(smem_u32(&bars[5]));                      // phase 0 of "p full": Q is in place
+            mbar_arrive(smem_u32(&bars[kPFull]));                 // phase 0 of "p full": Q is in place
         }
         // Online softmax with a lazily updated reference: weights are exp2(s - m_ref) where m_ref is
         // the row's reference maximum (scaled log2 domain). As long as no score of a new tile exceeds
@@ -310,7 +330,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         // independent of which references were used.
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
-        auto tile_pass = [&](int key0, auto edge_tag, float m_use, float& mx, float& sum, int p_free_parity) {
+        auto tile_pass = [&](int key0, auto edge_tag, float m_use, float& mx, float& sum, int p_free_parity, bool last_pass) {
             // one pass over the tile's scores: running maximum of the raw scores, weights, their sum,
             // and the weights as bfloat16 into the K-major P tile; loads of the next 32 columns are
             // in flight while the current ones are processed. The masking of tiles that some row
@@ -323,6 +343,28 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             for (int c = 0; c < kKeys / 32; ++c) {
                 if (c + 1 < kKeys / 32) tmem_ld32(tmem_s + lane_addr + (c + 1) * 32, buf[(c + 1) & 1]);
                 const uint32_t* sv = buf[c & 1];
+                if (c + 1 == kKeys / 32) {
+                    // All scores of the tile are in registers. If this pass is the tile's last one (the
+                    // reference maximum stays: known once the last 32 scores are looked at, before their
+                    // weights are made), the tensor cores may write the next tile's scores over them.
+                    if (!last_pass) {
+                        float mx_all = mx;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            float v = __uint_as_float(sv[j]);
+                            if (kEdge) {
+                                const int key = key0 + c * 32 + j;
+                                if (!(key >= row_lo && key <= row_pos)) v = -INFINITY;
+                            }
+                            mx_all = fmaxf(mx_all, v);
+                        }
+                        last_pass = !__any_sync(0xffffffffu, mx_all * scale_log2 > m_ref + 8.0f);
+                    }
+                    if (last_pass) {
+                        tc_fence_before();
+                        mbar_arrive(smem_u32(&bars[kSRead]));
+                    }
+                }
                 uint32_t packed[16];
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
@@ -341,7 +383,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 if (c == 0 && p_free_parity >= 0) {
                     // P of the tile before is still being read by its MMAs (they were issued after this
                     // tile's S): the first store waits for them; O may be touched from here on, too
-                    if (!mbar_wait(smem_u32(&bars[6]), static_cast<uint32_t>(p_free_parity), abort_flag)) ok = false;
+                    if (!mbar_wait(smem_u32(&bars[kODone]), static_cast<uint32_t>(p_free_parity), abort_flag)) ok = false;
                     tc_fence_after();
                 }
 #pragma unroll
@@ -353,17 +395,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 if (c + 1 < kKeys / 32) tmem_ld_wait();
             }
         };
-        auto tile_pass_any = [&](int key0, bool edge, float m_use, float& mx, float& sum, int p_free_parity) {
-            if (edge) tile_pass(key0, std::true_type{}, m_use, mx, sum, p_free_parity);
-            else tile_pass(key0, std::false_type{}, m_use, mx, sum, p_free_parity);
+        auto tile_pass_any = [&](int key0, bool edge, float m_use, float& mx, float& sum, int p_free_parity, bool last_pass) {
+            if (edge) tile_pass(key0, std::true_type{}, m_use, mx, sum, p_free_parity, last_pass);
+            else tile_pass(key0, std::false_type{}, m_use, mx, sum, p_free_parity, last_pass);
         };
         for (int i = 0; i < n_tiles; ++i) {
             const int key0 = (first_tile + i) * kKeys;
-            if (!mbar_wait(smem_u32(&bars[4]), i & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(smem_u32(&bars[kSFull]), i & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const bool edge = key0 < lo_last || key0 + kKeys - 1 > pos_first;      // some row masks some key of this tile
             float mx = -INFINITY, sum = 0.f;
-            tile_pass_any(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum, i > 0 ? ((i - 1) & 1) : -1);
+            tile_pass_any(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum, i > 0 ? ((i - 1) & 1) : -1, false);
             if (!ok) break;
             const float m_tile = mx * scale_log2;
             const bool move = m_tile > m_ref + 8.0f;                     // also true for the first visible key (m_ref = -inf)
@@ -386,12 +428,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 m_ref = m_new;
                 mx = -INFINITY;
                 sum = 0.f;
-                tile_pass_any(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum, -1);
+                tile_pass_any(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum, -1, true);
             }
             l += sum;
             if (key0 < lo_first || key0 + kKeys - 1 > pos_last) {
                 // value rows outside every query's range were not fetched or never written; they meet
                 // weights of exactly 0 in the MMA and must be finite: row r of the tile is this thread's
+                // (after the tile has arrived: the copy must not land on top of the zeros)
+                if (!mbar_wait(smem_u32(&bars[kVFull + i % kStages]), (i / kStages) & 1, abort_flag)) { ok = false; break; }
                 const int key = key0 + r;
                 if (key < lo_first || key > pos_last) {
                     uint8_t* v_tile = kv_smem + (i % kStages) * 2 * C::kTileBytes + C::kTileBytes;
@@ -402,9 +446,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
-            mbar_arrive(smem_u32(&bars[5]));
+            mbar_arrive(smem_u32(&bars[kPFull]));
         }
-        if (ok && mbar_wait(smem_u32(&bars[6]), (n_tiles - 1) & 1, abort_flag)) {
+        if (ok && mbar_wait(smem_u32(&bars[kODone]), (n_tiles - 1) & 1, abort_flag)) {
             tc_fence_after();
             const float inv = 1.0f / l;
             __nv_bfloat16* dst = out + (static_cast<size_t>(t0 + tok) * H + g * G + hh) * HD;
@@ -494,3 +538,4 @@ extern "C" int gi_attention_prefill_tc(const void* q, const void* k_cache, const
     return atc::launch<128>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv,
                             page_size, scale, window, n_pages, static_cast<int*>(status), st);
 }
+
