@@ -131,6 +131,17 @@ __device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
     d |= static_cast<uint64_t>(2) << 61;
     return d;
 }
+// The same with several 64-element blocks of the contiguous index in one MMA: the leading offset is
+// the distance between them.
+__device__ __forceinline__ uint64_t desc_mn_major_blocks(uint32_t addr, uint32_t block_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((block_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
 
 template <int HD>
 struct Cfg {
@@ -143,7 +154,7 @@ struct Cfg {
     // D f32, A and B bf16, M = 128
     static constexpr uint32_t kIdescS = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kKeys >> 3) << 17) | (8u << 24);
     static constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) /* B is MN-major */ |
-                                         (static_cast<uint32_t>(64 >> 3) << 17) | (8u << 24);
+                                         (static_cast<uint32_t>(HD >> 3) << 17) | (8u << 24);
 };
 
 template <int HD>
@@ -288,11 +299,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         const int kk = kb * 4 + k;                                  // 16 keys per step
-#pragma unroll
-                        for (int h = 0; h < C::kBlocks; ++h) {
-                            const uint64_t dv = desc_mn_major(v_tile + h * (kKeys * 128) + kk * (16 * 128));
-                            umma(tmem_o + h * 64, dp + 2 * k, dv, C::kIdescPV, (i > 0 || kk > 0) ? 1u : 0u);
-                        }
+                        // all HD columns of O in one MMA: the 64-wide blocks of V lie kKeys * 128 bytes apart
+                        const uint64_t dv = desc_mn_major_blocks(v_tile + kk * (16 * 128), kKeys * 128);
+                        umma(tmem_o, dp + 2 * k, dv, C::kIdescPV, (i > 0 || kk > 0) ? 1u : 0u);
                     }
                 }
                 umma_commit(smem_u32(&bars[kVEmpty + s]));  // the value tile may be refilled
