@@ -31,12 +31,13 @@ _TMP = tempfile.TemporaryDirectory(prefix="geneinfer_tests_")
 CASES = {
     "a": (tc.TINY_A, tc.SHARP_A), "b": (tc.TINY_B, tc.SHARP_B),
     "a_named": (tc.TINY_A, tc.WEIGHTS_A), "b_named": (tc.TINY_B, tc.WEIGHTS_B),
-    "c": (tc.TINY_C, tc.SHARP_C), "d": (tc.TINY_D, tc.SHARP_D),
+    "c": (tc.TINY_C, tc.SHARP_C), "d": (tc.TINY_D, tc.SHARP_D), "w": (tc.WIDE_W, tc.SHARP_W),
+    "w3": (tc.WIDE_W3, tc.SHARP_W3),
 }
 
 REQUEST_LENGTHS = {"a": [40, 75, 128, 100, 64, 33, 90], "b": [1, 5, 24, 64, 100, 200, 256],
                    "a_named": [7, 16, 33], "b_named": [1, 5, 24, 64, 100], "c": [300, 140, 512, 129, 2, 260],
-                   "d": [200, 384, 131, 66, 3]}
+                   "d": [200, 384, 131, 66, 3], "w": [150, 37], "w3": [140, 35]}
 
 
 @functools.lru_cache(maxsize=None)

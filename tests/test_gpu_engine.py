@@ -62,6 +62,20 @@ def test_mixed_batches_reusing_pages(case, dtype, seed):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ["w", "w3"])
+def test_full_widths_of_the_1b_and_3b_shapes(case, dtype):
+    """Two layers at the real widths of Llama-3.2-1B (hidden 2048, 32:8 heads of 64, intermediate 8192,
+    vocabulary 128256) and one at those of Llama-3.2-3B (hidden 3072, 24:8 heads of 128): the sizes at
+    which the products split over K, run in clusters and tile the vocabulary, whole, with the tail
+    decoded and in portions beside each other."""
+    reqs = gf.requests(case)
+    plain, tol = gf.plain_logits(case, dtype), gf.tolerance(dtype, case)
+    for name, steps in (("whole", tt.trace_whole(reqs)), ("tail", tt.trace_tail_decode(reqs, tail=32)),
+                        ("mixed", tt.trace_mixed(reqs, seed=4, max_live=2))):
+        tt.compare(_play(case, dtype, steps), plain, tol, f"full widths {case}, {name}, {dtype}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_cuts_agree_bitwise_in_32bit_and_closely_in_bf16(dtype):
     """The same position computed whole, decoded and in portions: identical in 32-bit (every output
     is one fixed chain of operations), within rounding in bfloat16."""

@@ -65,3 +65,17 @@ TINY_D = {   # head size 128 as in the 3B and 8B shapes, 4:2 heads, untied head,
     "rms_norm_eps": 2e-6, "tie_word_embeddings": False,
 }
 SHARP_D = {"seed": 41, "dtype": "bfloat16", "std": 0.1, "norm_mean": 1.0, "norm_std": 0.1}
+
+WIDE_W = {   # the Llama-3.2-1B widths, heads, vocabulary and RoPE scaling with two of its sixteen layers
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_act": "silu",
+    "hidden_size": 2048, "intermediate_size": 8192, "num_hidden_layers": 2, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 64, "vocab_size": 128256, "max_position_embeddings": 8192,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+}
+SHARP_W = {"seed": 51, "dtype": "bfloat16", "std": 0.05, "norm_mean": 1.0, "norm_std": 0.1}
+
+WIDE_W3 = dict(WIDE_W, hidden_size=3072, num_attention_heads=24, head_dim=128, num_hidden_layers=1)   # the Llama-3.2-3B widths, one layer
+SHARP_W3 = {"seed": 52, "dtype": "bfloat16", "std": 0.04, "norm_mean": 1.0, "norm_std": 0.1}
