@@ -16,7 +16,9 @@
 // efficiency. The split over K (few tokens, narrow weight matrices) runs the splits of a tile as
 // one thread-block cluster where they fit: splits 1.. write their partial tiles into the shared
 // memory of split 0 (st.shared::cluster) and arrive on its mbarrier, and split 0 adds them in split
-// order. Where a cluster does not fit, partial tiles go to a workspace in global memory and the CTA
+// order. The tiles have a place of their own behind the pipeline stages where there is room (few
+// tokens); otherwise they land in split 0's stages once it has told the others that its products are
+// done with them. Where a cluster does not fit, partial tiles go to a workspace in global memory and the CTA
 // that arrives last adds them, again in split order; results never depend on the order of arrival.
 //
 // Every wait on an mbarrier is bounded: when a limit is hit the kernel records a code in the
@@ -151,8 +153,19 @@ struct TcConfig {
                                          : ((BLOCK_Q >= 256) ? 4 : (BLOCK_Q >= 128) ? 6 : 8);
     static constexpr int kTmemCols = BLOCK_Q < 32 ? 32 : BLOCK_Q;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
-    // a cluster's split 0 also holds the partial tiles of the other splits, [split - 1][q][128 rows]
+    // A cluster's split 0 receives the partial tiles of the other splits, [split - 1][q][128 rows], in its
+    // pipeline stages once its own products are done with them (it tells the others when); behind them
+    // lie the per-token arrays of the rotating epilogue.
     static constexpr int kPartialBytes = BLOCK_Q * kBlockP * 4;
+    static constexpr int kTokenInfoBytes = BLOCK_Q * 12;
+    // (not for 16 tokens: their partial tiles always find a place of their own, and the kernel that every
+    // small decode step runs stays free of the extra code)
+    static constexpr bool kStagesReceive = BLOCK_Q >= 32;
+    static constexpr bool cluster_fits(int cluster_splits) {
+        return kStagesReceive && (cluster_splits - 1) * kPartialBytes + kPartialBytes + kTokenInfoBytes <= kStages * kStageBytes;
+    }
+    // ... or, where the shared memory has room for it, in a place of their own behind the stages: then
+    // nobody has to wait for split 0 (about 2 us less for a product of 16 tokens)
     static constexpr int smem_bytes(int cluster_splits) {
         return kSmemBytes + (cluster_splits > 1 ? (cluster_splits - 1) * kPartialBytes : 0);
     }
@@ -251,9 +264,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
     // bars[0..kStages) full, [kStages..2kStages) empty, [2kStages] accumulator ready,
-    // [2kStages + 1] the other splits' partial tiles have arrived (cluster reduce, split 0)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2);
-    float* partials = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes + 256);
+    // [2kStages + 1] the other splits' partial tiles have arrived (cluster reduce, split 0),
+    // [2kStages + 2] split 0's stages are free to receive them (cluster reduce, the other splits)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 3);
+    float* partials = reinterpret_cast<float*>((Cfg::kStagesReceive && p.cluster == 2) ? smem : smem + kStages * Cfg::kStageBytes + 256);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = const_cast<int*>(abort_flag) + 1;
     int* epi_abort = last_flag + 1;
@@ -273,6 +287,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         }
         mbar_init(smem_u32(&bars[2 * kStages]), 1);
         mbar_init(smem_u32(&bars[2 * kStages + 1]), p.cluster ? static_cast<uint32_t>(p.splits - 1) * 128u : 1u);
+        mbar_init(smem_u32(&bars[2 * kStages + 2]), 1);
         *abort_flag = 0;
         *last_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -429,8 +444,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             // Splits 1.. hand their partial tile to split 0 (rank 0 of the cluster) and arrive on
             // its barrier, even after giving up, so that split 0 never waits for a CTA that is gone;
             // split 0 waits (bounded) before it leaves, so its memory outlives every write to it.
+            // Where the tiles land in split 0's pipeline stages (cluster == 2): split 0 says when its
+            // products are done with them (an arrival on every other split's "stages free" barrier,
+            // sent even after giving up), and the others wait for that (bounded) before they write and
+            // before they leave, so that the arrival never finds their memory gone.
+            if (split == 0) {
+                if (Cfg::kStagesReceive && p.cluster == 2 && warp == 2 && lane == 0) {
+                    for (int s = 1; s < p.splits; ++s)
+                        cluster_mbar_arrive(cluster_map(smem_u32(&bars[2 * kStages + 2]), static_cast<uint32_t>(s)));
+                }
+            }
             if (split != 0) {
-                if (!aborted) {
+                bool stages_free = !Cfg::kStagesReceive || p.cluster != 2 || mbar_try_wait_cluster(smem_u32(&bars[2 * kStages + 2]), 0);
+                const unsigned long long t0 = clock64();
+                while (!stages_free) {
+                    stages_free = mbar_try_wait_cluster(smem_u32(&bars[2 * kStages + 2]), 0);
+                    if (!stages_free && clock64() - t0 > kWaitCycles) { atomicCAS(p.status, 0, kErrClusterWait); break; }
+                }
+                if (!aborted && stages_free) {
                     const uint32_t remote = cluster_map(smem_u32(partials), 0) +
                                             static_cast<uint32_t>((split - 1) * BLOCK_Q * kBlockP + row_in_tile) * 4u;
 #pragma unroll 1
@@ -548,7 +579,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         }
         if (p.rope_on) {
             const RopeStoreParams& rp = p.rope;
-            int* tpos = reinterpret_cast<int*>(xch + BLOCK_Q * kBlockP);
+            // behind the finished tile and, in a cluster, behind the partial tiles that other threads may still be reading
+            int* tpos = reinterpret_cast<int*>(xch + ((Cfg::kStagesReceive && p.cluster == 2) ? max(1, p.splits - 1) : 1) * BLOCK_Q * kBlockP);
             long long* tbase = reinterpret_cast<long long*>(tpos + BLOCK_Q);
             if (row_in_tile < BLOCK_Q) { tpos[row_in_tile] = tok_pos; tbase[row_in_tile] = tok_base; }
             asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -1017,14 +1049,15 @@ template <int BLOCK_Q, bool TILED>
 static int cluster_capacity(int splits) {
     using Cfg = TcConfig<BLOCK_Q, TILED>;
     static int cached[kMaxClusterSplits + 1] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
-    if (splits < 2 || splits > kMaxClusterSplits || Cfg::smem_bytes(splits) > kMaxSmemPerBlock) return 0;
+    const bool own_place = Cfg::smem_bytes(splits) <= kMaxSmemPerBlock;
+    if (splits < 2 || splits > kMaxClusterSplits || !(own_place || Cfg::cluster_fits(splits))) return 0;
     if (cached[splits] >= 0) return cached[splits];
     int n = 0;
     if (cudaFuncSetAttribute(gemm_tc_kernel<BLOCK_Q, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemPerBlock) == cudaSuccess) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(1, 1, splits);
         cfg.blockDim = dim3(kThreads);
-        cfg.dynamicSmemBytes = Cfg::smem_bytes(splits);
+        cfg.dynamicSmemBytes = own_place ? Cfg::smem_bytes(splits) : Cfg::kSmemBytes;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 1;
@@ -1052,6 +1085,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, TcParams p, d
     // would cost more than the reduce through global memory
     const long long tiles = static_cast<long long>(grid.x) * grid.y;
     p.cluster = (p.splits > 1 && g_cluster_reduce && tiles <= cluster_capacity<BLOCK_Q, TILED>(p.splits)) ? 1 : 0;
+    if (p.cluster && Cfg::smem_bytes(p.splits) > kMaxSmemPerBlock) p.cluster = 2;    // partial tiles in split 0's stages
     if (!p.cluster) {
         launch_kernel((gemm_tc_kernel<BLOCK_Q, TILED>), dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, mp, mq, p);
         return check_launch("gemm_tc");
@@ -1059,7 +1093,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, TcParams p, d
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = Cfg::smem_bytes(p.splits);
+    cfg.dynamicSmemBytes = p.cluster == 2 ? Cfg::kSmemBytes : Cfg::smem_bytes(p.splits);
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -1096,8 +1130,21 @@ extern "C" int gi_gemm_tc_set_cluster(int on) {
 }
 
 // Clusters of `splits` CTAs the device holds at once for the kernel of this block_q (0: the
-// workspace path is used).
+// workspace path is used). A negative count asks the same for -splits with the partial tiles in a
+// place of their own only.
 extern "C" int gi_gemm_tc_cluster_capacity(int block_q, int splits, int tiled) {
+    if (splits < 0) {       // -splits: only if the partial tiles have a place of their own (nobody waits for split 0)
+        splits = -splits;
+        bool own = false;
+        switch (block_q) {
+            case 16: own = (tiled ? TcConfig<16, true>::smem_bytes(splits) : TcConfig<16, false>::smem_bytes(splits)) <= kMaxSmemPerBlock; break;
+            case 32: own = (tiled ? TcConfig<32, true>::smem_bytes(splits) : TcConfig<32, false>::smem_bytes(splits)) <= kMaxSmemPerBlock; break;
+            case 64: own = (tiled ? TcConfig<64, true>::smem_bytes(splits) : TcConfig<64, false>::smem_bytes(splits)) <= kMaxSmemPerBlock; break;
+            case 128: own = (tiled ? TcConfig<128, true>::smem_bytes(splits) : TcConfig<128, false>::smem_bytes(splits)) <= kMaxSmemPerBlock; break;
+            default: break;
+        }
+        if (!own) return 0;
+    }
     switch (block_q) {
         case 16: return tiled ? cluster_capacity<16, true>(splits) : cluster_capacity<16, false>(splits);
         case 32: return tiled ? cluster_capacity<32, true>(splits) : cluster_capacity<32, false>(splits);

@@ -357,14 +357,16 @@ class StepEngine:
         block tables) lives in the descriptor buffer, refreshed before the replay."""
         fresh = any(s.fresh_state for s in ctx.segments) and self.layer_state
         if not (self.use_graphs and ctx.all_single and not fresh):
-            return self.model.forward(ctx)
+            with kernels.on_current_stream():
+                return self.model.forward(ctx)
         key = (ctx.n_tokens, ctx.n_logit_rows, ctx.longest_single)
         entry = self._graphs.get(key)
         if entry is None:
-            out = self.model.forward(ctx)          # also sizes scratch and configures the kernels
+            with kernels.on_current_stream():
+                out = self.model.forward(ctx)      # also sizes scratch and configures the kernels
             before = kernels.launch_count()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph), kernels.on_current_stream():
                 captured = self.model.forward(ctx)
             n_kernels = kernels.launch_count() - before
             kernels.count_launches(-n_kernels)     # captured, not launched

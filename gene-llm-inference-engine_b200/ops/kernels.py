@@ -37,10 +37,30 @@ def count_launches(n: int) -> None:
     _launches += n
 
 
+_scoped_stream: Optional[int] = None
+
+
+class on_current_stream:
+    """Within this block every kernel goes to the stream that is current at its entry: the handle is
+    looked up once instead of at every launch (a few microseconds each, a third of a millisecond of a
+    step that launches 150 kernels). Blocks nest (a graph capture inside a step has its own stream)."""
+
+    def __enter__(self):
+        global _scoped_stream
+        self._outer = _scoped_stream
+        _scoped_stream = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _scoped_stream
+        _scoped_stream = self._outer
+        return False
+
+
 def _stream() -> int:
     global _launches
     _launches += 1
-    return torch.cuda.current_stream().cuda_stream
+    return _scoped_stream if _scoped_stream is not None else torch.cuda.current_stream().cuda_stream
 
 
 def _dev(t: torch.Tensor, name: str, dtype: Optional[torch.dtype] = None) -> int:
@@ -318,12 +338,18 @@ def gemm_tc_cluster_splits(block_q: int, tiles: int, splits: int, tiled: bool = 
     in shared memory instead of through global memory. A property of the device, asked once."""
     key = (block_q, tiles, splits, tiled)
     if key not in _cluster_splits_cache:
-        chosen = splits
-        for s in range(splits, max(1, splits - 3), -1):
-            if s >= 2 and lib().gi_gemm_tc_cluster_capacity(block_q, s, int(tiled)) >= tiles:
-                chosen = s
-                break
-        _cluster_splits_cache[key] = chosen
+        chosen = None
+        # first with the partial tiles in shared memory of their own (no split waits for another), then
+        # in the first split's pipeline stages (it tells the others when they are free)
+        # (the first only while it keeps three quarters of the planned splits: fewer CTAs streaming the
+        # weights cost more than the wait)
+        for sign in (-1, 1):
+            for s in range(splits, max(1, splits - 3), -1):
+                if sign < 0 and 4 * s < 3 * splits:
+                    continue
+                if chosen is None and s >= 2 and lib().gi_gemm_tc_cluster_capacity(block_q, sign * s, int(tiled)) >= tiles:
+                    chosen = s
+        _cluster_splits_cache[key] = chosen or splits
     return _cluster_splits_cache[key]
 
 
@@ -345,6 +371,9 @@ def tile_weight(w: torch.Tensor) -> torch.Tensor:
     return torch.gather(t, 3, src).contiguous().view(-1)        # place q of row r holds piece q ^ (r % 8)
 
 
+_gemm_choice = {}      # (M, N, K, output dtype, tiled weights) -> (swap, block_q, splits, persistent): the sizes decide, once
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, plan=None,
             w_tiles: Optional[torch.Tensor] = None) -> None:
     """out[M,N] (+)= a[M,K] @ w[N,K]^T on the tensor cores: bfloat16 operands, 32-bit accumulation,
@@ -354,15 +383,22 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (M, N):
         raise KernelError(f"gemm: shapes do not agree (a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)})")
-    swap, block_q, splits = plan or gemm_tc_plan(M, N, K)
-    persistent = not swap and out.dtype is torch.float32 and N % 4 == 0 and block_q >= 128
-    if not swap and not persistent:
-        if plan is None and M <= 128:
-            swap, block_q, splits = _swap_plan(M, N, K)      # the persistent kernel cannot write this output
-        else:
-            splits = 1
-    if plan is None and swap and splits > 1:
-        splits = gemm_tc_cluster_splits(block_q, (N + 127) // 128, splits, w_tiles is not None and block_q <= 128)
+    key = (M, N, K, out.dtype, w_tiles is not None) if plan is None else None
+    chosen = _gemm_choice.get(key) if key is not None else None
+    if chosen is None:
+        swap, block_q, splits = plan or gemm_tc_plan(M, N, K)
+        persistent = not swap and out.dtype is torch.float32 and N % 4 == 0 and block_q >= 128
+        if not swap and not persistent:
+            if plan is None and M <= 128:
+                swap, block_q, splits = _swap_plan(M, N, K)      # the persistent kernel cannot write this output
+            else:
+                splits = 1
+        if plan is None and swap and splits > 1:
+            splits = gemm_tc_cluster_splits(block_q, (N + 127) // 128, splits, w_tiles is not None and block_q <= 128)
+        chosen = (swap, block_q, splits, persistent)
+        if key is not None:
+            _gemm_choice[key] = chosen
+    swap, block_q, splits, persistent = chosen
     st = _tc_state(a.device)
     if persistent:
         # many tokens, 32-bit output: the persistent kernel (epilogue overlapped, TMA stores)

@@ -320,6 +320,7 @@ def test_sample_matches_plain_sampler(V, temperature, top_k, top_p):
     (129, 100, 96, (False, 128, 1)), (256, 64, 128, (False, 64, 1)),
     (1, 128, 64, (True, 16, 1)), (7, 384, 96, (True, 16, 1)), (16, 128, 1024, (True, 16, 4)), (8, 2048, 2048, (True, 16, 8)),
     (33, 200, 160, (True, 64, 1)), (64, 300, 1536, (True, 64, 3)), (100, 256, 512, (True, 128, 2)), (20, 130, 264, (True, 32, 2)),
+    (24, 300, 2048, (True, 32, 7)), (60, 256, 4096, (True, 64, 6)), (128, 200, 1024, (True, 128, 4)),   # partial tiles in the first split's stages
 ])
 @pytest.mark.parametrize("c_dtype", ["float32", "bfloat16"])
 def test_gemm_tensor_cores(M, N, K_, plan, c_dtype):
@@ -535,6 +536,7 @@ def test_attention_tcgen05_window(window):
                                                      (257, 3, 3, 32, 16, 128, True), (200, 4, 2, 64, 32, 256, False),
                                                      (8, 5, 1, 64, 16, 192, True), (3, 2, 2, 128, 8, 264, True),
                                                      (40, 6, 2, 32, 16, 128, True), (60, 4, 4, 16, 16, 136, True),
+                                                     (24, 6, 2, 32, 16, 1024, True), (31, 3, 1, 64, 8, 2048, True),
                                                      (17, 3, 1, 64, 16, 200, False)])
 def test_gemm_rope_store_fused(T, H, Hkv, hd, ps, D, rotated, monkeypatch):
     """The [q; k; v] product with rotation and page store in its epilogue against the product followed by
