@@ -231,6 +231,29 @@ def time_prefill(engine, tokens, warmup, vocab, portions=1):
     return sorted(times)[len(times) // 2]
 
 
+SHORT_PROMPT, SHORT_NEW = 16, 64      # the reference arm's workload (its serve bench's own defaults)
+
+
+def time_short_requests(llm, batch, vocab, runs=3):
+    """``batch`` requests of 16 random prompt ids and 64 greedy tokens each through ``Engine.generate``
+    (host token ids in, generated ids out), all submitted together: generated tokens per second of
+    wall time, prompts included; the median of ``runs`` after one warm-up run."""
+    import numpy as np
+    import torch
+    rng = np.random.default_rng(7)
+    prompts = [[int(t) for t in rng.integers(0, vocab, SHORT_PROMPT)] for _ in range(batch)]
+    walls = []
+    for run in range(-1, runs):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = llm.generate(prompts, max_new_tokens=SHORT_NEW, temperature=0.0)
+        torch.cuda.synchronize()
+        if run >= 0:
+            walls.append(time.perf_counter() - t0)
+        assert all(len(o) == SHORT_NEW for o in out)
+    return round(batch * SHORT_NEW / sorted(walls)[len(walls) // 2], 1)
+
+
 def run_ours(args):
     import torch
     from geneinfer_b200 import Engine
@@ -258,10 +281,15 @@ def run_ours(args):
     ms_e2e, h2d, d2h = time_decode_e2e(llm, batch, CONTEXT, args.steps, args.warmup, vocab)
     ms_prefill = time_prefill(llm.steps, PREFILL_TOKENS, max(1, args.warmup), vocab)
     ms_prefill_4 = time_prefill(llm.steps, PREFILL_TOKENS, 1, vocab, portions=4)
-    ms_short, _ = time_decode_device(llm.steps, batch, 128, max(4, args.steps // 2), args.warmup, vocab)
-    bytes_step = step_bytes(model, cfg, batch, CONTEXT)
-    achieved = bytes_step / (ms_step * 1e-3) / 1e9
+    ms_short, _ = time_decode_device(llm.steps, batch, 128, args.steps, args.warmup, vocab)
+    short = {f"short_requests_b{batch}": time_short_requests(llm, batch, vocab)}
     flops = prefill_flops(cfg, PREFILL_TOKENS)
+
+    def roofline(b, context, ms):
+        achieved = step_bytes(model, cfg, b, context) / (ms * 1e-3) / 1e9
+        return {"achieved": round(achieved, 1), "frac": round(achieved / pk["hbm_gbs"], 4)}
+
+    rooflines = {"decode_b8": roofline(batch, CONTEXT, ms_step), "decode_b8_context128": roofline(batch, 128, ms_short)}
     del llm
     torch.cuda.empty_cache()
 
@@ -269,10 +297,13 @@ def run_ours(args):
               "prefill_2048_in_4_portions": round(PREFILL_TOKENS / (ms_prefill_4 * 1e-3), 1)}
     for b in (1, 64):
         e = make(b)
-        ms_b, _ = time_decode_device(e.steps, b, CONTEXT, max(4, args.steps // 2), args.warmup, vocab)
+        ms_b, _ = time_decode_device(e.steps, b, CONTEXT, args.steps, args.warmup, vocab)
         points[f"decode_b{b}"] = round(b / (ms_b * 1e-3), 1)
+        rooflines[f"decode_b{b}"] = roofline(b, CONTEXT, ms_b)
+        short[f"short_requests_b{b}"] = time_short_requests(e, b, vocab)
         del e
         torch.cuda.empty_cache()
+    points.update(short)
 
     value = batch / (ms_step * 1e-3)
     line = {
@@ -294,10 +325,14 @@ def run_ours(args):
                 "d2h_bytes_per_step": d2h, "ms_per_step": round(ms_e2e, 4)},
         "gpu_launches": launches,
         "prefill": {"value": round(PREFILL_TOKENS / (ms_prefill * 1e-3), 1), "tokens": PREFILL_TOKENS,
-                    "ms": round(ms_prefill, 3), "frac": round(flops / (ms_prefill * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+                    "ms": round(ms_prefill, 3), "frac": round(flops / (ms_prefill * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                    "peak": pk["bf16_tflops"], "peak_kind": "cuBLAS bf16 burst, TFLOP/s",
+                    "frac_of_sustained": round(flops / (ms_prefill * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)},
+        "roofline": dict(rooflines["decode_b8"], bound="hbm", peak=pk["hbm_gbs"], unit="GB/s"),
+        "rooflines": rooflines,
         "points": points,
+        "short_requests": "points.short_requests_b*: generated tok/s of b requests of 16 prompt + 64 generated tokens through "
+                          "Engine.generate, wall time with the prompts (the workload of the reference arm)",
         "clocks": clock_record,
     }
     print(json.dumps(line), flush=True)
@@ -340,8 +375,11 @@ def run_scenario(args):
            "config": {"model": f"{shape_name} shape", "layers": cfg["num_hidden_layers"], "requests": n_req,
                       "prompt_tokens": sum(len(p) for p in prompts), "generated_per_request": new, "max_running": running,
                       "step_tokens": 2048, "page_size": PAGE}}
+    dtype = "float32" if args.dtype == "float32" else "bfloat16"
+    out["dtype"] = "fp32" if dtype == "float32" else "bf16"
+    results = {}
     for name, cache_on in variants:
-        llm = Engine(folder, dtype="bfloat16", max_seq_len=longest, page_size=PAGE, kv_pages=pages, max_running=running,
+        llm = Engine(folder, dtype=dtype, max_seq_len=longest, page_size=PAGE, kv_pages=pages, max_running=running,
                      step_tokens=2048, prefix_cache=cache_on)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
@@ -360,6 +398,7 @@ def run_scenario(args):
         bad = [r.error or len(r.generated_tokens) for r in res if r.error or len(r.generated_tokens) != new]
         if bad:
             raise RuntimeError(f"scenario {args.scenario}: requests did not finish as expected: {bad[:4]}")
+        results[name] = [list(r.generated_tokens) for r in res]
         st = llm.stats
         out[name] = {"seconds": round(dt, 3), "generated_tok_s": round(n_req * new / dt, 1),
                      "all_tok_s": round((sum(len(p) for p in prompts) + n_req * new) / dt, 1), "steps": st.steps,
@@ -371,18 +410,121 @@ def run_scenario(args):
             raise RuntimeError("scenario: pages were lost")
         del llm
         torch.cuda.empty_cache()
+    # a sampled subset again, each request alone (the reference's serve bench compares every request with its run
+    # alone, bench/serve_bench_main.cpp:18,202). In 32-bit every output is one fixed chain of operations, so the tokens
+    # must be identical; in bfloat16 a product of 1 token and one of 2,048 round differently, and the nearly flat logits
+    # of random weights let a near-tie fall either way: there the count is reported, with the first place that differs.
+    order = sorted(range(n_req), key=lambda i: len(prompts[i]))
+    subset = sorted({order[0], order[n_req // 2], order[-1]})
+    alone = Engine(folder, dtype=dtype, max_seq_len=longest, page_size=PAGE, kv_pages=(longest + PAGE - 1) // PAGE + 1,
+                   max_running=1, step_tokens=2048, prefix_cache=False)
+    same, first_diff = 0, None
+    for i in subset:
+        got = alone.generate([prompts[i]], max_new_tokens=new, temperature=0.0)[0]
+        batched = results[variants[0][0]][i]
+        if got == batched:
+            same += 1
+        elif first_diff is None:
+            first_diff = {"request": i, "token": next(k for k in range(new) if got[k] != batched[k])}
+    out["alone"] = {"requests_checked": len(subset), "identical_to_running_alone": same, "first_difference": first_diff}
+    if dtype == "float32" and same != len(subset):
+        raise RuntimeError(f"scenario {args.scenario}: in 32-bit a request generated other tokens than alone: {first_diff}")
     out["value"] = out[variants[0][0]]["generated_tok_s"]
     out["unit"] = "tok/s"
     print(json.dumps(out), flush=True)
     return 0
 
 
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+REF_RUNS = 3
+
+
+def reference_binary():
+    """Path of the reference's own serve bench built with its CUDA backend, or (None, why). The
+    reference is a CMake project (pip has nothing to install); its stock ``gi_serve_bench`` is built
+    from the unmodified source tree into baseline/_ref/build when it is not there yet."""
+    exe = os.path.join(REF_DIR, "build", "gi_serve_bench")
+    if os.path.isfile(exe) and os.access(exe, os.X_OK):
+        return exe, None
+    src = os.environ.get("GI_REFERENCE_SRC") or os.path.join(os.path.dirname(ROOT), "reference")
+    if not os.path.isfile(os.path.join(src, "CMakeLists.txt")):
+        return None, f"the reference's source tree is not at {src} and no built gi_serve_bench is under baseline/_ref/build"
+    os.makedirs(REF_DIR, exist_ok=True)
+    steps = (["cmake", "-S", src, "-B", os.path.join(REF_DIR, "build"), "-DCMAKE_BUILD_TYPE=Release", "-DGI_CUDA=ON",
+              "-DCMAKE_CUDA_ARCHITECTURES=100"],
+             ["cmake", "--build", os.path.join(REF_DIR, "build"), "--target", "gi_serve_bench", "-j", "8"])
+    env = dict(os.environ)
+    if os.path.isfile("/usr/local/cuda/bin/nvcc"):
+        env.setdefault("CUDACXX", "/usr/local/cuda/bin/nvcc")
+    for cmd in steps:
+        try:
+            p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=1200, env=env)
+        except (OSError, subprocess.TimeoutExpired) as e:
+            return None, f"building the reference failed: {e}"
+        if p.returncode != 0:
+            tail = [l for l in p.stdout.splitlines() if l.strip()][-3:]
+            return None, "building the reference with its CMake files failed: " + " | ".join(tail)[:400]
+    return (exe, None) if os.path.isfile(exe) else (None, "the reference's build produced no gi_serve_bench")
+
+
 def run_reference(args):
-    # The reference is a CMake project without setup.py or pyproject.toml:
-    # `pip install --no-index --target baseline/_ref <reference>` answers "not installable".
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "pip cannot install the reference: it is a CMake C++ project with neither setup.py nor pyproject.toml"}),
-          flush=True)
+    """The unmodified reference through its own serve bench and CUDA backend, on the random model
+    folder this bench writes: 8 requests of 16 prompt + 64 generated tokens run together, the
+    workload that finishes (at context 8192 its run printed nothing within 15 minutes and is not
+    run again). Nothing of this repository's models, kernels or engine is on this path."""
+    if args.gpus != 1:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's device backend runs on one GPU"}), flush=True)
+        return 0
+    exe, why = reference_binary()
+    if exe is None:
+        print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+        return 0
+    shape_name, shape = SHAPES["1b"]
+    cfg = dict(shape)
+    folder = model_folder(cfg)
+    batch = 8
+    cmd = [exe, "--model", folder, "--device", "cuda", "--concurrency", str(batch), "--prompt-tokens", str(SHORT_PROMPT),
+           "--decode-tokens", str(SHORT_NEW), "--runs", str(REF_RUNS), "--max-seq-len", "256"]
+    clocks = ClockSampler()
+    clocks.start()
+    try:
+        p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=1500)
+    except (OSError, subprocess.TimeoutExpired) as e:
+        clocks.stop()
+        print(json.dumps({"impl": "reference", "unavailable": f"gi_serve_bench did not finish: {e}"}), flush=True)
+        return 0
+    clock_record = clocks.stop()
+    row = None
+    for l in p.stdout.splitlines():
+        f = l.split()
+        if len(f) >= 8 and f[0] == str(batch):
+            try:
+                row = (float(f[1]), float(f[2]), float(f[4]), " ".join(f[7:]))
+            except ValueError:
+                pass
+    if row is None:
+        tail = " | ".join([l for l in p.stdout.splitlines() if l.strip()][-3:])[:400]
+        print(json.dumps({"impl": "reference", "unavailable": f"gi_serve_bench gave no result line (exit {p.returncode}): {tail}"}),
+              flush=True)
+        return 0
+    wall, tps, rows_per_pass, outputs = row
+    line = {
+        "metric": f"generated tok/s, {batch} concurrent requests of {SHORT_PROMPT} prompt + {SHORT_NEW} generated tokens "
+                  f"({shape_name} shape, random bf16 weights), wall time with the prompts",
+        "value": tps, "unit": "tok/s", "n_gpus": 1, "impl": "reference", "same_config": False,
+        "steps": REF_RUNS * SHORT_NEW, "warmup": SHORT_NEW, "ms_per_step": round(wall / SHORT_NEW * 1e3, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 weights; 32-bit activations and cache (the reference's device backend)",
+        "data": "synthetic: the same random model folder as the other arm, the tool's own random token ids",
+        "config": {"model": f"{shape_name} shape", "global_batch": batch, "seq_len": SHORT_PROMPT + SHORT_NEW,
+                   "parallelism": "single GPU", "tool": "gi_serve_bench --device cuda", "runs": REF_RUNS,
+                   "rows_per_pass": rows_per_pass, "outputs": outputs,
+                   "compare_with": "points.short_requests_b8 of the other arm (the same workload through Engine.generate)",
+                   "why_not_context_8192": "the reference's run at context 8192 printed no result within 15 minutes"},
+        "e2e": {"value": tps, "unit": "tok/s", "note": "the tool's own wall clock: token ids from the host in, generated ids out"},
+        "clocks": clock_record,
+    }
+    print(json.dumps(line), flush=True)
     return 0
 
 
@@ -394,6 +536,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0 = all)")
     ap.add_argument("--shape", choices=sorted(SHAPES), default="1b", help="layer sizes (the default is the baseline's third configuration)")
+    ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
+                    help="precision of a --scenario run (float32: the requests run alone must give identical tokens)")
     ap.add_argument("--scenario", choices=["mixed", "prefix"], default="", help="a workload through the scheduler instead of the default run")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -1,8 +1,8 @@
 """Small workloads of single kernels and of whole steps, for timing and for profiler captures.
 
-    python -m geneinfer_b200.cli.kernel_cases <case> [--batch B] [--context C] [--tokens T] [--layers L] [--repeat R]
+    python bench_kernels.py <case> [--shape 1b|3b|8b] [--batch B] [--context C] [--tokens T] [--layers L] [--repeat R]
 
-Cases at the Llama-3.2-1B layer sizes (random data, sizes larger than L2 where bandwidth matters):
+Cases at the layer sizes of one of bench.py's shapes (random data, sizes larger than L2 where bandwidth matters):
   gemm_prefill       the four products of a layer for T tokens (tensor cores, persistent kernel)
   gemm_decode        the same products for B tokens (weights on the 128-row side, read tile by tile, split over K)
   attention_decode   B single tokens, each over a context of C cached positions
@@ -20,7 +20,20 @@ import sys
 
 import torch
 
-D, H, HKV, HD, I, V, PAGE = 2048, 32, 8, 64, 8192, 128256, 16
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import bench  # noqa: E402  (the shapes and the model folder are bench.py's)
+
+PAGE = bench.PAGE
+D = H = HKV = HD = I = V = 0          # layer sizes of the chosen shape, set by main()
+
+
+def _set_shape(name: str) -> dict:
+    global D, H, HKV, HD, I, V
+    cfg = dict(bench.SHAPES[name][1])
+    D, H, HKV, HD = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    I, V = cfg["intermediate_size"], cfg["vocab_size"]
+    return cfg
 
 
 def _time(name, fn, repeat, nbytes=0, flops=0):
@@ -109,14 +122,11 @@ def attention_prefill_case(tokens, repeat, dev, kernels):
               repeat, flops=2 * tokens * tokens * HD * H)
 
 
-def step_case(kind, batch, context, tokens, layers, repeat):
-    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-    sys.path.insert(0, root)
-    import bench
+def step_case(kind, shape_cfg, batch, context, tokens, layers, repeat):
     from geneinfer_b200 import Engine
     from geneinfer_b200.engine.step import StepEntry
     from geneinfer_b200.ops import kernels
-    cfg = dict(bench.LLAMA_1B, num_hidden_layers=layers)
+    cfg = dict(shape_cfg, num_hidden_layers=layers or shape_cfg["num_hidden_layers"])
     folder = bench.model_folder(cfg)
     llm = Engine(folder, dtype="bfloat16", max_seq_len=max(context, tokens), page_size=PAGE,
                  kv_pages=batch * ((max(context, tokens) + PAGE - 1) // PAGE), max_running=batch, step_tokens=max(tokens, batch),
@@ -131,7 +141,7 @@ def step_case(kind, batch, context, tokens, layers, repeat):
         def run(i):
             logits = eng.step([StepEntry(k, [17 + i], [0]) for k in keys])
             kernels.argmax(logits, ids)
-        _time(f"decode step B={batch} context={context} layers={layers} (direct launches)", run, repeat)
+        _time(f"decode step B={batch} context={context} layers={cfg['num_hidden_layers']} (direct launches)", run, repeat)
     else:
         toks = torch.randint(0, V, (tokens,)).tolist()
 
@@ -139,20 +149,22 @@ def step_case(kind, batch, context, tokens, layers, repeat):
             eng.open("p")
             eng.step([StepEntry("p", toks, [tokens - 1])])
             eng.close("p")
-        _time(f"prefill step T={tokens} layers={layers}", run, repeat)
+        _time(f"prefill step T={tokens} layers={cfg['num_hidden_layers']}", run, repeat)
 
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     ap.add_argument("case", choices=["gemm_prefill", "gemm_decode", "attention_decode", "attention_prefill", "decode_step",
                                      "prefill_step"])
+    ap.add_argument("--shape", choices=sorted(bench.SHAPES), default="1b")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--tokens", type=int, default=2048)
-    ap.add_argument("--layers", type=int, default=16)
+    ap.add_argument("--layers", type=int, default=0, help="layers of the step cases (0 = all of the shape)")
     ap.add_argument("--repeat", type=int, default=10)
     a = ap.parse_args()
-    from ..ops import kernels
+    from geneinfer_b200.ops import kernels
+    shape_cfg = _set_shape(a.shape)
     dev = torch.device("cuda:0")
     if a.case == "gemm_prefill":
         gemm_case(a.tokens, a.repeat, dev, kernels)
@@ -163,7 +175,7 @@ def main() -> int:
     elif a.case == "attention_prefill":
         attention_prefill_case(a.tokens, a.repeat, dev, kernels)
     else:
-        step_case(a.case, a.batch, a.context, a.tokens, a.layers, a.repeat)
+        step_case(a.case, shape_cfg, a.batch, a.context, a.tokens, a.layers, a.repeat)
     status = kernels.gemm_tc_status(dev)
     print(f"status word: {status}")
     return 0 if status == 0 else 1

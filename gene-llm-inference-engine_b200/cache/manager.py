@@ -265,6 +265,29 @@ class CacheManager:
         rc.length = rc.reserved = len(pages) * self.page_size
         rc.fresh_state = False
 
+    def fork(self, src: RequestCache, key: Hashable, length: Optional[int] = None) -> RequestCache:
+        """Opens a request that starts on the first ``length`` cached positions of ``src`` (all of
+        them by default) and shares the pages that hold them (the reference pairs KvPool::retain
+        with Sequence::adopt and truncate for this, tools/multiseq_check_main.cpp:279-286). Neither
+        request sees what the other writes afterwards: ``reserve`` copies a shared page before a
+        request writes into it (copy-on-write)."""
+        if len(self.groups) != 1 or self.groups[0].need.window or self.state_layers:
+            raise RuntimeError("fork: only models with one full-attention group and no state can share pages")
+        n = src.length if length is None else int(length)
+        if src.closed or not (0 < n <= src.length):
+            raise ValueError(f"fork: length {n} is outside the {src.length} cached positions of {src.key!r}")
+        rc = self.open(key)
+        pages = (n + self.page_size - 1) // self.page_size
+        pool = self.groups[0].pool
+        for i in range(pages):
+            p = int(src.tables[0][i])
+            pool.retain(p)
+            rc.tables[0][i] = p
+        rc.n_pages[0] = pages
+        rc.length = rc.reserved = n
+        rc.fresh_state = False
+        return rc
+
     # ------------------------------------------------------------------ checks
     def check_invariants(self) -> None:
         """No page lost, none held by two tables without two references, none freed twice."""

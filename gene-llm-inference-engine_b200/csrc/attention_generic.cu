@@ -144,6 +144,9 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
 
 using namespace gi;
 
+// 1 when the general kernel serves this head size: the model is refused when it is built, not at its first step.
+extern "C" int gi_attention_generic_supported(int hd) { return hd % 16 == 0 && hd >= 16 && hd <= kMaxHeadDim; }
+
 extern "C" int gi_attention_generic(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
                                     const int* row_req, const int* positions, const int* block_tables,
                                     int table_stride, int T, int H, int Hkv, int hd, int page_size, float scale,

@@ -19,9 +19,14 @@ extern "C" {
 
 // Same result as gi_sample (one token id per row of logits [rows, vocab] under temperature,
 // top-k and top-p, with the caller's uniform number per row), but without a scratch argument.
+//   * A row whose temperature is <= 0 (greedy) is left alone: out[row] keeps the value the caller
+//     put there. As with gi_sample, write the row's argmax into out (gi_argmax) before this call if
+//     greedy rows are mixed with sampled ones; a row that is never written is not a token id.
 //   * Allocates nothing: no cudaMalloc, cudaFree or allocating library call, on any call.
 //   * The first call on a device looks up the device address of the built-in work area (with that
 //     device current) and remembers it; make that first call before any stream capture begins.
+//     The address is remembered for the life of the process: after cudaDeviceReset() it is stale,
+//     so a process that resets the device must not call this entry point afterwards.
 //   * rows * vocab above GI_SAMPLE_NO_ALLOC_MAX_FLOATS is refused with an error (non-zero return,
 //     message from gi_last_error()), never truncated.
 //   * All calls on a device share the one work area, which keeps what the last call left there.

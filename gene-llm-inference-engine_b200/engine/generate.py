@@ -94,6 +94,8 @@ class Engine:
                  top_k: int = 0, top_p: float = 1.0, seed: int = 1, stop_ids: Sequence[int] = ()) -> List[List[int]]:
         """Generates up to ``max_new_tokens`` for every prompt (all requests run together) and
         returns the generated token ids. Request i samples with seed ``seed + i``."""
+        if max_new_tokens <= 0:
+            return [[] for _ in prompts]
         ids = []
         for i, p in enumerate(prompts):
             params = SamplingParams(temperature, top_k, top_p, seed + i)

@@ -1,6 +1,10 @@
-"""Per-kernel timing of one decode step, for ``gi_generate --profile``: every kernel wrapper is
-timed with CUDA events around one more step of the finished request's context (the idea of the
-reference's per-section report, src/gpu/gpu_transformer.cpp:178-222)."""
+"""Per-operation timing of one decode step, for ``gi_generate --profile``, in the manner of the
+reference's device profile (src/gpu/gpu_transformer.cpp:178-222): one line per kind of operation
+with its time, its share of the step and, for matrix products, the rate at which the weights were
+read. Every kernel wrapper is timed with a pair of CUDA events; the timed step runs outside CUDA
+graphs (events inside a captured graph measure nothing), so the kernels do not overlap their
+neighbours as they do in serving and the sum is an upper bound of the step's time.
+"""
 from __future__ import annotations
 
 from collections import defaultdict
@@ -9,40 +13,70 @@ import torch
 
 from ..ops import kernels
 
+# wrapper in ops.kernels -> (operation as the report names it, index of its weight argument or None)
+OPERATIONS = {
+    "embed": ("embedding lookup", None),
+    "rmsnorm": ("rmsnorm", None),
+    "gemm_rope_store": ("q/k/v projections + rope + store", 1),
+    "rope_store": ("rope + store", None),
+    "attention_generic": ("attention", None),
+    "attention_decode": ("attention", None),
+    "attention_prefill": ("attention", None),
+    "attention_prefill_tc": ("attention", None),
+    "gemm_tc": ("matrix products (tensor cores)", 1),
+    "gemm_simt": ("matrix products (32-bit)", 1),
+    "gemm_swiglu": ("ffn gate+up with silu * up", 1),
+    "swiglu": ("silu * up", None),
+    "copy_pages": ("page copies", None),
+    "argmax": ("sampling", None),
+    "sample": ("sampling", None),
+}
+
 
 def profile_report(engine, prompt) -> str:
+    """Feeds ``prompt`` (all but its last token untimed), then times one decode step at that context."""
+    from ..sampling.params import SamplingParams
     from .step import StepEntry
-    names = ["embed", "rmsnorm", "swiglu", "rope_store", "attention_generic", "gemm_simt", "argmax"]
-    names += [n for n in ("gemm_bf16", "attention_decode", "attention_prefill") if hasattr(kernels, n)]
     records = defaultdict(list)
-    saved = {n: getattr(kernels, n) for n in names}
+    saved = {name: getattr(kernels, name) for name in OPERATIONS}
 
     def timed(name, fn):
+        label, weight_arg = OPERATIONS[name]
+
         def wrapper(*a, **k):
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
             out = fn(*a, **k)
             e.record()
-            records[name].append((s, e))
+            w = a[weight_arg] if weight_arg is not None and len(a) > weight_arg else None
+            records[label].append((s, e, w.numel() * w.element_size() if w is not None else 0))
             return out
         return wrapper
 
     steps = engine.steps
-    n = min(len(prompt), steps.model.max_position - 1)
+    n = max(1, min(len(prompt), steps.model.max_position) - 1)
+    graphs = steps.use_graphs
     steps.open("profile")
     try:
-        steps.step([StepEntry("profile", list(prompt[:n]), [])])
-        for name in names:
+        if n > 1 or len(prompt) > 1:
+            steps.step([StepEntry("profile", list(prompt[:n]), [])])
+        steps.use_graphs = False
+        for name in OPERATIONS:
             setattr(kernels, name, timed(name, saved[name]))
-        steps.step([StepEntry("profile", [int(prompt[0])], [0])])
+        logits = steps.step([StepEntry("profile", [int(prompt[min(n, len(prompt) - 1)])], [0])])
+        engine.sampler.sample(logits, [SamplingParams(0.0)], [0.0])      # the step's greedy pick belongs to it
         torch.cuda.synchronize()
     finally:
-        for name in names:
+        for name in OPERATIONS:
             setattr(kernels, name, saved[name])
+        steps.use_graphs = graphs
         steps.close("profile")
-    total = sum(s.elapsed_time(e) for v in records.values() for s, e in v) or 1e-9
-    lines = [f"[profile] one decode step at context {n}: {total:.3f} ms in kernels"]
-    for name, v in sorted(records.items(), key=lambda kv: -sum(s.elapsed_time(e) for s, e in kv[1])):
-        ms = sum(s.elapsed_time(e) for s, e in v)
-        lines.append(f"[profile]   {name:<20} {len(v):4d} launches {ms:9.3f} ms {100 * ms / total:5.1f} %")
+    per = {label: (len(v), sum(s.elapsed_time(e) for s, e, _ in v), sum(b for _, _, b in v)) for label, v in records.items()}
+    total = sum(ms for _, ms, _ in per.values()) or 1e-9
+    lines = [f"device profile: one decode step at context {n}, "
+             f"{total:.3f} ms in {sum(c for c, _, _ in per.values())} timed operations (outside CUDA graphs, nothing overlaps)",
+             f"  {'operation':<36} {'calls':>5} {'ms':>9} {'share':>7} {'weights GB/s':>13}"]
+    for label, (count, ms, nbytes) in sorted(per.items(), key=lambda kv: -kv[1][1]):
+        rate = f"{nbytes / (ms * 1e-3) / 1e9:.1f}" if nbytes and ms > 0 else ""
+        lines.append(f"  {label:<36} {count:>5} {ms:>9.3f} {100 * ms / total:>6.1f}% {rate:>13}")
     return "\n".join(lines) + "\n"

@@ -55,6 +55,7 @@ class StepContext:
         self.segments = segments
         self.page_size = engine.page_size
         self.max_requests = engine.max_requests
+        self.max_logit_rows = engine.max_logit_rows
         self.compute_dtype = engine.model.dtype
         self.tokens = views["tokens"]
         self.feedback = engine.feedback          # sampled ids of the step before, for tokens given as -(k + 1)
@@ -91,6 +92,14 @@ class StepContext:
 
     def scratch(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype, capacity: Optional[int] = None) -> torch.Tensor:
         return self._engine.scratch(name, shape, dtype, capacity)
+
+    def tap(self, tag: str, layer: int, tensor: torch.Tensor) -> None:
+        """Shows an intermediate activation to whoever listens (``StepEngine.tap``); the tags follow
+        the reference's trace callback (src/model/model.h:16-22): "embedding", "attn_out" and
+        "ffn_out" (the residual stream [tokens, hidden] after a layer's mixer / feed-forward; layer
+        -1 for tensors outside the layers) and "final_norm" ([wanted rows, hidden])."""
+        if self._engine.tap is not None:
+            self._engine.tap(tag, layer, tensor, self)
 
     def attention_work(self, tokens_per_tile: int):
         """How this step's rows are shared between the two attention kernels: (rows of requests
@@ -166,23 +175,41 @@ class StepEngine:
             for layer in model.layers)
         self._graphs: Dict[Tuple, Tuple] = {}
         self.graph_replays = 0
+        # a listener for intermediate activations: tap(tag, layer, tensor, ctx); steps run outside graphs while it is set
+        self.tap = None
+        # the kernels' status word (a bounded wait that gave up) follows every step to pinned memory
+        self._status_host = [torch.zeros(1, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._status_events: List[Optional[torch.cuda.Event]] = [None] * 4
+        self._status_next = 0
+        self.scratch_generation = 0     # counts replaced scratch buffers: what was recorded before is stale
 
     # ------------------------------------------------------------------ memory
+    # a buffer is given its full capacity at once while that stays below this many bytes; a larger one
+    # (logits of thousands of wanted rows at a large vocabulary) grows as steps ask for more rows
+    _SCRATCH_AT_ONCE = 64 << 20
+
     def scratch(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype, capacity: Optional[int] = None) -> torch.Tensor:
         """A reusable buffer; the same name, trailing shape and dtype give the same memory each step.
-        ``capacity`` is the most rows the buffer will ever need (default: the step's token limit)."""
+        ``capacity`` is the most rows the buffer will ever need (default: the step's token limit).
+        When a buffer has to grow, every captured graph is dropped first: a graph holds the addresses
+        of the buffers it was captured with, and the old buffer goes back to the allocator."""
         key = (name, tuple(shape[1:]), dtype)
         buf = self._scratch.get(key)
         if buf is None or buf.shape[0] < shape[0]:
-            if name in ("logits", "head_in"):      # wanted rows are usually few: grow on demand
-                rows = min(self.max_logit_rows, max(8, 1 << (shape[0] - 1).bit_length()))
-            elif capacity is not None:
-                rows = max(shape[0], capacity)
-            else:
-                rows = max(shape[0], self.max_step_tokens)
+            most = max(shape[0], capacity if capacity is not None else self.max_step_tokens)
+            row_bytes = max(1, int(np.prod(shape[1:], dtype=np.int64)) * torch.empty((), dtype=dtype).element_size())
+            at_once = max(8, self._SCRATCH_AT_ONCE // row_bytes)
+            rows = most if most <= at_once else min(most, max(at_once, 1 << (shape[0] - 1).bit_length()))
+            if buf is not None:
+                self._drop_captures()
             buf = torch.empty((rows, *shape[1:]), dtype=dtype, device=self.device)
             self._scratch[key] = buf
         return buf[:shape[0]]
+
+    def _drop_captures(self) -> None:
+        """Forgets everything that holds addresses of scratch memory (called before a buffer is replaced)."""
+        self._graphs.clear()
+        self.scratch_generation += 1
 
     def _init_descriptor(self) -> None:
         """One int32 buffer holds everything the kernels read about a step's rows and requests; a
@@ -239,6 +266,11 @@ class StepEngine:
     def close(self, key: Hashable) -> None:
         self.cache.close(self.cache.requests[key])
 
+    def fork(self, key: Hashable, new_key: Hashable, length: Optional[int] = None) -> RequestCache:
+        """A new request on the first ``length`` cached positions of ``key`` (all by default), sharing
+        their pages; the first step that writes into a shared page copies it on the device first."""
+        return self.cache.fork(self.cache.requests[key], new_key, length)
+
     def length(self, key: Hashable) -> int:
         return self.cache.requests[key].length
 
@@ -279,6 +311,8 @@ class StepEngine:
             raise ValueError(f"{len(entries)} requests in one step exceed the limit {self.max_requests}")
         if n_want > self.max_logit_rows:
             raise ValueError(f"{n_want} wanted rows exceed the limit {self.max_logit_rows}")
+
+        self._poll_status(wait=False)      # before anything is reserved: an earlier step's failure ends this call
 
         # ---- reserve pages for every entry, all or nothing
         reserved: List[RequestCache] = []
@@ -345,6 +379,7 @@ class StepEngine:
                     st[seg.state_slot].zero_()
         ctx = StepContext(self, total, R, k, segments, views)
         logits = self._run(ctx)
+        self._post_status()
         for e in entries:
             self.cache.advance(self.cache.requests[e.key], len(e.tokens))
         return logits
@@ -356,7 +391,7 @@ class StepEngine:
         the host. Everything a replay reads that changes from step to step (tokens, positions,
         block tables) lives in the descriptor buffer, refreshed before the replay."""
         fresh = any(s.fresh_state for s in ctx.segments) and self.layer_state
-        if not (self.use_graphs and ctx.all_single and not fresh):
+        if not (self.use_graphs and ctx.all_single and not fresh and self.tap is None):
             with kernels.on_current_stream():
                 return self.model.forward(ctx)
         key = (ctx.n_tokens, ctx.n_logit_rows, ctx.longest_single)
@@ -377,6 +412,44 @@ class StepEngine:
         self.graph_replays += 1
         kernels.count_launches(n_kernels)
         return captured
+
+    # ------------------------------------------------------------------ the kernels' status word
+    def _post_status(self) -> None:
+        """Sends the status word after the step's kernels to pinned memory (no wait)."""
+        slot = self._status_next
+        self._status_next = (slot + 1) % len(self._status_host)
+        if self._status_events[slot] is not None:
+            self._status_events[slot].synchronize()
+            self._raise_on(self._status_host[slot])
+        self._status_host[slot].copy_(kernels.status_word(self.device), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._status_events[slot] = ev
+
+    def _poll_status(self, wait: bool) -> None:
+        """Looks at the status words of steps that have finished (of all steps with ``wait``) and
+        raises ``KernelError`` if a kernel recorded that one of its bounded waits gave up: what
+        that step computed is not to be trusted."""
+        for slot, ev in enumerate(self._status_events):
+            if ev is not None and (wait or ev.query()):
+                ev.synchronize()
+                self._status_events[slot] = None
+                self._raise_on(self._status_host[slot])
+
+    def _raise_on(self, word: torch.Tensor) -> None:
+        code = int(word[0])
+        if code:
+            word[0] = 0
+            kernels.status_word(self.device).zero_()
+            for i in range(len(self._status_events)):
+                self._status_events[i] = None
+            raise kernels.KernelError(f"a kernel gave up a bounded wait (status {code:#x}): the results of the "
+                                      f"last steps are not valid")
+
+    def check_status(self) -> None:
+        """Waits for the steps launched so far and raises if any kernel reported a failed wait.
+        Callers that read logits themselves call this before they trust them."""
+        self._poll_status(wait=True)
 
     def _copy_pages(self, copies) -> None:
         for g, pages in enumerate(self.group_pages):

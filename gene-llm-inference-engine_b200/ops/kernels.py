@@ -170,6 +170,11 @@ def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         head_dim, page_size, float(scale), int(window or 0), _stream()), "attention")
 
 
+def attention_supported(head_dim: int) -> bool:
+    """Whether any attention kernel of the library serves this head size (multiples of 16 up to 256)."""
+    return bool(lib().gi_attention_generic_supported(head_dim))
+
+
 def attention_fast_supported(head_dim: int, num_heads: int, num_kv_heads: int) -> bool:
     """Whether the tensor-core attention kernels are built for this head size and grouping."""
     return bool(lib().gi_attention_fast_supported(head_dim, num_heads, num_kv_heads))
@@ -272,9 +277,16 @@ class _TensorCoreState:
     COUNTERS = 4096
 
     def __init__(self, device: torch.device):
-        self.workspace = torch.empty(self.WORKSPACE_FLOATS, dtype=torch.float32, device=device)
+        self.device = device
+        self._workspace = None
         self.counters = torch.zeros(self.COUNTERS, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    @property
+    def workspace(self) -> torch.Tensor:
+        if self._workspace is None:        # only products split over K need it (the 32-bit path never does)
+            self._workspace = torch.empty(self.WORKSPACE_FLOATS, dtype=torch.float32, device=self.device)
+        return self._workspace
 
 
 _tc_states = {}
@@ -287,6 +299,22 @@ def _tc_state(device: torch.device) -> _TensorCoreState:
     return _tc_states[key]
 
 
+_B200_SMS = 148          # only for looking at plans on a machine without a device
+_sm_count: Optional[int] = None
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the device the kernels run on (asked once); the plans below
+    size their grids by it. Without a device (plans examined on a CPU) the B200's count."""
+    global _sm_count
+    if _sm_count is None:
+        if torch.cuda.is_available():
+            _sm_count = int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+        else:
+            return _B200_SMS
+    return _sm_count
+
+
 def _persistent_plan(M: int, N: int, K: int):
     block_q = 256 if N >= 256 else 128 if N > 64 else 64
     splits = 1
@@ -295,7 +323,7 @@ def _persistent_plan(M: int, N: int, K: int):
         # so that about as many work items as SMs exist, each with at least 8 steps of 64
         tiles = ((M + 127) // 128) * ((N + block_q - 1) // block_q)
         k_blocks = (K + 63) // 64
-        splits = max(1, min(8, 148 // tiles, k_blocks // 8))
+        splits = max(1, min(8, sm_count() // tiles, k_blocks // 8))
         if splits < 3 and k_blocks < 64:
             splits = 1           # measured: two ranges of a short K cost more (a second kernel adds them) than they save
     return False, block_q, splits
@@ -321,10 +349,11 @@ def _swap_plan(M: int, N: int, K: int):
     block_q = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
     tiles = (N + 127) // 128
     k_blocks = (K + 63) // 64
-    # split K until about 100 CTAs stream weights, keeping at least 4 steps of 64 per CTA
-    # (measured on B200 at the Llama-3.2-1B widths: 4 splits for 24 tiles, 6..8 for 16, 1 for 128)
+    # split K until about three quarters of the SMs stream weights (112 CTAs on a B200), keeping at least
+    # 4 steps of 64 per CTA (measured on B200 at the Llama-3.2-1B widths: 4 splits for 24 tiles, 6..8 for 16, 1 for 128)
+    streaming = sm_count() * 3 // 4 + 1
     splits = 1
-    while tiles * (splits + 1) <= 112 and k_blocks // (splits + 1) >= 4 and splits < 8:
+    while tiles * (splits + 1) <= streaming and k_blocks // (splits + 1) >= 4 and splits < 8:
         splits += 1
     return True, block_q, splits
 
@@ -495,6 +524,11 @@ def gemm_rope_store(a: torch.Tensor, w_qkv: torch.Tensor, positions: torch.Tenso
     else:
         check(lib().gi_gemm_tc_persistent_rope(_dev(a, "a", torch.bfloat16), _dev(w_qkv, "w_qkv", torch.bfloat16), M, K, K, K,
                                                *rope_args, st.status.data_ptr(), _stream()), "gemm_rope_store")
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The device word [1] (int32) in which a kernel records a bounded wait that gave up (0 = none)."""
+    return _tc_state(device).status
 
 
 def gemm_tc_status(device: torch.device) -> int:

@@ -52,6 +52,7 @@ _SIGNATURES = {
                                 c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p, c_void_p],
     "gi_attention_prefill_tc_supported": [c_int, c_int, c_int, c_int],
     "gi_attention_fast_supported": [c_int, c_int, c_int],
+    "gi_attention_generic_supported": [c_int],
     "gi_attention_chunk_keys": [],
     "gi_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "gi_sample": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],

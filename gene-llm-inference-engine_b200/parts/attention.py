@@ -32,6 +32,9 @@ class AttentionMixer:
         self.window = params.get("window")
         if self.num_heads % self.num_kv_heads:
             raise ValueError("attention: num_heads must be a multiple of num_kv_heads")
+        if not kernels.attention_supported(self.head_dim):
+            raise ValueError(f"attention: head size {self.head_dim} is not supported by the attention kernels "
+                             f"(multiples of 16 up to 256)")
         pos_spec = params.get("position") or PartSpec("none", {})
         self.position = build_part(POSITION_ENCODINGS, "position encoding", pos_spec, {}, build)
         qkv_rows = (self.num_heads + 2 * self.num_kv_heads) * self.head_dim

@@ -24,5 +24,7 @@ class PreNormBlock:
         xn = ctx.scratch("normed", tuple(x.shape), self.dtype)
         self.mixer_norm.forward(x, xn)
         self.mixer.forward(ctx, run, xn, x)
+        ctx.tap("attn_out", run.layer, x)
         self.feed_forward_norm.forward(x, xn)
         self.feed_forward.forward(ctx, xn, x)
+        ctx.tap("ffn_out", run.layer, x)

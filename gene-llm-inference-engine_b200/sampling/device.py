@@ -19,11 +19,20 @@ _RING = 4          # samples that may be in flight before the oldest must have b
 class PendingSample:
     """The token ids of one sampling call, on their way to the host."""
 
-    def __init__(self, host: torch.Tensor, rows: int, event: torch.cuda.Event):
-        self._host, self._rows, self._event = host, rows, event
+    def __init__(self, host: torch.Tensor, rows: int, event, status: Optional[torch.Tensor] = None, on_failure=None):
+        """``status``: the host copy [1] of the kernels' status word, taken behind the ids; a value
+        other than 0 says that a kernel of the steps before gave up a bounded wait, so the ids are
+        not to be trusted. ``on_failure`` is called (to clear the device's word) before the error."""
+        self._host, self._rows, self._event, self._status, self._on_failure = host, rows, event, status, on_failure
 
     def result(self) -> List[int]:
         self._event.synchronize()
+        if self._status is not None and int(self._status[0]) != 0:
+            code = int(self._status[0])
+            self._status[0] = 0
+            if self._on_failure is not None:
+                self._on_failure()
+            raise kernels.KernelError(f"a kernel gave up a bounded wait (status {code:#x}): the sampled tokens are not valid")
         return self._host[:self._rows].tolist()
 
 
@@ -43,6 +52,7 @@ class DeviceSampler:
         if rows > self._rows:
             self._rows = max(rows, 2 * self._rows, 8, self._ids.numel())
             self._host_ids = [torch.empty(self._rows, dtype=torch.int32).pin_memory() for _ in range(_RING)]
+            self._host_status = [torch.zeros(1, dtype=torch.int32).pin_memory() for _ in range(_RING)]
             self._host = [torch.empty((4, self._rows), dtype=torch.float32).pin_memory() for _ in range(_RING)]
             self._dev = torch.empty((4, self._rows), dtype=torch.float32, device=self.device)
             self._top_k = torch.empty(self._rows, dtype=torch.int32, device=self.device)
@@ -77,10 +87,13 @@ class DeviceSampler:
             kernels.sample(logits, self._probs, self._dev[0, :rows], top_k, self._dev[2, :rows], self._dev[3, :rows], ids)
         host_ids = self._host_ids[slot]
         host_ids[:rows].copy_(ids, non_blocking=True)
+        word = kernels.status_word(self.device)
+        status = self._host_status[slot]
+        status.copy_(word, non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         self._events[slot] = event
-        return PendingSample(host_ids, rows, event)
+        return PendingSample(host_ids, rows, event, status, word.zero_)
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], uniforms: Sequence[float]) -> List[int]:
         if logits.shape[0] == 0:

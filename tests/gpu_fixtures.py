@@ -16,15 +16,29 @@ TOL_F32 = 2e-5
 # computations that round in a slightly different order (the running maximum of an online softmax
 # over tiles of keys, the order of a sum) differ by a fraction of the model's own bfloat16 noise,
 # which depends on how much the weights amplify it and on how many tiles a sequence has. The
-# tolerance is therefore tied to that noise, measured per model with the measure the comparison
+# bound is therefore tied to that noise, measured per model with the measure the comparison
 # itself uses (per position, max|a-b| / max(1, max|b|), worst position of all requests) as the
-# distance between the rounding and the exact plain implementation: an engine must stay within
-# three quarters of it. Measured on B200: 0.22 to 0.57 of it, the largest share on the model with
-# the longest requests (512 tokens, 8 key tiles), with the mma.sync and the tcgen05 prefill kernel
-# alike; against the exact plain implementation the engine is as close as the rounding one is.
-# A wrong key, position or page in the sharp models moves logits by about their own size, an order
-# of magnitude more than this.
-BF16_NOISE_SHARE = 0.75
+# distance between the rounding and the exact plain implementation. Two conditions, both set from
+# what the engine shows on B200 (worst position 0.22 to 0.57 of the noise, the median position
+# below a tenth of it): no position beyond MAX_SHARE of the noise, and the median position of a
+# comparison within MEDIAN_SHARE of it. A wrong key, position or page in the sharp models moves
+# logits by about their own size, an order of magnitude more than the noise; a slightly wrong
+# scale or a lost low-order contribution shifts the median before it shows at the worst place.
+BF16_MAX_SHARE = 0.65
+BF16_MEDIAN_SHARE = 0.25
+
+
+class Bound:
+    """What a comparison with the plain implementation must keep: every position below ``worst``,
+    the median position below ``median`` (None: not checked). ``noise`` is the model's own
+    bfloat16 noise, for the message (0 in 32-bit)."""
+
+    def __init__(self, worst: float, median=None, noise: float = 0.0):
+        self.worst, self.median, self.noise = worst, median, noise
+
+    def __float__(self) -> float:
+        return self.worst
+
 
 _TMP = tempfile.TemporaryDirectory(prefix="geneinfer_tests_")
 
@@ -71,8 +85,11 @@ def bf16_noise(case: str) -> float:
     return float(max(rows.max() for rows in per_row))
 
 
-def tolerance(dtype: str, case: str) -> float:
-    return TOL_F32 if dtype == "float32" else BF16_NOISE_SHARE * bf16_noise(case)
+def tolerance(dtype: str, case: str) -> Bound:
+    if dtype == "float32":
+        return Bound(TOL_F32)
+    noise = bf16_noise(case)
+    return Bound(BF16_MAX_SHARE * noise, BF16_MEDIAN_SHARE * noise, noise)
 
 
 def make_engine(case: str, dtype: str, n_pages: int, max_requests: int = 4, page_size: int = 16,

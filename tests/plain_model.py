@@ -178,14 +178,18 @@ def plain_layer(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, cfg: d
     return x + h @ w[prefix + "mlp.down_proj.weight"].T
 
 
-def plain_forward(w: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int], rnd=no_rounding) -> torch.Tensor:
-    """Logits [T, vocab] at every position of one whole sequence (final norm and head:
-    src/model/transformer.cpp:453-474; the head is the embedding table when tied)."""
+def plain_forward(w: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int], rnd=no_rounding,
+                  positions: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Logits [T, vocab] at every position of one whole sequence, or only at ``positions`` (in
+    their order) when given (final norm and head: src/model/transformer.cpp:453-474; the head is
+    the embedding table when tied)."""
     T = len(tokens)
     cos, sin = plain_rope_table(range(T), cfg["head_dim"], cfg["theta"], cfg["scaling"])
     x = plain_embedding(w["model.embed_tokens.weight"], tokens)
     for l in range(cfg["layers"]):
         x = plain_layer(x, w, f"model.layers.{l}.", cfg, cos, sin, rnd)
+    if positions is not None:
+        x = x[torch.tensor(list(positions), dtype=torch.long)]
     xn = rnd(plain_rmsnorm(x, w["model.norm.weight"], cfg["eps"]))
     head = w["model.embed_tokens.weight"] if cfg["tied"] else w["lm_head.weight"]
     return xn @ head.to(F32).T

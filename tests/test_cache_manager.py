@@ -182,3 +182,31 @@ def test_copy_on_write_of_a_shared_page():
     assert [(c.src, c.dst) for c in copies] == [(shared[1], int(a.tables[0][1]))] and a.tables[0][1] != shared[1]
     assert a.tables[0][0] == shared[0] and pool.ref_count(shared[1]) == 1 and pool.ref_count(shared[0]) == 2
     m.check_invariants()
+
+
+def test_fork_shares_pages_until_one_side_writes():
+    m = CacheManager({0: CacheNeed(1, 16)}, 4, 8, 64, 4)
+    a = m.open("a")
+    m.reserve(a, 10)
+    m.advance(a, 10)                                      # pages 0, 1 full, page 2 half full
+    pool = m.groups[0].pool
+    b = m.fork(a, "b", 6)                                 # into the middle of a's second page
+    assert b.length == 6 and b.n_pages[0] == 2 and list(b.tables[0][:2]) == list(a.tables[0][:2])
+    assert pool.ref_count(int(a.tables[0][0])) == 2 and pool.ref_count(int(a.tables[0][2])) == 1
+    copies = m.reserve(b, 3)                              # positions 6..8: page 1 is copied, page 2 is b's own
+    assert [(c.src, c.dst) for c in copies] == [(int(a.tables[0][1]), int(b.tables[0][1]))]
+    assert b.tables[0][1] != a.tables[0][1] and b.tables[0][0] == a.tables[0][0] and b.n_pages[0] == 3
+    m.advance(b, 3)
+    assert m.reserve(a, 1) == []                          # a's last page was never shared
+    m.advance(a, 1)
+    c = m.fork(a, "c")                                    # everything, the half-full last page included
+    assert c.length == 11 and m.pages_needed(a, 1) == 1 and m.pages_needed(c, 1) == 1
+    first = m.reserve(a, 1)
+    assert len(first) == 1 and m.reserve(c, 1) == [], "once one side has its own copy the other owns the original"
+    m.check_invariants()
+    with pytest.raises(ValueError):
+        m.fork(a, "d", 99)
+    for rc in (a, b, c):
+        m.close(rc)
+    assert pool.free_count == 8
+    m.check_invariants()

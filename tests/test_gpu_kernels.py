@@ -587,9 +587,10 @@ def test_gemm_rope_store_fused(T, H, Hkv, hd, ps, D, rotated, monkeypatch):
         err = (got - want).abs().max().item()
         assert err <= 2.0 ** -7 * want.abs().max().item(), f"{what}: differs from the two-kernel path by {err}"   # one bfloat16 step
         assert (got != want).float().mean().item() < 0.02, f"{what}: too many values round differently"
-    # no write without write_kv
+    # no write without write_kv, and the same queries
     kc3, vc3 = _paged("bfloat16", n_pages, Hkv, ps, hd)
-    K().gemm_rope_store(a, w, positions, row_req, tables, cos, sin, False, q, kc3, vc3, H, Hkv, hd, ps, write_kv=False,
+    q3 = torch.full_like(q, float("nan"))
+    K().gemm_rope_store(a, w, positions, row_req, tables, cos, sin, False, q3, kc3, vc3, H, Hkv, hd, ps, write_kv=False,
                         w_tiles=w_tiles)
     assert torch.isnan(kc3.float()).all() and torch.isnan(vc3.float()).all()
-    assert torch.equal(torch.nan_to_num(q.float()), torch.nan_to_num(q.float())) and not torch.isnan(q.float()).any()
+    assert not torch.isnan(q3.float()).any() and torch.equal(q3, q), "queries must not depend on write_kv"

@@ -201,3 +201,23 @@ def test_submit_refuses_bad_requests():
     with pytest.raises(ValueError):
         SamplingParams(top_k=-1)
     assert s.step() is False
+
+
+def test_sampled_ids_are_refused_when_a_kernel_reported_a_failed_wait():
+    """The kernels' status word travels to the host with the sampled ids: a value other than 0 (a
+    bounded wait that gave up, so a tile of garbage) must end the call instead of returning tokens."""
+    import torch
+    from geneinfer_b200.ops.library import KernelError
+    from geneinfer_b200.sampling.device import PendingSample
+
+    class Done:
+        def synchronize(self):
+            pass
+
+    ids = torch.tensor([4, 9, 2], dtype=torch.int32)
+    assert PendingSample(ids, 2, Done(), torch.zeros(1, dtype=torch.int32)).result() == [4, 9]
+    cleared = []
+    status = torch.tensor([0x21], dtype=torch.int32)
+    with pytest.raises(KernelError, match="0x21"):
+        PendingSample(ids, 3, Done(), status, lambda: cleared.append(True)).result()
+    assert cleared == [True] and int(status[0]) == 0

@@ -72,6 +72,18 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point():
     assert torch.cuda.memory_allocated() - before < 4096
 
 
+def test_a_greedy_row_among_sampled_rows_keeps_the_callers_value():
+    """Rows with temperature <= 0 are skipped by the kernel (the header says so): the id that the
+    caller wrote there before the call (its argmax) is still there afterwards."""
+    c = _case(6, 3000, seed=4, top_k=0, top_p=1.0)
+    c["temperature"][2] = 0.0
+    want = _ordinary(c)                              # the ordinary entry point leaves its -1 in row 2 as well
+    assert want[2] == -1
+    rc, got = _no_alloc(c)
+    assert rc == 0 and got == want
+    assert got[2] == -1 and all(0 <= t < 3000 for i, t in enumerate(got) if i != 2)
+
+
 def test_sizes_beyond_the_work_area_are_refused_with_a_clear_error():
     from geneinfer_b200.ops import lib
     rows, vocab = 17, 128256                         # 17 x 128256 > 2 Mi floats; nothing is launched
