@@ -277,12 +277,12 @@ def run_ours(args):
     clocks = ClockSampler()
     clocks.start()
     ms_step, launches = time_decode_device(llm.steps, batch, CONTEXT, args.steps, args.warmup, vocab)
-    clock_record = clocks.stop()
     ms_e2e, h2d, d2h = time_decode_e2e(llm, batch, CONTEXT, args.steps, args.warmup, vocab)
     ms_prefill = time_prefill(llm.steps, PREFILL_TOKENS, max(1, args.warmup), vocab)
     ms_prefill_4 = time_prefill(llm.steps, PREFILL_TOKENS, 1, vocab, portions=4)
     ms_short, _ = time_decode_device(llm.steps, batch, 128, args.steps, args.warmup, vocab)
     short = {f"short_requests_b{batch}": time_short_requests(llm, batch, vocab)}
+    clock_record = clocks.stop()          # sampled through the timed regions above, which follow one another under load
     flops = prefill_flops(cfg, PREFILL_TOKENS)
 
     def roofline(b, context, ms):

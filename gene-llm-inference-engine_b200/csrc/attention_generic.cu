@@ -147,7 +147,7 @@ using namespace gi;
 // 1 when the general kernel serves this head size: the model is refused when it is built, not at its first step.
 extern "C" int gi_attention_generic_supported(int hd) { return hd % 16 == 0 && hd >= 16 && hd <= kMaxHeadDim; }
 
-extern "C" int gi_attention_generic(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
+static int gi_attention_generic_impl(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
                                     const int* row_req, const int* positions, const int* block_tables,
                                     int table_stride, int T, int H, int Hkv, int hd, int page_size, float scale,
                                     int window, void* stream) {
@@ -173,4 +173,10 @@ extern "C" int gi_attention_generic(const void* q, const void* k_cache, const vo
         GI_REQUIRE(false, "attention: unsupported dtype code %d", dtype);
     }
     return check_launch("attention_generic");
+}
+
+// The exported names: each runs its implementation above and, while a launch program is recorded, leaves a copy of
+// its arguments in the program (common.cuh).
+extern "C" int gi_attention_generic(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype, const int* row_req, const int* positions, const int* block_tables, int table_stride, int T, int H, int Hkv, int hd, int page_size, float scale, int window, void* stream) {
+    return gi::dispatch(gi_attention_generic_impl, q, k_cache, v_cache, out, dtype, row_req, positions, block_tables, table_stride, T, H, Hkv, hd, page_size, scale, window, stream);
 }

@@ -1096,7 +1096,7 @@ extern "C" int gi_attention_chunk_keys() { return kChunkKeys; }
 // Single decoded tokens: rows[i] is the step row of the i-th one. part_o holds
 // n_rows * H * max_chunks * hd floats and part_ml n_rows * H * max_chunks * 2; n_chunks covers the
 // longest context among the rows.
-extern "C" int gi_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* rows,
+static int gi_attention_decode_impl(const void* q, const void* k_cache, const void* v_cache, void* out, const int* rows,
                                    int n_rows, const int* row_req, const int* positions, const int* block_tables,
                                    int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window,
                                    float* part_o, float* part_ml, int max_chunks, int n_chunks, long long n_pages,
@@ -1134,7 +1134,7 @@ extern "C" int gi_attention_decode(const void* q, const void* k_cache, const voi
 }
 
 // Prompt portions: work[3*i..] = (first step row of the tile, tokens in the tile, request index).
-extern "C" int gi_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work,
+static int gi_attention_prefill_impl(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work,
                                     int n_work, const int* positions, const int* block_tables, int table_stride, int H,
                                     int Hkv, int hd, int page_size, float scale, int window, long long n_pages,
                                     void* status, void* stream) {
@@ -1162,4 +1162,14 @@ extern "C" int gi_attention_prefill(const void* q, const void* k_cache, const vo
         default: GI_PREFILL(128);
     }
 #undef GI_PREFILL
+}
+
+// The exported names: each runs its implementation above and, while a launch program is recorded, leaves a copy of
+// its arguments in the program (common.cuh).
+extern "C" int gi_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* rows, int n_rows, const int* row_req, const int* positions, const int* block_tables, int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window, float* part_o, float* part_ml, int max_chunks, int n_chunks, long long n_pages, void* status, void* stream) {
+    return gi::dispatch(gi_attention_decode_impl, q, k_cache, v_cache, out, rows, n_rows, row_req, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale, window, part_o, part_ml, max_chunks, n_chunks, n_pages, status, stream);
+}
+
+extern "C" int gi_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work, int n_work, const int* positions, const int* block_tables, int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window, long long n_pages, void* status, void* stream) {
+    return gi::dispatch(gi_attention_prefill_impl, q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale, window, n_pages, status, stream);
 }

@@ -532,7 +532,7 @@ extern "C" int gi_attention_prefill_tc_supported(int hd, int H, int Hkv, int pag
 
 // Prompt portions: work[3*i..] = (first step row of the tile, tokens in the tile (at most
 // 128 / group size), request index).
-extern "C" int gi_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work,
+static int gi_attention_prefill_tc_impl(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work,
                                        int n_work, const int* positions, const int* block_tables, int table_stride, int H,
                                        int Hkv, int hd, int page_size, float scale, int window, long long n_pages,
                                        void* status, void* stream) {
@@ -548,3 +548,8 @@ extern "C" int gi_attention_prefill_tc(const void* q, const void* k_cache, const
                             page_size, scale, window, n_pages, static_cast<int*>(status), st);
 }
 
+// The exported names: each runs its implementation above and, while a launch program is recorded, leaves a copy of
+// its arguments in the program (common.cuh).
+extern "C" int gi_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work, int n_work, const int* positions, const int* block_tables, int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window, long long n_pages, void* status, void* stream) {
+    return gi::dispatch(gi_attention_prefill_tc_impl, q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale, window, n_pages, status, stream);
+}

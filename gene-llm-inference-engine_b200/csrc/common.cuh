@@ -10,6 +10,9 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <functional>
+#include <tuple>
+#include <vector>
 
 namespace gi {
 
@@ -67,6 +70,30 @@ inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);      // errors surface in check_launch
+}
+
+// Launch programs. While a program is being recorded on the calling thread (gi_program_begin ..
+// gi_program_end), every entry point that launches kernels runs as usual and also leaves a copy of its
+// arguments in the program. gi_program_run() then repeats the whole sequence on a stream with one
+// call: the host cost of a step's launches (argument checks, bindings) is paid once per shape.
+// A program holds raw pointers and sizes: it is valid while the buffers it names are.
+struct Program {
+    std::vector<std::function<int(void*)>> calls;
+};
+extern thread_local Program* tl_recording;
+
+// Runs impl(args...) and, while a program is recorded, stores a copy that takes the stream (the last
+// argument of every launching entry point) from the later run.
+template <typename... A>
+inline int dispatch(int (*impl)(A...), A... args) {
+    if (tl_recording != nullptr) {
+        std::tuple<A...> tup(args...);
+        tl_recording->calls.emplace_back([impl, tup](void* stream) mutable {
+            std::get<sizeof...(A) - 1>(tup) = stream;
+            return std::apply(impl, tup);
+        });
+    }
+    return impl(args...);
 }
 
 }  // namespace gi

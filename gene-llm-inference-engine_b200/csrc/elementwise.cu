@@ -270,7 +270,7 @@ int gi_set_pdl(int enabled) {
 
 // tokens[t] >= 0 is a token id; tokens[t] = -(k + 1) takes the id from feedback[k] (device memory
 // that an earlier sampling kernel wrote; may be null when no entry is negative).
-int gi_embed(const void* table, int table_dtype, const int* tokens, const int* feedback, float* out, int T, int D,
+static int gi_embed_impl(const void* table, int table_dtype, const int* tokens, const int* feedback, float* out, int T, int D,
              float scale, void* stream) {
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && D > 0, "embed: T and D must be positive (T=%d, D=%d)", T, D);
@@ -285,7 +285,7 @@ int gi_embed(const void* table, int table_dtype, const int* tokens, const int* f
     return check_launch("embed");
 }
 
-int gi_rmsnorm(const float* x, const int* rows, const float* weight, void* out, int out_dtype, int n_rows, int D,
+static int gi_rmsnorm_impl(const float* x, const int* rows, const float* weight, void* out, int out_dtype, int n_rows, int D,
                float eps, void* stream) {
     if (n_rows == 0) return 0;
     GI_REQUIRE(n_rows > 0 && D > 0, "rmsnorm: sizes must be positive (rows=%d, D=%d)", n_rows, D);
@@ -300,7 +300,7 @@ int gi_rmsnorm(const float* x, const int* rows, const float* weight, void* out, 
     return check_launch("rmsnorm");
 }
 
-int gi_swiglu(const float* gate_up, void* out, int out_dtype, int T, int I, void* stream) {
+static int gi_swiglu_impl(const float* gate_up, void* out, int out_dtype, int T, int I, void* stream) {
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && I > 0, "swiglu: sizes must be positive (T=%d, I=%d)", T, I);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -317,7 +317,7 @@ int gi_swiglu(const float* gate_up, void* out, int out_dtype, int T, int I, void
 }
 
 // dtype: the type of q_out and of the cache (both f32 on the 32-bit path, both bf16 otherwise).
-int gi_rope_store(const float* qkv, const int* positions, const int* row_req, const int* block_tables,
+static int gi_rope_store_impl(const float* qkv, const int* positions, const int* row_req, const int* block_tables,
                   int table_stride, const float* cos_t, const float* sin_t, int rot_half, int interleaved,
                   void* q_out, void* k_cache, void* v_cache, int dtype, int T, int H, int Hkv, int hd,
                   int page_size, int write_kv, void* stream) {
@@ -344,7 +344,7 @@ int gi_rope_store(const float* qkv, const int* positions, const int* row_req, co
     return check_launch("rope_store");
 }
 
-int gi_copy_pages(void* base, long long array_stride_bytes, int n_arrays, long long page_bytes, const int* src,
+static int gi_copy_pages_impl(void* base, long long array_stride_bytes, int n_arrays, long long page_bytes, const int* src,
                   const int* dst, int n_copies, void* stream) {
     if (n_copies == 0 || n_arrays == 0) return 0;
     GI_REQUIRE(page_bytes % 16 == 0, "copy_pages: a page of %lld bytes is not a multiple of 16", page_bytes);
@@ -355,3 +355,25 @@ int gi_copy_pages(void* base, long long array_stride_bytes, int n_arrays, long l
 }
 
 }  // extern "C"
+
+// The exported names: each runs its implementation above and, while a launch program is recorded, leaves a copy of
+// its arguments in the program (common.cuh).
+extern "C" int gi_embed(const void* table, int table_dtype, const int* tokens, const int* feedback, float* out, int T, int D, float scale, void* stream) {
+    return gi::dispatch(gi_embed_impl, table, table_dtype, tokens, feedback, out, T, D, scale, stream);
+}
+
+extern "C" int gi_rmsnorm(const float* x, const int* rows, const float* weight, void* out, int out_dtype, int n_rows, int D, float eps, void* stream) {
+    return gi::dispatch(gi_rmsnorm_impl, x, rows, weight, out, out_dtype, n_rows, D, eps, stream);
+}
+
+extern "C" int gi_swiglu(const float* gate_up, void* out, int out_dtype, int T, int I, void* stream) {
+    return gi::dispatch(gi_swiglu_impl, gate_up, out, out_dtype, T, I, stream);
+}
+
+extern "C" int gi_rope_store(const float* qkv, const int* positions, const int* row_req, const int* block_tables, int table_stride, const float* cos_t, const float* sin_t, int rot_half, int interleaved, void* q_out, void* k_cache, void* v_cache, int dtype, int T, int H, int Hkv, int hd, int page_size, int write_kv, void* stream) {
+    return gi::dispatch(gi_rope_store_impl, qkv, positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved, q_out, k_cache, v_cache, dtype, T, H, Hkv, hd, page_size, write_kv, stream);
+}
+
+extern "C" int gi_copy_pages(void* base, long long array_stride_bytes, int n_arrays, long long page_bytes, const int* src, const int* dst, int n_copies, void* stream) {
+    return gi::dispatch(gi_copy_pages_impl, base, array_stride_bytes, n_arrays, page_bytes, src, dst, n_copies, stream);
+}

@@ -90,7 +90,7 @@ int launch_simt(const void* A, const void* W, void* C, int c_dtype, int accumula
 using namespace gi;
 
 // C[M,N] (+)= A[M,K] * W[N,K]^T; row strides lda, ldw, ldc in elements.
-extern "C" int gi_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype,
+static int gi_gemm_simt_impl(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype,
                             int accumulate, int M, int N, int K, int lda, int ldw, int ldc, void* stream) {
     if (M == 0 || N == 0) return 0;
     GI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: sizes must be positive (M=%d, N=%d, K=%d)", M, N, K);
@@ -101,4 +101,10 @@ extern "C" int gi_gemm_simt(const void* A, int a_dtype, const void* W, int w_dty
     if (a_dtype == kF32 && w_dtype == kBF16) return launch_simt<float, __nv_bfloat16>(A, W, C, c_dtype, accumulate, M, N, K, lda, ldw, ldc, st);
     if (a_dtype == kBF16 && w_dtype == kBF16) return launch_simt<__nv_bfloat16, __nv_bfloat16>(A, W, C, c_dtype, accumulate, M, N, K, lda, ldw, ldc, st);
     GI_REQUIRE(false, "gemm: unsupported operand dtype codes (A=%d, W=%d)", a_dtype, w_dtype);
+}
+
+// The exported names: each runs its implementation above and, while a launch program is recorded, leaves a copy of
+// its arguments in the program (common.cuh).
+extern "C" int gi_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype, int accumulate, int M, int N, int K, int lda, int ldw, int ldc, void* stream) {
+    return gi::dispatch(gi_gemm_simt_impl, A, a_dtype, W, w_dtype, C, c_dtype, accumulate, M, N, K, lda, ldw, ldc, stream);
 }

@@ -1223,7 +1223,7 @@ static int run_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int a
     }
 }
 
-extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int accumulate, int M, int N, int K,
+static int gi_gemm_tc_impl(const void* A, const void* W, void* C, int c_dtype, int accumulate, int M, int N, int K,
                           long long lda, long long ldw, long long ldc, int swap, int block_q, int splits,
                           void* workspace, long long workspace_floats, void* counters, int n_counters, void* status,
                           const void* w_tiles, void* stream) {
@@ -1234,7 +1234,7 @@ extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
 // The [q; k; v] product of few tokens (at most block_q <= 128, weights on the 128-row side) with rotation
 // and page store done by the CTA that holds a tile's sum (RopeStoreParams). The head size must divide 128
 // so that both members of a rotated pair lie in one tile; any rotary size and pairing.
-extern "C" int gi_gemm_tc_rope(const void* A, const void* W, int M, int K, long long lda, long long ldw, int block_q,
+static int gi_gemm_tc_rope_impl(const void* A, const void* W, int M, int K, long long lda, long long ldw, int block_q,
                                int splits, void* workspace, long long workspace_floats, void* counters, int n_counters,
                                void* status, const void* w_tiles, const int* positions, const int* row_req,
                                const int* block_tables, int table_stride, const float* cos_t, const float* sin_t,
@@ -1287,7 +1287,7 @@ __global__ void reduce_splits_kernel(const float* __restrict__ ws, float* __rest
 // splits > 1 (epilogues 0 and 1, N a multiple of 4, at most 8): K is cut into ranges whose tiles are work
 // items of their own; their results go to `workspace` (splits x ceil(M / 128) x 128 x N floats) and a
 // second kernel adds them up in order into C. Few output tiles (a few hundred tokens) then still fill the GPU.
-extern "C" int gi_gemm_tc_persistent(const void* A, const void* W, void* C, int epilogue, int M, int N, int K,
+static int gi_gemm_tc_persistent_impl(const void* A, const void* W, void* C, int epilogue, int M, int N, int K,
                                      long long lda, long long ldw, long long ldc, int block_q, void* status,
                                      int splits, void* workspace, long long workspace_floats, void* stream) {
     if (M == 0 || N == 0) return 0;
@@ -1352,7 +1352,7 @@ extern "C" int gi_gemm_tc_persistent(const void* A, const void* W, void* C, int 
 // The [q; k; v] product of many tokens with rotation and page store in its epilogue (RopeStoreParams):
 // A [M, K] bfloat16 activations, W [(H + 2 Hkv) * hd, K]; nothing else is written. Head sizes 32, 64, 128
 // with the whole head rotated (rot_half = hd / 2) in the half-split pairing, or no rotation at all.
-extern "C" int gi_gemm_tc_persistent_rope(const void* A, const void* W, int M, int K, long long lda, long long ldw,
+static int gi_gemm_tc_persistent_rope_impl(const void* A, const void* W, int M, int K, long long lda, long long ldw,
                                           const int* positions, const int* row_req, const int* block_tables,
                                           int table_stride, const float* cos_t, const float* sin_t, int rot_half,
                                           int interleaved, void* q_out, void* k_cache, void* v_cache, int H, int Hkv,
@@ -1395,4 +1395,22 @@ extern "C" int gi_gemm_tc_persistent_rope(const void* A, const void* W, int M, i
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (block_q == 192) return launch_persistent<192, kEpiRopeStore>(mp, mq, mp /* no TMA store */, p, st);
     return launch_persistent<256, kEpiRopeStore>(mp, mq, mp /* no TMA store */, p, st);
+}
+
+// The exported names: each runs its implementation above and, while a launch program is recorded, leaves a copy of
+// its arguments in the program (common.cuh).
+extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int accumulate, int M, int N, int K, long long lda, long long ldw, long long ldc, int swap, int block_q, int splits, void* workspace, long long workspace_floats, void* counters, int n_counters, void* status, const void* w_tiles, void* stream) {
+    return gi::dispatch(gi_gemm_tc_impl, A, W, C, c_dtype, accumulate, M, N, K, lda, ldw, ldc, swap, block_q, splits, workspace, workspace_floats, counters, n_counters, status, w_tiles, stream);
+}
+
+extern "C" int gi_gemm_tc_rope(const void* A, const void* W, int M, int K, long long lda, long long ldw, int block_q, int splits, void* workspace, long long workspace_floats, void* counters, int n_counters, void* status, const void* w_tiles, const int* positions, const int* row_req, const int* block_tables, int table_stride, const float* cos_t, const float* sin_t, int rot_half, int interleaved, void* q_out, void* k_cache, void* v_cache, int H, int Hkv, int hd, int page_size, int write_kv, void* stream) {
+    return gi::dispatch(gi_gemm_tc_rope_impl, A, W, M, K, lda, ldw, block_q, splits, workspace, workspace_floats, counters, n_counters, status, w_tiles, positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved, q_out, k_cache, v_cache, H, Hkv, hd, page_size, write_kv, stream);
+}
+
+extern "C" int gi_gemm_tc_persistent(const void* A, const void* W, void* C, int epilogue, int M, int N, int K, long long lda, long long ldw, long long ldc, int block_q, void* status, int splits, void* workspace, long long workspace_floats, void* stream) {
+    return gi::dispatch(gi_gemm_tc_persistent_impl, A, W, C, epilogue, M, N, K, lda, ldw, ldc, block_q, status, splits, workspace, workspace_floats, stream);
+}
+
+extern "C" int gi_gemm_tc_persistent_rope(const void* A, const void* W, int M, int K, long long lda, long long ldw, const int* positions, const int* row_req, const int* block_tables, int table_stride, const float* cos_t, const float* sin_t, int rot_half, int interleaved, void* q_out, void* k_cache, void* v_cache, int H, int Hkv, int hd, int page_size, int write_kv, void* status, void* stream) {
+    return gi::dispatch(gi_gemm_tc_persistent_rope_impl, A, W, M, K, lda, ldw, positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved, q_out, k_cache, v_cache, H, Hkv, hd, page_size, write_kv, status, stream);
 }

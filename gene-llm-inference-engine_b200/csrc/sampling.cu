@@ -358,7 +358,7 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ probs_all, i
 using namespace gi;
 
 // part_val / part_idx: caller's scratch of rows * 32 floats / ints.
-extern "C" int gi_argmax(const float* logits, int rows, int V, int* out, float* part_val, int* part_idx, void* stream) {
+static int gi_argmax_impl(const float* logits, int rows, int V, int* out, float* part_val, int* part_idx, void* stream) {
     if (rows == 0) return 0;
     GI_REQUIRE(rows > 0 && V > 0, "argmax: sizes must be positive (rows=%d, V=%d)", rows, V);
     GI_REQUIRE(rows <= 65535, "argmax: %d rows exceed the grid limit", rows);
@@ -372,7 +372,7 @@ extern "C" int gi_argmax(const float* logits, int rows, int V, int* out, float* 
 
 // probs_scratch: [rows, V] floats owned by the caller. Rows with temperature[r] <= 0 are skipped:
 // out[r] is left as it is (the caller writes the row's argmax there first).
-extern "C" int gi_sample(const float* logits, float* probs_scratch, int rows, int V, const float* temperature,
+static int gi_sample_impl(const float* logits, float* probs_scratch, int rows, int V, const float* temperature,
                          const int* top_k, const float* top_p, const float* uniform, int* out, void* stream) {
     if (rows == 0) return 0;
     GI_REQUIRE(rows > 0 && V > 0, "sample: sizes must be positive (rows=%d, V=%d)", rows, V);
@@ -441,4 +441,14 @@ extern "C" int gi_sample_no_alloc(const float* logits, int rows, int vocab, cons
     launch_kernel((sample_kernel), dim3(rows), dim3(kSampleThreads), 0, static_cast<cudaStream_t>(stream), 
         logits, work, vocab, temperature, top_k, top_p, uniform, out);
     return check_launch("sample_no_alloc");
+}
+
+// The exported names: each runs its implementation above and, while a launch program is recorded, leaves a copy of
+// its arguments in the program (common.cuh).
+extern "C" int gi_argmax(const float* logits, int rows, int V, int* out, float* part_val, int* part_idx, void* stream) {
+    return gi::dispatch(gi_argmax_impl, logits, rows, V, out, part_val, part_idx, stream);
+}
+
+extern "C" int gi_sample(const float* logits, float* probs_scratch, int rows, int V, const float* temperature, const int* top_k, const float* top_p, const float* uniform, int* out, void* stream) {
+    return gi::dispatch(gi_sample_impl, logits, probs_scratch, rows, V, temperature, top_k, top_p, uniform, out, stream);
 }

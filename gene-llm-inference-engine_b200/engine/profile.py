@@ -55,12 +55,12 @@ def profile_report(engine, prompt) -> str:
 
     steps = engine.steps
     n = max(1, min(len(prompt), steps.model.max_position) - 1)
-    graphs = steps.use_graphs
+    graphs, programs = steps.use_graphs, steps.use_programs
     steps.open("profile")
     try:
         if n > 1 or len(prompt) > 1:
             steps.step([StepEntry("profile", list(prompt[:n]), [])])
-        steps.use_graphs = False
+        steps.use_graphs = steps.use_programs = False      # every launch goes through its (timed) wrapper
         for name in OPERATIONS:
             setattr(kernels, name, timed(name, saved[name]))
         logits = steps.step([StepEntry("profile", [int(prompt[min(n, len(prompt) - 1)])], [0])])
@@ -69,7 +69,7 @@ def profile_report(engine, prompt) -> str:
     finally:
         for name in OPERATIONS:
             setattr(kernels, name, saved[name])
-        steps.use_graphs = graphs
+        steps.use_graphs, steps.use_programs = graphs, programs
         steps.close("profile")
     per = {label: (len(v), sum(s.elapsed_time(e) for s, e, _ in v), sum(b for _, _, b in v)) for label, v in records.items()}
     total = sum(ms for _, ms, _ in per.values()) or 1e-9

@@ -93,6 +93,27 @@ class StepContext:
     def scratch(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype, capacity: Optional[int] = None) -> torch.Tensor:
         return self._engine.scratch(name, shape, dtype, capacity)
 
+    def recorded(self, owner, key: Tuple, launch) -> None:
+        """Runs ``launch()``, a part's kernel calls for this step, through a launch program: the
+        first step with this ``key`` runs it as it is and records its launches, later steps repeat the
+        recording with one call into the library. ``key`` must name everything the calls depend on
+        besides the contents of device buffers: the token count, how the rows split between kernels,
+        whose cache is used. Addresses are covered by the engine: its buffers keep their places, and
+        when one has to be replaced every recording is dropped."""
+        eng = self._engine
+        if not eng.use_programs or eng.tap is not None:
+            launch()
+            return
+        full = (id(owner), key)
+        program = eng._programs.get(full)
+        if program is None:
+            with kernels.record() as rec:
+                launch()
+            eng._programs[full] = rec.program
+        else:
+            program.run()
+            eng.program_runs += 1
+
     def tap(self, tag: str, layer: int, tensor: torch.Tensor) -> None:
         """Shows an intermediate activation to whoever listens (``StepEngine.tap``); the tags follow
         the reference's trace callback (src/model/model.h:16-22): "embedding", "attn_out" and
@@ -175,6 +196,10 @@ class StepEngine:
             for layer in model.layers)
         self._graphs: Dict[Tuple, Tuple] = {}
         self.graph_replays = 0
+        # launch programs of the parts, by (part, shape key): see StepContext.recorded
+        self.use_programs = True
+        self._programs: Dict[Tuple, object] = {}
+        self.program_runs = 0
         # a listener for intermediate activations: tap(tag, layer, tensor, ctx); steps run outside graphs while it is set
         self.tap = None
         # the kernels' status word (a bounded wait that gave up) follows every step to pinned memory
@@ -209,6 +234,7 @@ class StepEngine:
     def _drop_captures(self) -> None:
         """Forgets everything that holds addresses of scratch memory (called before a buffer is replaced)."""
         self._graphs.clear()
+        self._programs.clear()
         self.scratch_generation += 1
 
     def _init_descriptor(self) -> None:
@@ -233,30 +259,44 @@ class StepEngine:
         self._ring_np = [b.numpy() for b in self._ring]
         self._ring_events: List[Optional[torch.cuda.Event]] = [None] * 4
         self._ring_next = 0
-        cap = 4 * (T + R)
-        self._aux_host = [torch.zeros(cap, dtype=torch.int32).pin_memory() for _ in range(8)]
-        self._aux_dev = [torch.zeros(cap, dtype=torch.int32, device=self.device) for _ in range(8)]
-        self._aux_events: List[Optional[torch.cuda.Event]] = [None] * 8
-        self._aux_next = 0
+        # small integer lists that parts derive from a step (work lists of the attention kernels): the k-th
+        # list of a step always lands in the same device buffer, through a ring of pinned staging buffers
+        self._aux_cap = 4 * (T + R)
+        self._aux_dev: List[torch.Tensor] = []
+        self._aux_host: List[List[torch.Tensor]] = []
+        self._aux_events: List[List[Optional[torch.cuda.Event]]] = []
+        self._aux_turn: List[int] = []
+        self._aux_calls = 0
 
     def upload_ints(self, values) -> torch.Tensor:
-        """Small integer lists that a part derives from the step (work lists): one pinned staging
-        buffer per call slot, copied asynchronously; the device view is valid until the next step."""
+        """Small integer lists that a part derives from the step (work lists): copied asynchronously
+        from pinned memory; the device view is valid until the next step. The k-th call of every step
+        returns the same device address (copies and kernels are ordered on the stream), which lets
+        recorded launches and captured graphs name it."""
         n = len(values)
-        slot = self._aux_next
-        self._aux_next = (slot + 1) % len(self._aux_host)
-        if self._aux_events[slot] is not None:
-            self._aux_events[slot].synchronize()
-        if n > self._aux_host[slot].numel():
-            self._aux_host[slot] = torch.zeros(2 * n, dtype=torch.int32).pin_memory()
-            self._aux_dev[slot] = torch.zeros(2 * n, dtype=torch.int32, device=self.device)
-        host, dev = self._aux_host[slot], self._aux_dev[slot]
+        k = self._aux_calls
+        self._aux_calls += 1
+        if k == len(self._aux_dev):
+            self._aux_dev.append(torch.zeros(self._aux_cap, dtype=torch.int32, device=self.device))
+            self._aux_host.append([torch.zeros(self._aux_cap, dtype=torch.int32).pin_memory() for _ in range(4)])
+            self._aux_events.append([None] * 4)
+            self._aux_turn.append(0)
+        if n > self._aux_dev[k].numel():
+            self._drop_captures()                  # the list's place changes
+            self._aux_dev[k] = torch.zeros(2 * n, dtype=torch.int32, device=self.device)
+            self._aux_host[k] = [torch.zeros(2 * n, dtype=torch.int32).pin_memory() for _ in range(4)]
+            self._aux_events[k] = [None] * 4
+        turn = self._aux_turn[k]
+        self._aux_turn[k] = (turn + 1) % 4
+        if self._aux_events[k][turn] is not None:
+            self._aux_events[k][turn].synchronize()
+        host, dev = self._aux_host[k][turn], self._aux_dev[k]
         if n:
             host[:n] = torch.tensor(values, dtype=torch.int32)
             dev[:n].copy_(host[:n], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
-        self._aux_events[slot] = ev
+        self._aux_events[k][turn] = ev
         return dev[:n]
 
     # ------------------------------------------------------------------ requests
@@ -330,6 +370,7 @@ class StepEngine:
             self._copy_pages(copies)
 
         # ---- describe the step
+        self._aux_calls = 0
         slot = self._ring_next
         self._ring_next = (slot + 1) % len(self._ring)
         if self._ring_events[slot] is not None:

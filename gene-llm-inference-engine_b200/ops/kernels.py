@@ -63,6 +63,53 @@ def _stream() -> int:
     return _scoped_stream if _scoped_stream is not None else torch.cuda.current_stream().cuda_stream
 
 
+class Program:
+    """A recorded sequence of this library's launches (csrc/program.cu): ``run()`` repeats it on the
+    current stream with one call into the library. It holds raw addresses and sizes, so it is valid
+    only while every buffer it was recorded with is."""
+
+    def __init__(self, handle: int, launches: int):
+        self._handle = handle
+        self.launches = launches
+
+    def run(self) -> None:
+        global _launches
+        stream = _scoped_stream if _scoped_stream is not None else torch.cuda.current_stream().cuda_stream
+        check(lib().gi_program_run(self._handle, stream), "program")
+        _launches += self.launches
+
+    def __len__(self) -> int:
+        return int(lib().gi_program_size(self._handle))
+
+    def __del__(self):
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle:
+            try:
+                lib().gi_program_free(handle)
+            except Exception:       # interpreter shutdown
+                pass
+
+
+class record:
+    """``with record() as r: ...`` runs the block's kernel calls as usual and records them;
+    ``r.program`` repeats them afterwards. Recordings do not nest."""
+
+    program: Optional[Program] = None
+
+    def __enter__(self):
+        check(lib().gi_program_begin(), "program")
+        self._before = _launches
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        handle = lib().gi_program_end()
+        if exc_type is None:
+            self.program = Program(handle, _launches - self._before)
+        elif handle:
+            lib().gi_program_free(handle)
+        return False
+
+
 def _dev(t: torch.Tensor, name: str, dtype: Optional[torch.dtype] = None) -> int:
     if not t.is_cuda:
         raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")

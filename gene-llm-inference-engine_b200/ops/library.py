@@ -54,6 +54,10 @@ _SIGNATURES = {
     "gi_attention_fast_supported": [c_int, c_int, c_int],
     "gi_attention_generic_supported": [c_int],
     "gi_attention_chunk_keys": [],
+    "gi_program_begin": [],
+    "gi_program_size": [c_void_p],
+    "gi_program_run": [c_void_p, c_void_p],
+    "gi_program_free": [c_void_p],
     "gi_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "gi_sample": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
 }
@@ -66,6 +70,8 @@ def lib() -> ctypes.CDLL:
         loaded = ctypes.CDLL(path)
         loaded.gi_last_error.restype = c_char_p
         loaded.gi_last_error.argtypes = []
+        loaded.gi_program_end.restype = c_void_p
+        loaded.gi_program_end.argtypes = []
         for name, argtypes in _SIGNATURES.items():
             fn = getattr(loaded, name, None)
             if fn is None:

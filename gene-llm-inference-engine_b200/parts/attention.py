@@ -75,6 +75,16 @@ class AttentionMixer:
     def state_need(self):
         return None
 
+    def launch_key(self, ctx, run):
+        """What the mixer's launches depend on besides the token count: whose cache it uses, and (tensor-core
+        kernels) how many rows are single decoded tokens, how many tiles the prompt portions make and how many
+        chunks the longest context of a single token has. Asking also places this step's work lists on the device."""
+        if not self.fast:
+            return (run.cache_layer, run.writes_cache)
+        rows, work, longest = ctx.attention_work(self.prefill_rows(ctx.page_size) // (self.num_heads // self.num_kv_heads))
+        return (run.cache_layer, run.writes_cache, rows.numel(), work.shape[0],
+                (longest + self.chunk_keys - 1) // self.chunk_keys)
+
     def forward(self, ctx, run, xn: torch.Tensor, x: torch.Tensor) -> None:
         """``xn``: normalised input [T, hidden] in the compute dtype; ``x``: the 32-bit residual
         stream, to which the mixer's output is added. ``run`` names whose cache to use."""

@@ -22,9 +22,43 @@ class PreNormBlock:
 
     def forward(self, ctx, run, x: torch.Tensor) -> None:
         xn = ctx.scratch("normed", tuple(x.shape), self.dtype)
+        T = x.shape[0]
+        # each half of the layer is one launch program when its parts say what their launches depend on
+        # (``launch_key``); a part without that method (one that computes with other libraries) runs as it is
+        key = _launch_key(ctx, (self.mixer_norm, None), (self.mixer, run))
+        if key is not None:
+            ctx.recorded(self, ("mixer", run, T) + key, lambda: self._mixer_half(ctx, run, xn, x))
+        else:
+            self._mixer_half(ctx, run, xn, x)
+        ctx.tap("attn_out", run.layer, x)
+        key = _launch_key(ctx, (self.feed_forward_norm, None), (self.feed_forward, None))
+        if key is not None:
+            ctx.recorded(self, ("feed_forward", T) + key, lambda: self._feed_forward_half(ctx, xn, x))
+        else:
+            self._feed_forward_half(ctx, xn, x)
+        ctx.tap("ffn_out", run.layer, x)
+
+    def _mixer_half(self, ctx, run, xn, x) -> None:
         self.mixer_norm.forward(x, xn)
         self.mixer.forward(ctx, run, xn, x)
-        ctx.tap("attn_out", run.layer, x)
+
+    def _feed_forward_half(self, ctx, xn, x) -> None:
         self.feed_forward_norm.forward(x, xn)
         self.feed_forward.forward(ctx, xn, x)
-        ctx.tap("ffn_out", run.layer, x)
+
+
+def _launch_key(ctx, *parts):
+    """The joint key of some parts' launches for this step, or None when one of them has none (or the
+    context records nothing)."""
+    if not hasattr(ctx, "recorded"):
+        return None
+    key = ()
+    for part, run in parts:
+        fn = getattr(part, "launch_key", None)
+        if fn is None:
+            return None
+        k = fn(ctx) if run is None else fn(ctx, run)
+        if k is None:
+            return None
+        key += tuple(k)
+    return key

@@ -30,6 +30,10 @@ class SwiGLUFeedForward:
         self.w_down = Linear(weights["w_down"], build.compute_dtype, build.device, tiles=build.weight_tiles)
         self.dtype = build.compute_dtype
 
+    def launch_key(self, ctx):
+        """Its launches depend on the token count only (which the caller's key holds)."""
+        return ()
+
     def forward(self, ctx, xn: torch.Tensor, x: torch.Tensor) -> None:
         T = xn.shape[0]
         h = ctx.scratch("ffn_hidden", (T, self.intermediate_size), self.dtype)

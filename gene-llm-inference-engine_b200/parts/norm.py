@@ -23,6 +23,10 @@ class RMSNorm:
             raise ValueError(f"rmsnorm: weight has shape {tuple(w.shape)}, expected ({self.size},)")
         self.weight = w.to(device=build.device, dtype=torch.float32).contiguous()
 
+    def launch_key(self, ctx):
+        """Its one launch depends on the number of rows only (which the caller's key holds)."""
+        return ()
+
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         kernels.rmsnorm(x, self.weight, out, self.eps, rows)
         return out

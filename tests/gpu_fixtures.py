@@ -19,13 +19,14 @@ TOL_F32 = 2e-5
 # bound is therefore tied to that noise, measured per model with the measure the comparison
 # itself uses (per position, max|a-b| / max(1, max|b|), worst position of all requests) as the
 # distance between the rounding and the exact plain implementation. Two conditions, both set from
-# what the engine shows on B200 (worst position 0.22 to 0.57 of the noise, the median position
-# below a tenth of it): no position beyond MAX_SHARE of the noise, and the median position of a
-# comparison within MEDIAN_SHARE of it. A wrong key, position or page in the sharp models moves
+# what the engine shows on B200 over all comparisons of the suite (the worst position of a
+# comparison 0.25 to 0.57 of the noise, its median position 0.05 to 0.24 of it, the largest medians
+# at the full widths of the 1B and 3B shapes): no position beyond MAX_SHARE of the noise, and the
+# median position of a comparison within MEDIAN_SHARE of it. A wrong key, position or page in the sharp models moves
 # logits by about their own size, an order of magnitude more than the noise; a slightly wrong
 # scale or a lost low-order contribution shifts the median before it shows at the worst place.
 BF16_MAX_SHARE = 0.65
-BF16_MEDIAN_SHARE = 0.25
+BF16_MEDIAN_SHARE = 0.30
 
 
 class Bound:
@@ -85,10 +86,12 @@ def bf16_noise(case: str) -> float:
     return float(max(rows.max() for rows in per_row))
 
 
-def tolerance(dtype: str, case: str) -> Bound:
+def tolerance(dtype: str, case: str, noise: float = None) -> Bound:
+    """The bound of a comparison; ``noise``: the bfloat16 noise measured on the comparison's own rows
+    (default: on the case's standard requests)."""
     if dtype == "float32":
         return Bound(TOL_F32)
-    noise = bf16_noise(case)
+    noise = bf16_noise(case) if noise is None else noise
     return Bound(BF16_MAX_SHARE * noise, BF16_MEDIAN_SHARE * noise, noise)
 
 

@@ -30,6 +30,18 @@ def _plain_rows(case, dtype, requests, wanted):
     return out
 
 
+def _plain_and_bound(case, dtype, requests, wanted):
+    """The plain rows to compare with and the bound they must be met within. In bfloat16 the model's own
+    noise (rounding against exact plain implementation) is measured on these very rows: it grows with
+    the length of a request, and these requests are longer than the ones the case's standard noise is from."""
+    plain = _plain_rows(case, dtype, requests, wanted)
+    if dtype == "float32":
+        return plain, gf.tolerance(dtype, case)
+    exact = _plain_rows(case, "float32", requests, wanted)
+    noise = max(tt.rel_err(plain[r][p], exact[r][p]) for r in plain for p in plain[r])
+    return plain, gf.tolerance(dtype, case, noise=max(noise, gf.bf16_noise(case)))
+
+
 def _wanted(steps):
     wanted = {}
     for rows in tt.wanted_positions(steps).values():
@@ -133,7 +145,8 @@ def test_long_portions_on_cached_tokens(case, dtype):
     engine = gf.make_engine(case, dtype, n_pages=tt.max_tokens_of(steps, reqs) // 16, max_step_tokens=640)
     got = tt.run_in_process(engine, steps)
     _finish(engine, dtype)
-    tt.compare(got, _plain_rows(case, dtype, reqs, _wanted(steps)), gf.tolerance(dtype, case), f"long portions {case} {dtype}")
+    plain, bound = _plain_and_bound(case, dtype, reqs, _wanted(steps))
+    tt.compare(got, plain, bound, f"long portions {case} {dtype}")
 
 
 # ------------------------------------------------------------------ many live requests
