@@ -162,9 +162,12 @@ def main() -> int:
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="layers of the step cases (0 = all of the shape)")
     ap.add_argument("--repeat", type=int, default=10)
+    ap.add_argument("--no-pairs", action="store_true", help="many-token products on single CTAs instead of pairs (cta_group::2)")
     a = ap.parse_args()
     from geneinfer_b200.ops import kernels
     shape_cfg = _set_shape(a.shape)
+    if a.no_pairs:
+        kernels.PAIRED_PRODUCTS = False
     dev = torch.device("cuda:0")
     if a.case == "gemm_prefill":
         gemm_case(a.tokens, a.repeat, dev, kernels)

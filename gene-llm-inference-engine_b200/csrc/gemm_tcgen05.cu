@@ -649,17 +649,68 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-template <int BLOCK_Q>
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster on neighbouring SMs work on one 256-row tile. Each
+// holds 128 rows of the tokens' operand and half of the rows of the weights' operand in its own shared
+// memory and 128 rows of the accumulator in its own tensor memory; one thread of the pair's first CTA
+// issues the MMAs for both. A CTA then fetches 32 KB instead of 48 KB per 64 columns of K, which is what
+// an SM can take in (about 64 bytes a cycle) while its tensor core works through them in 512 cycles.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(both) : "memory");
+}
+// a TMA load into this CTA's shared memory whose bytes are counted on a barrier of either CTA of the pair
+// (bar: a shared::cluster address). No multicast: each CTA fetches its own tiles.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const unsigned long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) return false;
+    }
+}
+
+template <int BLOCK_Q, bool PAIR = false>
 struct TcPersistentConfig {
+    static constexpr int kRowsQ = PAIR ? BLOCK_Q / 2 : BLOCK_Q;  // rows of the weights' tile in this CTA's shared memory
     static constexpr int kStageBytesP = kBlockP * kBlockK * 2;
-    static constexpr int kStageBytesQ = BLOCK_Q * kBlockK * 2;
+    static constexpr int kStageBytesQ = kRowsQ * kBlockK * 2;
     static constexpr int kStageBytes = kStageBytesP + kStageBytesQ;
-    static constexpr int kStages = (BLOCK_Q >= 192) ? 4 : 6;
+    static constexpr int kStages = PAIR ? ((BLOCK_Q >= 192) ? 6 : 8) : ((BLOCK_Q >= 192) ? 4 : 6);
     static constexpr int kStagingBytes = kBlockP * 128;          // 128 rows x 128 bytes, two of them
     static constexpr int kAccStride = (BLOCK_Q > 128) ? 256 : BLOCK_Q;   // columns between the two accumulators
     static constexpr int kTmemCols = 2 * kAccStride;                     // a power of two
     static constexpr int kSmemBytes = kStages * kStageBytes + 2 * kStagingBytes + 1024 + 256;
-    static constexpr uint32_t kIdesc = TcConfig<BLOCK_Q>::kIdesc;
+    // a pair's MMA covers 256 rows (M >> 4 at bits 24..28)
+    static constexpr uint32_t kIdesc = PAIR ? ((TcConfig<BLOCK_Q>::kIdesc & ~(0x1Fu << 24)) | (static_cast<uint32_t>(256 >> 4) << 24))
+                                            : TcConfig<BLOCK_Q>::kIdesc;
+    static_assert(kSmemBytes <= 232448, "the pipeline does not fit into an SM's shared memory");
 };
 
 struct TcPersistentParams {
@@ -675,11 +726,11 @@ struct TcPersistentParams {
 
 constexpr int kPersistentThreads = 64 + 2 * 128;     // producer warp, MMA warp, two epilogue groups of four warps
 
-template <int BLOCK_Q, int EPI>
+template <int BLOCK_Q, int EPI, bool PAIR>
 __global__ void __launch_bounds__(kPersistentThreads, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                           const __grid_constant__ CUtensorMap map_c, const TcPersistentParams p) {
-    using Cfg = TcPersistentConfig<BLOCK_Q>;
+    using Cfg = TcPersistentConfig<BLOCK_Q, PAIR>;
     constexpr int kStages = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -691,11 +742,16 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_kb = (p.K + kBlockK - 1) / kBlockK;
+    // PAIR: the two CTAs of a cluster walk over the same work items; rank r takes rows 128 r .. 128 r + 127 of a
+    // 256-row tile of tokens and fetches rows r BLOCK_Q/2 .. of the weights' tile; p.tiles_p counts 256-row tiles.
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const int worker = PAIR ? blockIdx.x / 2 : blockIdx.x, n_workers = PAIR ? gridDim.x / 2 : gridDim.x;
     const int out_tiles = p.tiles_p * p.tiles_q;
     const int n_tiles = out_tiles * p.splits;
     // work item t: output tile t % out_tiles, range t / out_tiles of K
     auto kb_first = [&](int t) { return (t / out_tiles) * p.kb_per_split; };
     auto kb_count = [&](int t) { return min(total_kb, kb_first(t) + p.kb_per_split) - kb_first(t); };
+    auto tile_p_of = [&](int t) { return PAIR ? 2 * ((t % out_tiles) % p.tiles_p) + static_cast<int>(rank) : (t % out_tiles) % p.tiles_p; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -704,24 +760,35 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bars[2 * kStages + b]), 1);
-            mbar_init(smem_u32(&bars[2 * kStages + 2 + b]), kPersistentThreads - 64);
+            mbar_init(smem_u32(&bars[2 * kStages + 2 + b]), (PAIR ? 2 : 1) * (kPersistentThreads - 64));
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    if (warp == 1) {
+        if (PAIR) tmem_alloc_pair(smem_u32(tmem_slot), Cfg::kTmemCols);
+        else tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     grid_launch_dependents();
+    if (PAIR) cluster_sync_all();    // both CTAs' barriers exist before either signals the other's
     grid_dependency_wait();          // everything below reads what earlier kernels wrote
+    // the first CTA's barriers as the other CTA addresses them: "stage full" counts both CTAs' bytes there, and
+    // "accumulator empty" both CTAs' epilogue threads
+    auto leader_bar = [&](int i) { return PAIR ? cluster_map(smem_u32(&bars[i]), 0u) : smem_u32(&bars[i]); };
+    auto acc_empty_arrive = [&](int buf) {
+        if (PAIR && rank != 0) cluster_mbar_arrive(leader_bar(2 * kStages + 2 + buf));
+        else mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf]));
+    };
 
     if (warp == 0) {
         if (lane == 0) {
             int it = 0, issued_ok = 1;
-            for (int t = blockIdx.x; t < n_tiles && issued_ok; t += gridDim.x) {
-                const int tile_p = (t % out_tiles) % p.tiles_p, tile_q = (t % out_tiles) / p.tiles_p;
+            for (int t = worker; t < n_tiles && issued_ok; t += n_workers) {
+                const int tile_p = tile_p_of(t), tile_q = (t % out_tiles) / p.tiles_p;
                 const int kb0 = kb_first(t), n_kb = kb_count(t);
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = it % kStages;
@@ -730,21 +797,32 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                         issued_ok = 0;
                         break;
                     }
-                    const uint32_t full = smem_u32(&bars[s]);
-                    mbar_expect_tx(full, Cfg::kStageBytes);
                     uint8_t* stage = smem + s * Cfg::kStageBytes;
                     const int k0 = (kb0 + kb) * kBlockK;
-                    tma_load_2d(smem_u32(stage), &map_p, k0, tile_p * kBlockP, full);
-                    if (EPI == kEpiSwiGLU) {
-                        const int n0 = tile_q * (BLOCK_Q / 2);
-                        tma_load_2d(smem_u32(stage + Cfg::kStageBytesP), &map_q, k0, n0, full);
-                        tma_load_2d(smem_u32(stage + Cfg::kStageBytesP + Cfg::kStageBytesQ / 2), &map_q, k0, p.up_row_offset + n0, full);
+                    if constexpr (PAIR) {
+                        // the first CTA's barrier expects the bytes of both; each CTA fetches its own tokens and its half
+                        // of the weights' rows (SwiGLU: the first CTA the gate rows, the second the up rows)
+                        const uint32_t full = leader_bar(s);
+                        if (rank == 0) mbar_expect_tx(smem_u32(&bars[s]), 2 * Cfg::kStageBytes);
+                        tma_load_2d_pair(smem_u32(stage), &map_p, k0, tile_p * kBlockP, full);
+                        const int n0 = (EPI == kEpiSwiGLU) ? tile_q * (BLOCK_Q / 2) + static_cast<int>(rank) * p.up_row_offset
+                                                           : tile_q * BLOCK_Q + static_cast<int>(rank) * (BLOCK_Q / 2);
+                        tma_load_2d_pair(smem_u32(stage + Cfg::kStageBytesP), &map_q, k0, n0, full);
                     } else {
-                        tma_load_2d(smem_u32(stage + Cfg::kStageBytesP), &map_q, k0, tile_q * BLOCK_Q, full);
+                        const uint32_t full = smem_u32(&bars[s]);
+                        mbar_expect_tx(full, Cfg::kStageBytes);
+                        tma_load_2d(smem_u32(stage), &map_p, k0, tile_p * kBlockP, full);
+                        if (EPI == kEpiSwiGLU) {
+                            const int n0 = tile_q * (BLOCK_Q / 2);
+                            tma_load_2d(smem_u32(stage + Cfg::kStageBytesP), &map_q, k0, n0, full);
+                            tma_load_2d(smem_u32(stage + Cfg::kStageBytesP + Cfg::kStageBytesQ / 2), &map_q, k0, p.up_row_offset + n0, full);
+                        } else {
+                            tma_load_2d(smem_u32(stage + Cfg::kStageBytesP), &map_q, k0, tile_q * BLOCK_Q, full);
+                        }
                     }
                 }
             }
-            if (*abort_flag) {
+            if (*abort_flag && (!PAIR || rank == 0)) {
                 const int first = max(0, it - kStages);
                 for (int i = first; i < it; ++i) {
                     const unsigned long long t0 = clock64();
@@ -755,12 +833,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {           // a pair's MMAs are issued by its first CTA
             int it = 0, j = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++j) {
+            for (int t = worker; t < n_tiles && ok; t += n_workers, ++j) {
                 const int buf = j & 1;
-                if (!mbar_wait(smem_u32(&bars[2 * kStages + 2 + buf]), ((j >> 1) & 1) ^ 1, abort_flag)) {
+                const uint32_t acc_empty = smem_u32(&bars[2 * kStages + 2 + buf]);
+                if (!(PAIR ? mbar_wait_cluster(acc_empty, ((j >> 1) & 1) ^ 1, abort_flag)
+                           : mbar_wait(acc_empty, ((j >> 1) & 1) ^ 1, abort_flag))) {
                     if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, kErrMmaWait); }
                     ok = false;
                     break;
@@ -780,11 +860,17 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                     const uint64_t desc_p = umma_desc(a_addr);
                     const uint64_t desc_q = umma_desc(a_addr + Cfg::kStageBytesP);
 #pragma unroll
-                    for (int k = 0; k < kBlockK / 16; ++k)
-                        umma_bf16(tmem_d, desc_p + 2 * k, desc_q + 2 * k, Cfg::kIdesc, (kb > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(smem_u32(&bars[kStages + s]));
+                    for (int k = 0; k < kBlockK / 16; ++k) {
+                        if (PAIR) umma_bf16_pair(tmem_d, desc_p + 2 * k, desc_q + 2 * k, Cfg::kIdesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        else umma_bf16(tmem_d, desc_p + 2 * k, desc_q + 2 * k, Cfg::kIdesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    if (PAIR) umma_commit_pair(smem_u32(&bars[kStages + s]));      // the stage is free in both CTAs
+                    else umma_commit(smem_u32(&bars[kStages + s]));
                 }
-                if (ok) umma_commit(smem_u32(&bars[2 * kStages + buf]));
+                if (ok) {
+                    if (PAIR) umma_commit_pair(smem_u32(&bars[2 * kStages + buf]));
+                    else umma_commit(smem_u32(&bars[2 * kStages + buf]));
+                }
             }
         }
     } else {
@@ -802,8 +888,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
         auto group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory"); };
         int j = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++j) {
-            const int tile_p = (t % out_tiles) % p.tiles_p, tile_q = (t % out_tiles) / p.tiles_p;
+        for (int t = worker; t < n_tiles; t += n_workers, ++j) {
+            const int tile_p = tile_p_of(t), tile_q = (t % out_tiles) / p.tiles_p;
             const int out_row = tile_p * kBlockP + (t / out_tiles) * p.split_rows;
             const int buf = j & 1;
             // Rotation and store: the token's position, its page row and the first cos/sin values are
@@ -851,7 +937,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                 const int heads_per_tile = BLOCK_Q / hd;
                 if (group >= heads_per_tile) {
                     tc_fence_before();
-                    mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf]));
+                    acc_empty_arrive(buf);
                 }
                 const bool valid = rope_token < p.rows_p;
                 for (int j = 0; j < half; j += 16) {
@@ -877,7 +963,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                         tmem_ld_x16(tmem_d + hh * hd + j, lo);
                         tmem_ld_x16(tmem_d + hh * hd + half + j, hi);
                         tmem_ld_wait();
-                        if (last_j && hh + 2 >= heads_per_tile) { tc_fence_before(); mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf])); }
+                        if (last_j && hh + 2 >= heads_per_tile) { tc_fence_before(); acc_empty_arrive(buf); }
                         if (dst == nullptr) continue;
                         uint32_t oa[8], ob[8];
 #pragma unroll
@@ -912,7 +998,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
             constexpr int kChunks = (EPI == kEpiSwiGLU) ? BLOCK_Q / 128 : BLOCK_Q / 32;   // TMA stores per tile
             if (group >= kChunks) {                               // a tile with a single chunk: this group has nothing to read
                 tc_fence_before();
-                mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf]));
+                acc_empty_arrive(buf);
             }
             for (int c = group; c < kChunks; c += 2) {
                 if (leader) bulk_wait_read0();                    // the group's last store has read the staging buffer
@@ -930,7 +1016,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                         tmem_ld_x16(tmem_d + BLOCK_Q / 2 + ch, u);
                         tmem_ld_x16(tmem_d + BLOCK_Q / 2 + ch + 16, u + 16);
                         tmem_ld_wait();
-                        if (last && half == 1) { tc_fence_before(); mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf])); }
+                        if (last && half == 1) { tc_fence_before(); acc_empty_arrive(buf); }
 #pragma unroll
                         for (int q4 = 0; q4 < 4; ++q4) {          // 8 channels = 16 bytes of bfloat16 per step
                             uint32_t packed[4];
@@ -952,7 +1038,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                     tmem_ld_x16(tmem_d + c * 32, r);
                     tmem_ld_x16(tmem_d + c * 32 + 16, r + 16);
                     tmem_ld_wait();
-                    if (last) { tc_fence_before(); mbar_arrive(smem_u32(&bars[2 * kStages + 2 + buf])); }
+                    if (last) { tc_fence_before(); acc_empty_arrive(buf); }
 #pragma unroll
                     for (int q4 = 0; q4 < 8; ++q4)
                         *reinterpret_cast<uint4*>(stg + row * 128 + ((q4 ^ (row & 7)) * 16)) =
@@ -972,9 +1058,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
         tc_fence_before();
     }
     __syncthreads();
+    if (PAIR) cluster_sync_all();    // neither CTA leaves (or frees tensor memory) while the other may still signal it
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+        if (PAIR) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+        else tmem_dealloc(tmem_base, Cfg::kTmemCols);
     }
 }
 
@@ -1029,14 +1117,68 @@ static int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, const
     using Cfg = TcPersistentConfig<BLOCK_Q>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BLOCK_Q, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BLOCK_Q, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
         if (e != cudaSuccess) { set_error("gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::kSmemBytes, cudaGetErrorString(e)); return 1; }
         configured = true;
     }
     const int tiles = p.tiles_p * p.tiles_q * p.splits;
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    launch_kernel((gemm_tc_persistent_kernel<BLOCK_Q, EPI>), dim3(grid), dim3(kPersistentThreads), Cfg::kSmemBytes, st, mp, mq, mc, p);
+    launch_kernel((gemm_tc_persistent_kernel<BLOCK_Q, EPI, false>), dim3(grid), dim3(kPersistentThreads), Cfg::kSmemBytes, st, mp, mq, mc, p);
     return check_launch("gemm_tc_persistent");
+}
+
+// The same product by pairs of CTAs (clusters of two, cta_group::2); p.tiles_p counts 256-row tiles. The grid holds
+// as many pairs as the device keeps resident at once (asked once per kernel), at most one per work item.
+template <int BLOCK_Q, int EPI>
+static int pair_capacity() {
+    using Cfg = TcPersistentConfig<BLOCK_Q, true>;
+    static int cached = -1;
+    if (cached >= 0) return cached;
+    int n = 0;
+    if (cudaFuncSetAttribute(gemm_tc_persistent_kernel<BLOCK_Q, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * sm_count());
+        cfg.blockDim = dim3(kPersistentThreads);
+        cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_persistent_kernel<BLOCK_Q, EPI, true>, &cfg) != cudaSuccess) n = 0;
+    }
+    cudaGetLastError();
+    cached = n;
+    return n;
+}
+
+template <int BLOCK_Q, int EPI>
+static int launch_persistent_pair(const CUtensorMap& mp, const CUtensorMap& mq, const CUtensorMap& mc,
+                                  const TcPersistentParams& p, cudaStream_t st) {
+    using Cfg = TcPersistentConfig<BLOCK_Q, true>;
+    const int capacity = pair_capacity<BLOCK_Q, EPI>();
+    if (capacity < 1) { set_error("gemm_tc: the device holds no pair of CTAs of the paired product"); return 1; }
+    const int items = p.tiles_p * p.tiles_q * p.splits;
+    const int pairs = items < capacity ? items : capacity;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(kPersistentThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = g_pdl_enabled ? 1 : 0;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_persistent_kernel<BLOCK_Q, EPI, true>, mp, mq, mc, p);
+    if (e != cudaSuccess) { set_error("gemm_tc: launch of the paired product failed: %s", cudaGetErrorString(e)); return 1; }
+    return check_launch("gemm_tc_persistent (pairs)");
 }
 
 static int g_cluster_reduce = 1;
@@ -1287,9 +1429,10 @@ __global__ void reduce_splits_kernel(const float* __restrict__ ws, float* __rest
 // splits > 1 (epilogues 0 and 1, N a multiple of 4, at most 8): K is cut into ranges whose tiles are work
 // items of their own; their results go to `workspace` (splits x ceil(M / 128) x 128 x N floats) and a
 // second kernel adds them up in order into C. Few output tiles (a few hundred tokens) then still fill the GPU.
+// pair: the product runs on pairs of CTAs that share 256-row tiles of tokens (block_q 256 only).
 static int gi_gemm_tc_persistent_impl(const void* A, const void* W, void* C, int epilogue, int M, int N, int K,
                                      long long lda, long long ldw, long long ldc, int block_q, void* status,
-                                     int splits, void* workspace, long long workspace_floats, void* stream) {
+                                     int splits, void* workspace, long long workspace_floats, int pair, void* stream) {
     if (M == 0 || N == 0) return 0;
     GI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: sizes must be positive (M=%d, N=%d, K=%d)", M, N, K);
     GI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
@@ -1300,10 +1443,12 @@ static int gi_gemm_tc_persistent_impl(const void* A, const void* W, void* C, int
     GI_REQUIRE((reinterpret_cast<uintptr_t>(A) % 16 == 0) && (reinterpret_cast<uintptr_t>(W) % 16 == 0) &&
                (reinterpret_cast<uintptr_t>(C) % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
     GI_REQUIRE(block_q == 128 || block_q == 256, "gemm_tc: block_q=%d is not 128 or 256", block_q);
+    GI_REQUIRE(!pair || block_q == 256, "gemm_tc: pairs of CTAs work on tiles of 256 columns only");
     GI_REQUIRE(status != nullptr, "gemm_tc: a status word is required");
     TcPersistentParams p = {};
     p.rows_p = M; p.rows_q = N; p.K = K;
-    p.tiles_p = (M + kBlockP - 1) / kBlockP;
+    p.tiles_p = pair ? (M + 2 * kBlockP - 1) / (2 * kBlockP) : (M + kBlockP - 1) / kBlockP;
+    const int rows_per_tile_p = pair ? 2 * kBlockP : kBlockP;
     p.up_row_offset = N;
     p.status = static_cast<int*>(status);
     const int total_kb = (K + kBlockK - 1) / kBlockK;
@@ -1317,7 +1462,7 @@ static int gi_gemm_tc_persistent_impl(const void* A, const void* W, void* C, int
         p.kb_per_split = (total_kb + splits - 1) / splits;
         splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;             // every range holds at least one block
         p.splits = splits;
-        p.split_rows = p.tiles_p * kBlockP;
+        p.split_rows = p.tiles_p * rows_per_tile_p;
         const long long need = static_cast<long long>(splits) * p.split_rows * N;
         GI_REQUIRE(workspace != nullptr && need <= workspace_floats, "gemm_tc: the workspace of %lld floats is too small for %lld", workspace_floats, need);
         if (make_out_map(&mc, workspace, splits * p.split_rows, N, N, false)) return 1;
@@ -1336,11 +1481,16 @@ static int gi_gemm_tc_persistent_impl(const void* A, const void* W, void* C, int
     if (epilogue == kEpiSwiGLU) {
         p.tiles_q = (N + block_q / 2 - 1) / (block_q / 2);
         if (make_map(&mq, W, 2 * N, K, ldw, block_q / 2)) return 1;
+        if (pair) return launch_persistent_pair<256, kEpiSwiGLU>(mp, mq, mc, p, st);
         if (block_q == 256) return launch_persistent<256, kEpiSwiGLU>(mp, mq, mc, p, st);
         return launch_persistent<128, kEpiSwiGLU>(mp, mq, mc, p, st);
     }
     p.tiles_q = (N + block_q - 1) / block_q;
-    if (make_map(&mq, W, N, K, ldw, block_q)) return 1;
+    if (make_map(&mq, W, N, K, ldw, pair ? block_q / 2 : block_q)) return 1;
+    if (pair) {
+        if (run_epilogue == kEpiAddF32) return launch_persistent_pair<256, kEpiAddF32>(mp, mq, mc, p, st);
+        return finish(launch_persistent_pair<256, kEpiStoreF32>(mp, mq, mc, p, st));
+    }
     if (block_q == 256) {
         if (run_epilogue == kEpiAddF32) return launch_persistent<256, kEpiAddF32>(mp, mq, mc, p, st);
         return finish(launch_persistent<256, kEpiStoreF32>(mp, mq, mc, p, st));
@@ -1356,7 +1506,7 @@ static int gi_gemm_tc_persistent_rope_impl(const void* A, const void* W, int M, 
                                           const int* positions, const int* row_req, const int* block_tables,
                                           int table_stride, const float* cos_t, const float* sin_t, int rot_half,
                                           int interleaved, void* q_out, void* k_cache, void* v_cache, int H, int Hkv,
-                                          int hd, int page_size, int write_kv, void* status, void* stream) {
+                                          int hd, int page_size, int write_kv, void* status, int pair, void* stream) {
     if (M == 0) return 0;
     GI_REQUIRE(M > 0 && K > 0 && H > 0 && Hkv > 0 && page_size > 0, "gemm_tc rope: sizes must be positive");
     GI_REQUIRE(hd == 32 || hd == 64 || hd == 128, "gemm_tc rope: head size %d is not 32, 64 or 128", hd);
@@ -1374,13 +1524,14 @@ static int gi_gemm_tc_persistent_rope_impl(const void* A, const void* W, int M, 
     const int N = (H + 2 * Hkv) * hd;
     TcPersistentParams p = {};
     p.rows_p = M; p.rows_q = N; p.K = K;
-    p.tiles_p = (M + kBlockP - 1) / kBlockP;
+    p.tiles_p = pair ? (M + 2 * kBlockP - 1) / (2 * kBlockP) : (M + kBlockP - 1) / kBlockP;
     // 256 or 192 accumulator columns per tile: whichever needs fewer column-rounds of the GPU (rounds of
     // tiles over the SMs x tile width); with 3072 outputs and 2048 tokens 192 tiles of 256 are 2 rounds
     // of 256, 256 tiles of 192 are 2 rounds of 192
+    const int workers = pair ? sm_count() / 2 : sm_count();
     auto rounds_cost = [&](int bq) {
         const long long tiles = static_cast<long long>(p.tiles_p) * ((N + bq - 1) / bq);
-        return (tiles + sm_count() - 1) / sm_count() * bq;
+        return (tiles + workers - 1) / workers * bq;
     };
     const int block_q = (192 % hd == 0 && rounds_cost(192) < rounds_cost(256)) ? 192 : 256;
     p.tiles_q = (N + block_q - 1) / block_q;
@@ -1391,8 +1542,12 @@ static int gi_gemm_tc_persistent_rope_impl(const void* A, const void* W, int M, 
                              static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
                              static_cast<__nv_bfloat16*>(v_cache), H, Hkv, hd, page_size, write_kv};
     CUtensorMap mp, mq;
-    if (make_map(&mp, A, M, K, lda, kBlockP) || make_map(&mq, W, N, K, ldw, block_q)) return 1;
+    if (make_map(&mp, A, M, K, lda, kBlockP) || make_map(&mq, W, N, K, ldw, pair ? block_q / 2 : block_q)) return 1;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (pair) {
+        if (block_q == 192) return launch_persistent_pair<192, kEpiRopeStore>(mp, mq, mp /* no TMA store */, p, st);
+        return launch_persistent_pair<256, kEpiRopeStore>(mp, mq, mp /* no TMA store */, p, st);
+    }
     if (block_q == 192) return launch_persistent<192, kEpiRopeStore>(mp, mq, mp /* no TMA store */, p, st);
     return launch_persistent<256, kEpiRopeStore>(mp, mq, mp /* no TMA store */, p, st);
 }
@@ -1407,10 +1562,10 @@ extern "C" int gi_gemm_tc_rope(const void* A, const void* W, int M, int K, long 
     return gi::dispatch(gi_gemm_tc_rope_impl, A, W, M, K, lda, ldw, block_q, splits, workspace, workspace_floats, counters, n_counters, status, w_tiles, positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved, q_out, k_cache, v_cache, H, Hkv, hd, page_size, write_kv, stream);
 }
 
-extern "C" int gi_gemm_tc_persistent(const void* A, const void* W, void* C, int epilogue, int M, int N, int K, long long lda, long long ldw, long long ldc, int block_q, void* status, int splits, void* workspace, long long workspace_floats, void* stream) {
-    return gi::dispatch(gi_gemm_tc_persistent_impl, A, W, C, epilogue, M, N, K, lda, ldw, ldc, block_q, status, splits, workspace, workspace_floats, stream);
+extern "C" int gi_gemm_tc_persistent(const void* A, const void* W, void* C, int epilogue, int M, int N, int K, long long lda, long long ldw, long long ldc, int block_q, void* status, int splits, void* workspace, long long workspace_floats, int pair, void* stream) {
+    return gi::dispatch(gi_gemm_tc_persistent_impl, A, W, C, epilogue, M, N, K, lda, ldw, ldc, block_q, status, splits, workspace, workspace_floats, pair, stream);
 }
 
-extern "C" int gi_gemm_tc_persistent_rope(const void* A, const void* W, int M, int K, long long lda, long long ldw, const int* positions, const int* row_req, const int* block_tables, int table_stride, const float* cos_t, const float* sin_t, int rot_half, int interleaved, void* q_out, void* k_cache, void* v_cache, int H, int Hkv, int hd, int page_size, int write_kv, void* status, void* stream) {
-    return gi::dispatch(gi_gemm_tc_persistent_rope_impl, A, W, M, K, lda, ldw, positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved, q_out, k_cache, v_cache, H, Hkv, hd, page_size, write_kv, status, stream);
+extern "C" int gi_gemm_tc_persistent_rope(const void* A, const void* W, int M, int K, long long lda, long long ldw, const int* positions, const int* row_req, const int* block_tables, int table_stride, const float* cos_t, const float* sin_t, int rot_half, int interleaved, void* q_out, void* k_cache, void* v_cache, int H, int Hkv, int hd, int page_size, int write_kv, void* status, int pair, void* stream) {
+    return gi::dispatch(gi_gemm_tc_persistent_rope_impl, A, W, M, K, lda, ldw, positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved, q_out, k_cache, v_cache, H, Hkv, hd, page_size, write_kv, status, pair, stream);
 }

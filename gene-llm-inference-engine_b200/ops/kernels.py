@@ -362,6 +362,15 @@ def sm_count() -> int:
     return _sm_count
 
 
+# Many-token products on pairs of CTAs (tcgen05 cta_group::2): the two CTAs of a pair share a 256-row tile of
+# tokens and each fetches half of the weights' tile, so an SM takes in 32 KB instead of 48 KB per 64 columns of K.
+PAIRED_PRODUCTS = True
+
+
+def _paired(M: int, block_q: int) -> int:
+    return int(PAIRED_PRODUCTS and M > 128 and block_q == 256)
+
+
 def _persistent_plan(M: int, N: int, K: int):
     block_q = 256 if N >= 256 else 128 if N > 64 else 64
     splits = 1
@@ -478,13 +487,13 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     st = _tc_state(a.device)
     if persistent:
         # many tokens, 32-bit output: the persistent kernel (epilogue overlapped, TMA stores)
-        need = splits * ((M + 127) // 128 * 128) * N
+        need = splits * ((M + 255) // 256 * 256) * N
         if splits > 1 and need > st.workspace.numel():
             splits = 1
         check(lib().gi_gemm_tc_persistent(_dev(a, "a", torch.bfloat16), _dev(w, "w", torch.bfloat16),
                                           _dev(out, "out", torch.float32), 1 if accumulate else 0, M, N, K, K, K, N,
-                                          block_q, st.status.data_ptr(), splits, st.workspace.data_ptr(),
-                                          st.workspace.numel(), _stream()), "gemm_tc")
+                                          block_q, st.status.data_ptr(), splits, st.workspace.data_ptr() if splits > 1 else 0,
+                                          st.workspace.numel() if splits > 1 else 0, _paired(M, block_q), _stream()), "gemm_tc")
         if splits > 1:
             count_launches(1)     # the kernel that adds the ranges up
         return
@@ -510,7 +519,7 @@ def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> 
     st = _tc_state(a.device)
     check(lib().gi_gemm_tc_persistent(_dev(a, "a", torch.bfloat16), _dev(w_gate_up, "w_gate_up", torch.bfloat16),
                                       _dev(out, "out", torch.bfloat16), 2, M, I, K, K, K, I, 256,
-                                      st.status.data_ptr(), 1, 0, 0, _stream()), "gemm_swiglu")
+                                      st.status.data_ptr(), 1, 0, 0, _paired(M, 256), _stream()), "gemm_swiglu")
 
 
 _ROPE_FEW_TOKENS = 32      # up to here the few-token product (weights on the 128-row side) does the rotation: measured
@@ -570,7 +579,7 @@ def gemm_rope_store(a: torch.Tensor, w_qkv: torch.Tensor, positions: torch.Tenso
                                     *rope_args, _stream()), "gemm_rope_store")
     else:
         check(lib().gi_gemm_tc_persistent_rope(_dev(a, "a", torch.bfloat16), _dev(w_qkv, "w_qkv", torch.bfloat16), M, K, K, K,
-                                               *rope_args, st.status.data_ptr(), _stream()), "gemm_rope_store")
+                                               *rope_args, st.status.data_ptr(), _paired(M, 256), _stream()), "gemm_rope_store")
 
 
 def status_word(device: torch.device) -> torch.Tensor:
