@@ -401,13 +401,16 @@ def gemm_tc_plan(M: int, N: int, K: int):
     return _persistent_plan(M, N, K)
 
 
+_STREAMING_SHARE = 0.75
+
+
 def _swap_plan(M: int, N: int, K: int):
     block_q = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
     tiles = (N + 127) // 128
     k_blocks = (K + 63) // 64
     # split K until about three quarters of the SMs stream weights (112 CTAs on a B200), keeping at least
     # 4 steps of 64 per CTA (measured on B200 at the Llama-3.2-1B widths: 4 splits for 24 tiles, 6..8 for 16, 1 for 128)
-    streaming = sm_count() * 3 // 4 + 1
+    streaming = int(sm_count() * _STREAMING_SHARE) + 1
     splits = 1
     while tiles * (splits + 1) <= streaming and k_blocks // (splits + 1) >= 4 and splits < 8:
         splits += 1

@@ -71,3 +71,31 @@ def test_plain_sampler_stream_and_rules():
     assert [p.sample(logits, u) for u in (0.0, 0.62, 0.63, 0.99)] == [0, 0, 1, 1]
     assert pm.PlainSampler(temperature=1.0, top_k=1).sample(logits, 0.99) == 0
     assert pm.PlainSampler(temperature=1.0, top_p=1e-6).sample(logits, 0.99) == 0
+
+
+def test_plain_sampler_matches_the_reference_sampler_token_for_token():
+    """tests/golden/sampler.npz holds what the reference's own sampler (its gi_sampler_check tool, built
+    on the CPU by tests/golden/make_sampler_golden.py) returns for fixed logits: its generator's
+    uniform numbers, its picks for given uniform numbers under every kind of setting (a tie of the
+    two best logits included), and whole draws from its generator."""
+    g = np.load(os.path.join(GOLDEN, "sampler.npz"))
+    seeds = [int(s) for s in g["seeds"]]
+    for seed, want in zip(seeds, g["uniforms"]):
+        s = pm.PlainSampler(0.8, 0, 1.0, seed=seed)
+        got = np.array([s.next_uniform() for _ in range(len(want))], dtype=np.float32)
+        assert np.array_equal(got, want), f"seed {seed}: the generator's numbers differ"
+    us = g["us"]
+    checked = 0
+    for vocab in (50, 384):
+        logits = g[f"logits_{vocab}"]
+        for k, (t, top_k, top_p) in enumerate(g["settings"]):
+            s = pm.PlainSampler(float(t), int(top_k), float(top_p))
+            got = [s.sample(logits, u) for u in us]
+            want = g[f"uniform_{vocab}_{k}"].tolist()
+            assert got == want, f"vocab {vocab}, temperature {t}, top-k {int(top_k)}, top-p {top_p}: picks differ"
+            checked += len(got)
+            if t > 0:
+                s = pm.PlainSampler(float(t), int(top_k), float(top_p), seed=seeds[k % len(seeds)])
+                drawn = [s.sample(logits) for _ in range(32)]
+                assert drawn == g[f"rng_{vocab}_{k}"].tolist(), f"vocab {vocab}, setting {k}: draws from the generator differ"
+    assert checked == 2 * 7 * 64
