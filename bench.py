@@ -425,7 +425,18 @@ def run_scenario(args):
         if got == batched:
             same += 1
         elif first_diff is None:
-            first_diff = {"request": i, "token": next(k for k in range(new) if got[k] != batched[k])}
+            k = next(k for k in range(new) if got[k] != batched[k])
+            # how close the two candidates were: the logits at that place once more (the request alone, fed in portions of 2,048)
+            from geneinfer_b200.engine.step import StepEntry
+            fed = list(prompts[i]) + batched[:k]
+            alone.steps.open("gap")
+            for c in range(0, len(fed), 2048):
+                part = fed[c:c + 2048]
+                logits = alone.steps.step([StepEntry("gap", part, [len(part) - 1] if c + 2048 >= len(fed) else [])])
+            row = logits[0].float().cpu()
+            alone.steps.close("gap")
+            first_diff = {"request": i, "token": k, "logit_gap": round(abs(float(row[got[k]] - row[batched[k]])), 5),
+                          "logit_spread": round(float(row.max() - row.median()), 3)}
     out["alone"] = {"requests_checked": len(subset), "identical_to_running_alone": same, "first_difference": first_diff}
     if dtype == "float32" and same != len(subset):
         raise RuntimeError(f"scenario {args.scenario}: in 32-bit a request generated other tokens than alone: {first_diff}")

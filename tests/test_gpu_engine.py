@@ -163,3 +163,40 @@ def test_trace_run_tool(case, dtype, tmp_path):
     vocab = gf.CASES[case][0]["vocab_size"]
     got = tt.run_trace_tool(gf.model_dir(case), dtype, steps, tt.max_tokens_of(steps, reqs), str(tmp_path / "out"), vocab)
     tt.compare(got, gf.plain_logits(case, dtype), gf.tolerance(dtype, case), f"trace_run {case} {dtype}")
+
+
+def test_trace_run_taps(tmp_path):
+    """``--taps`` writes the residual stream of the wanted rows with the reference's tags
+    (tools/forward_main.cpp:92-102): checked against the plain implementation layer by layer."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import torch
+    import plain_model as pm
+    case = "a"
+    toks = gf.requests(case)["r0"]
+    head = 25
+    steps = [{"step": 0, "entries": [{"id": "t", "tokens": toks[:head], "want": [0, head - 1]}], "end": []},
+             {"step": 1, "entries": [{"id": "t", "tokens": toks[head:head + 1], "want": [0]}], "end": ["t"]}]
+    out = tmp_path / "out"
+    cmd = [sys.executable, os.path.join(tt.ROOT, "bin", "trace_run"), "--model", gf.model_dir(case), "--dtype", "float32",
+           "--out", str(out), "--max-tokens", "64", "--taps"]
+    p = subprocess.run(cmd, input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    w, cfg = pm.load_plain(gf.model_dir(case))
+    D = cfg["hidden"] if "hidden" in cfg else w["model.embed_tokens.weight"].shape[1]
+    n = head + 1
+    cos, sin = pm.plain_rope_table(range(n), cfg["head_dim"], cfg["theta"], cfg["scaling"])
+    x = pm.plain_embedding(w["model.embed_tokens.weight"], toks[:n])
+    want = {"embedding": x.clone()}
+    for l in range(cfg["layers"]):
+        x = pm.plain_layer(x, w, f"model.layers.{l}.", cfg, cos, sin, pm.no_rounding)
+        want[f"layer{l:02d}_ffn_out"] = x.clone()
+    want["final_norm"] = pm.plain_rmsnorm(x, w["model.norm.weight"], cfg["eps"])
+    for step, rows in ((0, [0, head - 1]), (1, [head])):
+        for tag, full in want.items():
+            got = np.fromfile(out / f"{step}.{tag}.f32", dtype="<f4").reshape(len(rows), D)
+            assert tt.rel_err(got, full[rows].numpy()) < gf.TOL_F32, f"step {step}, tap {tag}"
+        for l in range(cfg["layers"]):
+            assert (out / f"{step}.layer{l:02d}_attn_out.f32").stat().st_size == len(rows) * D * 4

@@ -87,6 +87,17 @@ class _Ctx:
                 torch.tensor(tiles, dtype=torch.int32, device=DEV).reshape(len(tiles), 3), 1)
 
 
+def test_a_head_size_the_kernels_do_not_serve_is_refused_when_the_model_is_built(tmp_path):
+    """config.json may give any even head size (the reference accepts it); the attention kernels serve
+    multiples of 16 up to 256. The refusal comes when the model is built, with the size in the message,
+    not at the first step after weights and pages are on the device."""
+    from geneinfer_b200.engine.loading import load_model
+    config = dict(tc.TINY_A, head_dim=24, hidden_size=96, num_attention_heads=4, num_key_value_heads=2)
+    folder = tc.make_model_dir(config, tc.WEIGHTS_A, str(tmp_path / "hd24"))
+    with pytest.raises(ValueError, match="head size 24"):
+        load_model(folder, dtype="float32")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_mixer_part(dtype):
     from geneinfer_b200.config import PartSpec
