@@ -27,12 +27,20 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """The parts of one layer. ``block`` names the arrangement (see parts/block.py)."""
+    """The parts of one layer. ``block`` names the arrangement (see parts/block.py); ``extra`` holds
+    further parts that an arrangement may name beyond the usual four (norms after the mixer or the
+    feed-forward of a sandwich arrangement, a second feed-forward run in parallel, ...): the block
+    builds them by their key, with the weights under ``layers.<i>.<key>.``."""
     mixer: PartSpec
     feed_forward: PartSpec
     mixer_norm: PartSpec
     feed_forward_norm: PartSpec
     block: str = "pre_norm"
+    extra: Dict[str, PartSpec] = field(default_factory=dict)
+
+    def __hash__(self):
+        return hash((self.mixer, self.feed_forward, self.mixer_norm, self.feed_forward_norm, self.block,
+                     tuple(sorted((k, hash(v)) for k, v in self.extra.items()))))
 
 
 @dataclass(frozen=True)
@@ -56,6 +64,7 @@ class ModelSpec:
     final_norm: PartSpec
     tie_word_embeddings: bool
     embedding_scale: float = 1.0   # multiplier on embedding rows (1 = none)
+    logit_transform: Optional[PartSpec] = None   # applied to the logits after the head (a scale, a soft cap); None = none
 
     def validate(self) -> None:
         n = len(self.layers)

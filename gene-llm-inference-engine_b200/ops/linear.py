@@ -21,6 +21,8 @@ from . import kernels
 
 
 class Linear:
+    not_weights = ("weight_tiles",)      # a second layout of the same weights, not counted among a model's weight bytes
+
     def __init__(self, weight: torch.Tensor, compute_dtype: torch.dtype, device: torch.device, tiles: bool = True):
         if weight.dim() != 2:
             raise ValueError("Linear: the weight must be a matrix")

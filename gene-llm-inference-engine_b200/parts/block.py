@@ -47,6 +47,14 @@ class PreNormBlock:
         self.feed_forward.forward(ctx, xn, x)
 
 
+def build_extra(layer_spec, key: str, table, what: str, weights, build):
+    """Builds the part that a layer's ``extra`` names ``key`` (for arrangements with more parts than
+    the usual four), with the weights under ``<key>.``."""
+    if key not in layer_spec.extra:
+        raise KeyError(f"block arrangement '{layer_spec.block}' needs a part '{key}' that the layer's specification lacks")
+    return build_part(table, what, layer_spec.extra[key], sub_weights(weights, key + "."), build)
+
+
 def _launch_key(ctx, *parts):
     """The joint key of some parts' launches for this step, or None when one of them has none (or the
     context records nothing)."""

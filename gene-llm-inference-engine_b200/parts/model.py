@@ -14,7 +14,7 @@ import torch
 from ..config import ModelSpec
 from ..ops import kernels
 from ..ops.linear import Linear
-from .registry import BLOCKS, NORMS, BuildContext, build_part, sub_weights
+from .registry import BLOCKS, LOGIT_TRANSFORMS, NORMS, BuildContext, build_part, sub_weights
 
 
 @dataclass(frozen=True)
@@ -59,6 +59,11 @@ class DecoderModel:
             self.head = Linear(params["head.weight"], compute_dtype, device, tiles=weight_tiles)
             if (self.head.out_features, self.head.in_features) != (spec.vocab_size, spec.hidden_size):
                 raise ValueError("head.weight has the wrong shape")
+        # what the architecture does to its logits after the head (``forward(ctx, logits)``, in place); Llama: nothing
+        self.logit_transform = None
+        if spec.logit_transform is not None:
+            self.logit_transform = build_part(LOGIT_TRANSFORMS, "logit transform", spec.logit_transform,
+                                              sub_weights(params, "logit_transform."), build)
 
     # ------------------------------------------------------------------ what the cache manager must provide
     def cache_needs(self):
@@ -79,9 +84,10 @@ class DecoderModel:
         return out
 
     def weight_bytes(self) -> int:
-        """Bytes of distinct weight tensors on the device (a tied head counts once; the tile-by-tile
-        copies that few-token products read in place of the row-major matrices are not counted: a step
-        reads one or the other)."""
+        """Bytes of distinct weight tensors on the device (a tied head counts once). Every device tensor
+        that a part holds counts, except the attributes the part's class lists in ``not_weights``:
+        tables computed from constants (cos/sin), and the tile-by-tile copies that few-token products
+        read in place of the row-major matrices (a step reads one or the other)."""
         seen, total = set(), 0
 
         def visit(obj):
@@ -91,10 +97,10 @@ class DecoderModel:
                     seen.add(obj.data_ptr())
                     total += obj.numel() * obj.element_size()
             elif hasattr(obj, "__dict__"):
+                skip = getattr(type(obj), "not_weights", ())
                 for k, v in vars(obj).items():
-                    if k in ("cos", "sin", "weight_tiles"):
-                        continue
-                    visit(v)
+                    if k not in skip:
+                        visit(v)
             elif isinstance(obj, (list, tuple)):
                 for v in obj:
                     visit(v)
@@ -103,6 +109,7 @@ class DecoderModel:
         visit(self.layers)
         visit(self.final_norm)
         visit(self.head)
+        visit(self.logit_transform)
         return total
 
     # ------------------------------------------------------------------ the forward pass of one step
@@ -123,4 +130,6 @@ class DecoderModel:
         ctx.tap("final_norm", -1, xn)
         logits = ctx.scratch("logits", (k, self.vocab_size), torch.float32, capacity=ctx.max_logit_rows)
         self.head.forward(xn, logits)
+        if self.logit_transform is not None:
+            self.logit_transform.forward(ctx, logits)
         return logits

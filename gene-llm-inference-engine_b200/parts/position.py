@@ -42,6 +42,7 @@ class RotaryPosition:
     the first dims)."""
 
     applies = "qk_before_store"
+    not_weights = ("cos", "sin")        # tables computed from constants: not counted among a model's weight bytes
 
     def __init__(self, params, weights, build):
         self.head_dim = int(params["head_dim"])

@@ -17,6 +17,7 @@ FEED_FORWARDS: Dict[str, Callable] = {}
 NORMS: Dict[str, Callable] = {}
 POSITION_ENCODINGS: Dict[str, Callable] = {}
 BLOCKS: Dict[str, Callable] = {}
+LOGIT_TRANSFORMS: Dict[str, Callable] = {}     # what an architecture does to its logits after the head; none is built in
 
 
 @dataclass
@@ -52,6 +53,10 @@ def register_position_encoding(kind: str):
 
 def register_block(kind: str):
     return _register(BLOCKS, kind)
+
+
+def register_logit_transform(kind: str):
+    return _register(LOGIT_TRANSFORMS, kind)
 
 
 def build_part(table: Dict[str, Callable], what: str, spec, weights, build: BuildContext):

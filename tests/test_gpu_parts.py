@@ -333,10 +333,45 @@ def _register_toy_routed():
     each expert a small gated unit) and a position encoding of its own (angles that grow with the
     square root of the position), entered through the public registries like the first toy."""
     from geneinfer_b200.config import (Architecture, LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture)
-    from geneinfer_b200.parts import FEED_FORWARDS, register_feed_forward, register_position_encoding
+    from geneinfer_b200.parts import (FEED_FORWARDS, MIXERS, NORMS, register_block, register_feed_forward,
+                                      register_logit_transform, register_position_encoding, build_part, sub_weights)
+    from geneinfer_b200.parts.block import build_extra
     from geneinfer_b200.weights.plan import TensorRule, WeightPlan
     if "toy_best_of_three" in FEED_FORWARDS:
         return
+
+    @register_logit_transform("toy_halve")
+    class Halve:
+        """What an architecture does to its logits after the head: here a constant factor."""
+        def __init__(self, params, weights, build):
+            self.factor = float(params["factor"])
+
+        def forward(self, ctx, logits):
+            logits.mul_(self.factor)
+
+    @register_block("toy_post_norm")
+    class PostNormBlock:
+        """An arrangement with a fifth part, taken from the layer's ``extra``: the mixer's output goes through a
+        norm of its own before it joins the residual stream; the feed-forward half is the usual pre-norm one."""
+        def __init__(self, layer_spec, weights, build):
+            self.mixer_norm = build_part(NORMS, "norm", layer_spec.mixer_norm, sub_weights(weights, "mixer_norm."), build)
+            self.mixer = build_part(MIXERS, "mixer", layer_spec.mixer, sub_weights(weights, "mixer."), build)
+            self.post_norm = build_extra(layer_spec, "post_mixer_norm", NORMS, "norm", weights, build)
+            self.feed_forward_norm = build_part(NORMS, "norm", layer_spec.feed_forward_norm, sub_weights(weights, "feed_forward_norm."), build)
+            self.feed_forward = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward, sub_weights(weights, "feed_forward."), build)
+            self.dtype = build.compute_dtype
+
+        def forward(self, ctx, run, x):
+            xn = ctx.scratch("normed", tuple(x.shape), self.dtype)
+            y = ctx.scratch("toy_mixer_out", tuple(x.shape), torch.float32)
+            yn = ctx.scratch("toy_mixer_out_normed", tuple(x.shape), torch.float32)
+            self.mixer_norm.forward(x, xn)
+            y.zero_()
+            self.mixer.forward(ctx, run, xn, y)
+            self.post_norm.forward(y, yn)
+            x.add_(yn)
+            self.feed_forward_norm.forward(x, xn)
+            self.feed_forward.forward(ctx, xn, x)
 
     @register_position_encoding("toy_sqrt_angles")
     class SqrtAngles:
@@ -387,9 +422,13 @@ def _register_toy_routed():
                                          "scale": 0.3, "window": None, "position": pos})
             routed = PartSpec("toy_best_of_three", {"hidden_size": D, "intermediate_size": 24})
             dense = PartSpec("swiglu", {"hidden_size": D, "intermediate_size": 40})
-            layers = [LayerSpec(att, routed if i % 2 == 0 else dense, norm, norm) for i in range(self.layers)]
+            # odd layers: the dense feed-forward and the arrangement with a norm after the mixer
+            layers = [LayerSpec(att, routed, norm, norm) if i % 2 == 0 else
+                      LayerSpec(att, dense, norm, norm, block="toy_post_norm", extra={"post_mixer_norm": norm})
+                      for i in range(self.layers)]
             return ModelSpec("ToyRoutedForCausalLM", D, self.vocab, self.max_pos, layers,
-                             [ScheduleEntry(i) for i in range(self.layers)], norm, True)
+                             [ScheduleEntry(i) for i in range(self.layers)], norm, True,
+                             logit_transform=PartSpec("toy_halve", {"factor": 0.5}))
 
     def plan(cfg):
         D = cfg.hidden
@@ -401,7 +440,7 @@ def _register_toy_routed():
                 rules += [TensorRule(f"l{i}.router", (3, D))] + [TensorRule(f"l{i}.e{e}.gu", (48, D)) for e in range(3)] + \
                          [TensorRule(f"l{i}.e{e}.down", (D, 24)) for e in range(3)]
             else:
-                rules += [TensorRule(f"l{i}.gu", (80, D)), TensorRule(f"l{i}.down", (D, 40))]
+                rules += [TensorRule(f"l{i}.gu", (80, D)), TensorRule(f"l{i}.down", (D, 40)), TensorRule(f"l{i}.n3", (D,), "vector")]
 
         def assemble(t):
             out = {"embedding.weight": t["emb"], "final_norm.weight": t["norm"], "head.weight": t["emb"]}
@@ -415,6 +454,7 @@ def _register_toy_routed():
                     out[q + "feed_forward.down"] = torch.stack([t[f"l{i}.e{e}.down"] for e in range(3)])
                 else:
                     out[q + "feed_forward.w_gate_up"], out[q + "feed_forward.w_down"] = t[f"l{i}.gu"], t[f"l{i}.down"]
+                    out[q + "post_mixer_norm.weight"] = t[f"l{i}.n3"]
             return out
         return WeightPlan(rules, [], assemble)
 
@@ -435,7 +475,8 @@ def _toy_routed_plain(w, cfg, toks):
         xn = pm.plain_rmsnorm(x, w[f"l{i}.n1"], 3e-6)
         qkv = xn @ w[f"l{i}.qkv"].T
         q, k, v = rot(qkv[:, :48].reshape(T, 3, 16)), rot(qkv[:, 48:96].reshape(T, 3, 16)), qkv[:, 96:].reshape(T, 3, 16)
-        x = x + pm.plain_attention(q, k, v, 0.3).reshape(T, 48) @ w[f"l{i}.o"].T
+        y = pm.plain_attention(q, k, v, 0.3).reshape(T, 48) @ w[f"l{i}.o"].T
+        x = x + (y if i % 2 == 0 else pm.plain_rmsnorm(y, w[f"l{i}.n3"], 3e-6))
         xn = pm.plain_rmsnorm(x, w[f"l{i}.n2"], 3e-6)
         if i % 2 == 0:
             best = (xn @ w[f"l{i}.router"].T).argmax(dim=-1)
@@ -449,7 +490,7 @@ def _toy_routed_plain(w, cfg, toks):
         else:
             gu = xn @ w[f"l{i}.gu"].T
             x = x + pm.plain_swiglu(gu[:, :40], gu[:, 40:]) @ w[f"l{i}.down"].T
-    return (pm.plain_rmsnorm(x, w["norm"], 3e-6) @ w["emb"].T).numpy(), routes
+    return (0.5 * (pm.plain_rmsnorm(x, w["norm"], 3e-6) @ w["emb"].T)).numpy(), routes
 
 
 def test_toy_architecture_with_a_routed_feed_forward_and_its_own_position_encoding(tmp_path):
