@@ -42,6 +42,20 @@ def _plain_and_bound(case, dtype, requests, wanted):
     return plain, gf.tolerance(dtype, case, noise=max(noise, gf.bf16_noise(case)))
 
 
+def _check_greedy_continuation(w, cfg, rnd, prompt, generated, dtype, what):
+    """Every generated token against the plain logits of its own past (teacher-forced: one plain pass over prompt
+    and generated tokens gives the logits at every place, each depending only on the tokens before it); only a
+    near-tie of the two candidates may differ."""
+    tokens = list(prompt) + list(generated)
+    places = list(range(len(prompt) - 1, len(tokens) - 1))
+    logits = pm.plain_forward(w, cfg, tokens[:-1], rnd, positions=places).numpy()
+    for k, t in enumerate(generated):
+        best = int(np.argmax(logits[k]))
+        if t != best:
+            gap = float(logits[k][best] - logits[k][t])
+            assert gap < (1e-4 if dtype == "float32" else 5e-2), f"{what} token {k}: {t} != {best} (gap {gap})"
+
+
 def _wanted(steps):
     wanted = {}
     for rows in tt.wanted_positions(steps).values():
@@ -240,14 +254,49 @@ def test_engine_preempts_and_evicts_when_pages_run_out(dtype):
         w, rnd = pm.round_weights_bf16(w), pm.bf16_rounding
     for i, (p, g) in enumerate(zip(prompts, got)):
         assert len(g) == new
-        tokens = list(p)
-        for k, t in enumerate(g):                            # teacher-forced: every token against the plain logits of its own past
-            logits = pm.plain_forward(w, cfg, tokens, rnd, positions=[len(tokens) - 1])[0].numpy()
-            best = int(np.argmax(logits))
-            if t != best:
-                gap = float(logits[best] - logits[t])
-                assert gap < (1e-4 if dtype == "float32" else 5e-2), f"request {i} token {k}: {t} != {best} (gap {gap})"
-            tokens.append(t)
+        _check_greedy_continuation(w, cfg, rnd, p, g, dtype, f"request {i}")
     engine.clear_prefix_cache()
     assert engine.steps.cache.free_pages() == 14 and not engine.steps.cache.requests
     engine.steps.cache.check_invariants()
+
+
+# ------------------------------------------------------------------ the entry point with sixteen running requests
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_engine_with_sixteen_running_requests_across_context_buckets(dtype, tmp_path):
+    """Twenty requests through ``Engine`` with sixteen running at a time: prompts from 3 to 1,030 tokens, so that
+    decode steps cross the context buckets their graphs are keyed by (256, 1,024, 2,048), a stop token for some,
+    more requests than places. The tokens must be the ones the engine gives without CUDA graphs and launch
+    programs, and the ones the plain implementation's logits name (teacher-forced; only a near-tie may differ)."""
+    from geneinfer_b200 import Engine, SamplingParams
+    config = dict(tc.TINY_C, max_position_embeddings=1280)
+    folder = tc.make_model_dir(config, tc.SHARP_C, str(tmp_path / "c_long"))
+    vocab = config["vocab_size"]
+    lengths = [3, 250, 1030, 17, 260, 1000, 64, 255, 1019, 129, 5, 300, 980, 31, 240, 1024, 90, 270, 33, 512]
+    prompts = [tc.random_tokens(n, vocab, 1200 + i) for i, n in enumerate(lengths)]
+    new = 24
+
+    def run(plain_launches):
+        engine = Engine(folder, dtype=dtype, max_running=16, kv_pages=16 * 40 + 200, step_tokens=512, prefill_chunk=300,
+                        prefix_cache=False)
+        if plain_launches:
+            engine.steps.use_graphs = engine.steps.use_programs = False
+        ids = [engine.submit(p, len(p) + new - 1, SamplingParams(0.0), stop_ids=[7, 11] if i % 3 == 0 else ())
+               for i, p in enumerate(prompts)]
+        engine.run_until_idle()
+        out = [engine.result(i) for i in ids]
+        assert all(not r.error for r in out)
+        assert engine.stats.max_running_seen == 16 and not engine.steps.cache.requests
+        engine.steps.check_status()
+        return engine, [list(r.generated_tokens) for r in out], [r.stopped_by_end_token for r in out]
+
+    fast, got, stopped = run(False)
+    assert fast.steps.graph_replays > 10 and fast.steps.program_runs > 10
+    _, want, want_stopped = run(True)
+    assert got == want and stopped == want_stopped, "graphs or launch programs change the tokens"
+    assert any(stopped) or all(len(g) == new for g in got)
+    w, cfg = pm.load_plain(folder)
+    rnd = pm.no_rounding
+    if dtype == "bfloat16":
+        w, rnd = pm.round_weights_bf16(w), pm.bf16_rounding
+    for i in (0, 2, 5, 8, 15, 19):                           # the shortest, the longest, the ones at the buckets' edges
+        _check_greedy_continuation(w, cfg, rnd, prompts[i], got[i], dtype, f"request {i}")
