@@ -23,13 +23,14 @@ class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_seq_len: Optional[int] = None, page_size: int = 16, kv_pages: Optional[int] = None,
                  max_running: int = 8, step_tokens: int = 2048, prefill_chunk: int = 0, prefix_cache: bool = True,
-                 decode_weight_copy: bool = True):
+                 decode_weight_copy: bool = True, nvtx: bool = False, debug_checks: bool = False):
         """``model_dir``: folder with config.json and model.safetensors. ``dtype``: "bfloat16"
         (serving kernels) or "float32" (everything in true 32-bit). ``max_seq_len`` lowers the
         context length. ``kv_pages``: pages of ``page_size`` positions in the pool (default: room
         for ``max_running`` full contexts, within 80 % of the free device memory).
         ``decode_weight_copy`` (bfloat16): a second copy of the matrices laid out for decode steps, which
-        then stream the weights faster; False saves that memory."""
+        then stream the weights faster; False saves that memory. ``nvtx`` wraps steps, layers and the head in NVTX
+        ranges; ``debug_checks`` validates every step's descriptor (positions, page ids) on the host before launch."""
         self.model = load_model(model_dir, dtype=dtype, device=device, max_position=max_seq_len,
                                 weight_tiles=decode_weight_copy)
         context = self.model.max_position
@@ -48,7 +49,8 @@ class Engine:
                 kv_pages = max(per_request, min(kv_pages, int(0.8 * free) // max(1, page_bytes * len(by_key))))
         step_tokens = max(1, min(step_tokens, max_running * context))
         self.steps = StepEngine(self.model, page_size=page_size, n_pages=kv_pages, max_requests=max_running,
-                                max_step_tokens=step_tokens, max_logit_rows=max_running)
+                                max_step_tokens=step_tokens, max_logit_rows=max_running, nvtx=nvtx,
+                                debug_checks=debug_checks)
         self.sampler = DeviceSampler(self.model.vocab_size, self.model.device, ids=self.steps.feedback)
         self.scheduler = Scheduler(self.steps, self.sampler.sample,
                                    SchedulerConfig(max_running, step_tokens, prefill_chunk, prefix_cache),

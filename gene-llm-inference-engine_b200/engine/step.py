@@ -114,6 +114,10 @@ class StepContext:
             program.run()
             eng.program_runs += 1
 
+    def range(self, name: str):
+        """A named range around some launches for profilers that show NVTX ranges (``StepEngine.nvtx``); free when off."""
+        return _NvtxRange(name) if self._engine.nvtx else _NO_RANGE
+
     def tap(self, tag: str, layer: int, tensor: torch.Tensor) -> None:
         """Shows an intermediate activation to whoever listens (``StepEngine.tap``); the tags follow
         the reference's trace callback (src/model/model.h:16-22): "embedding", "attn_out" and
@@ -150,11 +154,38 @@ class StepContext:
         return self._cache[key]
 
 
+class _NvtxRange:
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        torch.cuda.nvtx.range_pop()
+        return False
+
+
+class _NoRange:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_RANGE = _NoRange()
+
+
 class StepEngine:
     token_feedback = True        # entries may name tokens by their place in ``feedback``
 
     def __init__(self, model: DecoderModel, page_size: int = 16, n_pages: int = 256, max_requests: int = 8,
-                 max_step_tokens: int = 2048, max_logit_rows: Optional[int] = None, use_graphs: bool = True):
+                 max_step_tokens: int = 2048, max_logit_rows: Optional[int] = None, use_graphs: bool = True,
+                 nvtx: bool = False, debug_checks: bool = False):
+        """``nvtx``: every step, layer half and the head are wrapped in NVTX ranges (for profilers that show them).
+        ``debug_checks``: before a step is launched its descriptor is checked on the host: every page a row reads or
+        writes lies inside the pool and belongs to the row's request, positions are consecutive and inside the context."""
         if not torch.cuda.is_available():
             raise RuntimeError("StepEngine needs a CUDA device: this engine has no CPU path")
         self.model = model
@@ -197,6 +228,8 @@ class StepEngine:
         self._graphs: Dict[Tuple, Tuple] = {}
         self.graph_replays = 0
         # launch programs of the parts, by (part, shape key): see StepContext.recorded
+        self.nvtx = nvtx
+        self.debug_checks = debug_checks
         self.use_programs = True
         self._programs: Dict[Tuple, object] = {}
         self.program_runs = 0
@@ -418,8 +451,11 @@ class StepEngine:
             if seg.fresh_state:
                 for st in self.layer_state.values():
                     st[seg.state_slot].zero_()
+        if self.debug_checks:
+            self._check_descriptor(host, segments, total)
         ctx = StepContext(self, total, R, k, segments, views)
-        logits = self._run(ctx)
+        with ctx.range(f"step {total} tokens {R} requests"):
+            logits = self._run(ctx)
         self._post_status()
         for e in entries:
             self.cache.advance(self.cache.requests[e.key], len(e.tokens))
@@ -453,6 +489,34 @@ class StepEngine:
         self.graph_replays += 1
         kernels.count_launches(n_kernels)
         return captured
+
+    def _check_descriptor(self, host: np.ndarray, segments: List[Segment], total: int) -> None:
+        """The step's descriptor as the kernels will read it, checked on the host (``debug_checks``): a wrong page id
+        or position would make a kernel read or write another request's memory without any error."""
+        lay = self._layout
+        pos = host[lay["positions"][0]:lay["positions"][0] + total]
+        req = host[lay["row_req"][0]:lay["row_req"][0] + total]
+        ps = self.page_size
+        for r, seg in enumerate(segments):
+            rows = slice(seg.start, seg.start + seg.length)
+            if not (req[rows] == r).all() or not (pos[rows] == np.arange(seg.first_position, seg.first_position + seg.length)).all():
+                raise AssertionError(f"step descriptor: rows of request {seg.key!r} are not its consecutive positions")
+            if seg.first_position + seg.length > self.model.max_position:
+                raise AssertionError(f"step descriptor: request {seg.key!r} runs beyond the context length")
+            rc = self.cache.requests[seg.key]
+            for g, group in enumerate(self.cache.groups):
+                table = host[self._table_off[g] + r * self._table_stride:self._table_off[g] + (r + 1) * self._table_stride]
+                first = rc.first_live[g] if group.need.window else 0
+                used = table[first:(seg.first_position + seg.length + ps - 1) // ps]
+                if ((used < 0) | (used >= self.n_pages)).any():
+                    raise AssertionError(f"step descriptor: request {seg.key!r} names a page outside the pool of {self.n_pages}")
+                if any(group.pool.ref_count(int(p)) < 1 for p in used):
+                    raise AssertionError(f"step descriptor: request {seg.key!r} names a page that is free")
+        pages = [int(p) for r, seg in enumerate(segments) for g in range(len(self.cache.groups))
+                 for p in self.cache.requests[seg.key].tables[g][(seg.first_position // ps):(seg.first_position + seg.length + ps - 1) // ps]]
+        written = [p for p in pages if p >= 0]
+        if len(set(written)) != len(written) and len(self.cache.groups) == 1:
+            raise AssertionError("step descriptor: two requests of one step write into the same page")
 
     # ------------------------------------------------------------------ the kernels' status word
     def _post_status(self) -> None:

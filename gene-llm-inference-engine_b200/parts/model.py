@@ -118,18 +118,21 @@ class DecoderModel:
         [wanted rows, vocab] (None when no row wants logits)."""
         T = ctx.n_tokens
         x = ctx.scratch("residual", (T, self.hidden_size), torch.float32)
-        kernels.embed(self.embedding, ctx.tokens, x, self.embedding_scale, ctx.feedback)
+        with ctx.range("embedding"):
+            kernels.embed(self.embedding, ctx.tokens, x, self.embedding_scale, ctx.feedback)
         ctx.tap("embedding", -1, x)
         for run in self.runs:
-            self.layers[run.layer].forward(ctx, run, x)
+            with ctx.range(f"layer {run.layer}"):
+                self.layers[run.layer].forward(ctx, run, x)
         k = ctx.n_logit_rows
         if k == 0:
             return None
         xn = ctx.scratch("head_in", (k, self.hidden_size), self.dtype, capacity=ctx.max_logit_rows)
-        self.final_norm.forward(x, xn, rows=ctx.logit_rows)
-        ctx.tap("final_norm", -1, xn)
         logits = ctx.scratch("logits", (k, self.vocab_size), torch.float32, capacity=ctx.max_logit_rows)
-        self.head.forward(xn, logits)
-        if self.logit_transform is not None:
-            self.logit_transform.forward(ctx, logits)
+        with ctx.range("final norm and head"):
+            self.final_norm.forward(x, xn, rows=ctx.logit_rows)
+            ctx.tap("final_norm", -1, xn)
+            self.head.forward(xn, logits)
+            if self.logit_transform is not None:
+                self.logit_transform.forward(ctx, logits)
         return logits

@@ -101,4 +101,4 @@ def make_engine(case: str, dtype: str, n_pages: int, max_requests: int = 4, page
     from geneinfer_b200.engine.step import StepEngine
     model = load_model(model_dir(case), dtype=dtype)
     return StepEngine(model, page_size=page_size, n_pages=n_pages, max_requests=max_requests,
-                      max_step_tokens=max_step_tokens)
+                      max_step_tokens=max_step_tokens, debug_checks=True)

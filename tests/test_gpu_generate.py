@@ -37,7 +37,7 @@ def _plain_continue(case, dtype, prompt, n_new, sampler, stop_ids=()):
 def test_greedy_generation_of_tiny_a(dtype):
     """BASELINE's first configuration: 3 requests of 7/16/33 random ids, 16 greedy tokens each."""
     from geneinfer_b200 import Engine
-    engine = Engine(gf.model_dir("a"), dtype=dtype, max_running=3, kv_pages=12, step_tokens=24)
+    engine = Engine(gf.model_dir("a"), dtype=dtype, max_running=3, kv_pages=12, step_tokens=24, nvtx=True, debug_checks=True)
     prompts = [tc.random_tokens(n, 256, 40 + n) for n in (7, 16, 33)]
     got = engine.generate(prompts, max_new_tokens=16, temperature=0.0)
     for p, g in zip(prompts, got):
