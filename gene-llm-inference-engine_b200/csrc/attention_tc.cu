@@ -1,7 +1,7 @@
 // Prefill attention on the 5th-generation tensor cores (tcgen05), bfloat16, head sizes 64 and 128.
 //
 // One CTA takes 128 query rows (tokens x the query heads of one key/value group) and walks the keys
-// in tiles of 128 over the request's pages:
+// in tiles of KEYS (128 at head size 64, 64 at head size 128) over the request's pages:
 //   warp 0      TMA producer: one box per page and head, each lane requesting its own box; keys and
 //               values have two-place rings and barriers of their own (a key tile is free once its S
 //               product is done, a value tile only after P V), and keys run one tile ahead of values;
@@ -15,7 +15,8 @@
 //               scale O by the correction factor in tensor memory, write P = exp2(S - m) as bfloat16
 //               into a swizzled K-major tile for the second MMA, and at the end normalise O.
 // Scores, maxima, sums and the output accumulator are 32-bit; P is rounded to bfloat16 as the
-// operand of P V. Two CTAs fit on an SM, so one CTA's softmax overlaps the other's MMAs.
+// operand of P V. Two CTAs fit on an SM (at head size 128 thanks to the shorter key tiles), so one
+// CTA's softmax overlaps the other's MMAs.
 // Every mbarrier wait is bounded; on expiry a code goes to the status word and the CTA winds down.
 #include <type_traits>
 
@@ -27,7 +28,6 @@ namespace gi {
 namespace atc {
 
 constexpr int kRows = 128;        // query rows per CTA
-constexpr int kKeys = 128;        // keys per tile
 constexpr int kThreads = 192;
 constexpr int kStages = 2;
 constexpr unsigned long long kWaitCycles = 4000000000ull;
@@ -143,28 +143,28 @@ __device__ __forceinline__ uint64_t desc_mn_major_blocks(uint32_t addr, uint32_t
     return d;
 }
 
-template <int HD>
+template <int HD, int KEYS>
 struct Cfg {
     static constexpr int kBlocks = HD / 64;                        // 64-wide blocks of the head dimension
     static constexpr int kQBytes = kRows * HD * 2;
-    static constexpr int kTileBytes = kKeys * HD * 2;              // one K or V tile
-    static constexpr int kPBytes = kRows * kKeys * 2;
+    static constexpr int kTileBytes = KEYS * HD * 2;               // one K or V tile
+    static constexpr int kPBytes = kRows * KEYS * 2;
     static constexpr int kSmemBytes = kQBytes + kStages * 2 * kTileBytes + kPBytes + 256;   // two CTAs fit in an SM's 228 KB
-    static constexpr int kTmemCols = 256;                          // S: 128 columns, O: HD columns
+    static constexpr int kTmemCols = (KEYS + HD <= 128) ? 128 : 256;     // S: KEYS columns, O: HD columns (a power of two)
     // D f32, A and B bf16, M = 128
-    static constexpr uint32_t kIdescS = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kKeys >> 3) << 17) | (8u << 24);
+    static constexpr uint32_t kIdescS = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(KEYS >> 3) << 17) | (8u << 24);
     static constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) /* B is MN-major */ |
                                          (static_cast<uint32_t>(HD >> 3) << 17) | (8u << 24);
 };
 
-template <int HD>
+template <int HD, int KEYS>
 __global__ void __launch_bounds__(kThreads, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ work, const int* __restrict__ positions,
                             const int* __restrict__ block_tables, int table_stride, int H, int Hkv, int page_size,
                             float scale_log2, int window, int* status) {
-    using C = Cfg<HD>;
+    using C = Cfg<HD, KEYS>;
     extern __shared__ __align__(1024) uint8_t smem[];
     if (smem_u32(smem) & 1023u) {                                  // the swizzled tiles need 1024-byte alignment
         if (threadIdx.x == 0) atomicCAS(status, 0, 12);
@@ -199,7 +199,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + kKeys;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + KEYS;
     pdl_prologue();
 
     const int t0 = work[blockIdx.y * 3], n_tok = work[blockIdx.y * 3 + 1], req = work[blockIdx.y * 3 + 2];
@@ -207,7 +207,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int pos_first = positions[t0], pos_last = pos_first + n_tok - 1;
     const int lo_first = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
     const int lo_last = (window > 0 && pos_last - window + 1 > 0) ? pos_last - window + 1 : 0;
-    const int first_tile = lo_first / kKeys, last_tile = pos_last / kKeys;
+    const int first_tile = lo_first / KEYS, last_tile = pos_last / KEYS;
     const int n_tiles = last_tile - first_tile + 1;
 
     if (warp == 0) {
@@ -216,12 +216,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         // per tile, started before the wait for the free stage, and each lane requests its own box: one
         // thread issuing all of a tile's copies in turn was late for the MMAs.
         const int* table = block_tables + static_cast<size_t>(req) * table_stride;
-        const int box_rows = page_size < kKeys ? page_size : kKeys;
-        const int boxes = kKeys / box_rows;                       // at most 16 (pages of 8)
+        const int box_rows = page_size < KEYS ? page_size : KEYS;
+        const int boxes = KEYS / box_rows;                       // at most 16 (pages of 8)
         // one tile of keys or of values: false when a wait gave up
         auto load_tile = [&](int i, bool values) -> bool {
             const int s = i % kStages;
-            const int key0 = (first_tile + i) * kKeys;
+            const int key0 = (first_tile + i) * KEYS;
             const int kb_lane = key0 + lane * box_rows;
             const bool lane_valid = lane < boxes && kb_lane <= pos_last && kb_lane + box_rows - 1 >= lo_first;
             const int page_lane = lane_valid ? table[kb_lane / page_size] : 0;
@@ -244,7 +244,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 const int row = (page_lane * Hkv + g) * page_size + kb_lane % page_size;
 #pragma unroll
                 for (int h = 0; h < C::kBlocks; ++h) {
-                    const uint32_t off = static_cast<uint32_t>(h * (kKeys * 128) + lane * box_rows * 128);
+                    const uint32_t off = static_cast<uint32_t>(h * (KEYS * 128) + lane * box_rows * 128);
                     tma_load_2d(tile + off, values ? &map_v : &map_k, h * 64, row, bar);
                 }
             }
@@ -273,7 +273,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
                 for (int kb = 0; kb < C::kBlocks; ++kb) {
                     const uint64_t dq = desc_k_major(smem_u32(q_smem) + kb * (kRows * 128));
-                    const uint64_t dk = desc_k_major(k_tile + kb * (kKeys * 128));
+                    const uint64_t dk = desc_k_major(k_tile + kb * (KEYS * 128));
 #pragma unroll
                     for (int k = 0; k < 4; ++k) umma(tmem_s, dq + 2 * k, dk + 2 * k, C::kIdescS, (kb > 0 || k > 0) ? 1u : 0u);
                 }
@@ -294,13 +294,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 tc_fence_after();
                 const uint32_t v_tile = smem_u32(kv_smem + s * 2 * C::kTileBytes) + C::kTileBytes;
 #pragma unroll
-                for (int kb = 0; kb < kKeys / 64; ++kb) {
+                for (int kb = 0; kb < KEYS / 64; ++kb) {
                     const uint64_t dp = desc_k_major(smem_u32(p_smem) + kb * (kRows * 128));
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         const int kk = kb * 4 + k;                                  // 16 keys per step
-                        // all HD columns of O in one MMA: the 64-wide blocks of V lie kKeys * 128 bytes apart
-                        const uint64_t dv = desc_mn_major_blocks(v_tile + kk * (16 * 128), kKeys * 128);
+                        // all HD columns of O in one MMA: the 64-wide blocks of V lie KEYS * 128 bytes apart
+                        const uint64_t dv = desc_mn_major_blocks(v_tile + kk * (16 * 128), KEYS * 128);
                         umma(tmem_o, dp + 2 * k, dv, C::kIdescPV, (i > 0 || kk > 0) ? 1u : 0u);
                     }
                 }
@@ -349,10 +349,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             tmem_ld32(tmem_s + lane_addr, buf[0]);
             tmem_ld_wait();
 #pragma unroll
-            for (int c = 0; c < kKeys / 32; ++c) {
-                if (c + 1 < kKeys / 32) tmem_ld32(tmem_s + lane_addr + (c + 1) * 32, buf[(c + 1) & 1]);
+            for (int c = 0; c < KEYS / 32; ++c) {
+                if (c + 1 < KEYS / 32) tmem_ld32(tmem_s + lane_addr + (c + 1) * 32, buf[(c + 1) & 1]);
                 const uint32_t* sv = buf[c & 1];
-                if (c + 1 == kKeys / 32) {
+                if (c + 1 == KEYS / 32) {
                     // All scores of the tile are in registers. If this pass is the tile's last one (the
                     // reference maximum stays: known once the last 32 scores are looked at, before their
                     // weights are made), the tensor cores may write the next tile's scores over them.
@@ -401,7 +401,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                     *reinterpret_cast<uint4*>(p_smem + (c >> 1) * (kRows * 128) + r * 128 + ((chunk ^ (r & 7)) << 4)) =
                         make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
                 }
-                if (c + 1 < kKeys / 32) tmem_ld_wait();
+                if (c + 1 < KEYS / 32) tmem_ld_wait();
             }
         };
         auto tile_pass_any = [&](int key0, bool edge, float m_use, float& mx, float& sum, int p_free_parity, bool last_pass) {
@@ -409,10 +409,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             else tile_pass(key0, std::false_type{}, m_use, mx, sum, p_free_parity, last_pass);
         };
         for (int i = 0; i < n_tiles; ++i) {
-            const int key0 = (first_tile + i) * kKeys;
+            const int key0 = (first_tile + i) * KEYS;
             if (!mbar_wait(smem_u32(&bars[kSFull]), i & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const bool edge = key0 < lo_last || key0 + kKeys - 1 > pos_first;      // some row masks some key of this tile
+            const bool edge = key0 < lo_last || key0 + KEYS - 1 > pos_first;      // some row masks some key of this tile
             float mx = -INFINITY, sum = 0.f;
             tile_pass_any(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum, i > 0 ? ((i - 1) & 1) : -1, false);
             if (!ok) break;
@@ -440,17 +440,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 tile_pass_any(key0, edge, (m_ref == -INFINITY) ? 0.f : m_ref, mx, sum, -1, true);
             }
             l += sum;
-            if (key0 < lo_first || key0 + kKeys - 1 > pos_last) {
+            if (key0 < lo_first || key0 + KEYS - 1 > pos_last) {
                 // value rows outside every query's range were not fetched or never written; they meet
                 // weights of exactly 0 in the MMA and must be finite: row r of the tile is this thread's
                 // (after the tile has arrived: the copy must not land on top of the zeros)
                 if (!mbar_wait(smem_u32(&bars[kVFull + i % kStages]), (i / kStages) & 1, abort_flag)) { ok = false; break; }
                 const int key = key0 + r;
-                if (key < lo_first || key > pos_last) {
+                if (r < KEYS && (key < lo_first || key > pos_last)) {
                     uint8_t* v_tile = kv_smem + (i % kStages) * 2 * C::kTileBytes + C::kTileBytes;
 #pragma unroll
                     for (int c = 0; c < HD / 8; ++c)
-                        *reinterpret_cast<uint4*>(v_tile + (c >> 3) * (kKeys * 128) + r * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(v_tile + (c >> 3) * (KEYS * 128) + r * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -493,18 +493,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
 }
 
-template <int HD>
+template <int HD, int KEYS>
 static int launch(const void* q, const void* kc, const void* vc, void* out, const int* work, int n_work,
                   const int* positions, const int* tables, int table_stride, int H, int Hkv, int page_size, float scale,
                   int window, long long n_pages, int* status, cudaStream_t st) {
-    using C = Cfg<HD>;
+    using C = Cfg<HD, KEYS>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, KEYS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
         if (e != cudaSuccess) { set_error("attention_prefill_tc: %s", cudaGetErrorString(e)); return 1; }
         configured = true;
     }
-    const int box_rows = page_size < kKeys ? page_size : kKeys;
+    const int box_rows = page_size < KEYS ? page_size : KEYS;
     CUtensorMap mk, mv;
     const unsigned long long rows_total = static_cast<unsigned long long>(n_pages) * Hkv * page_size;
     if (make_tensor_map_2d(&mk, kc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_total, HD, HD, box_rows, 64,
@@ -512,7 +512,7 @@ static int launch(const void* q, const void* kc, const void* vc, void* out, cons
     if (make_tensor_map_2d(&mv, vc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_total, HD, HD, box_rows, 64,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "attention_prefill_tc")) return 1;
     dim3 grid(Hkv, n_work);
-    launch_kernel((attention_prefill_tc_kernel<HD>), dim3(grid), dim3(kThreads), C::kSmemBytes, st, mk, mv,
+    launch_kernel((attention_prefill_tc_kernel<HD, KEYS>), dim3(grid), dim3(kThreads), C::kSmemBytes, st, mk, mv,
                   static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), work, positions, tables,
                   table_stride, H, Hkv, page_size, scale * kLog2e, window, status);
     return check_launch("attention_prefill_tc");
@@ -541,11 +541,16 @@ static int gi_attention_prefill_tc_impl(const void* q, const void* k_cache, cons
     GI_REQUIRE(status != nullptr, "attention_prefill_tc: a status word is required");
     GI_REQUIRE(n_work <= 65535, "attention_prefill_tc: %d work items exceed the grid limit 65535", n_work);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (hd == 64)
-        return atc::launch<64>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv,
-                               page_size, scale, window, n_pages, static_cast<int*>(status), st);
-    return atc::launch<128>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv,
-                            page_size, scale, window, n_pages, static_cast<int*>(status), st);
+#define GI_ATC_LAUNCH(HD_, KEYS_)                                                                                          \
+    atc::launch<HD_, KEYS_>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv, page_size, \
+                            scale, window, n_pages, static_cast<int*>(status), st)
+    // Keys per tile: 128 at head size 64; 64 at head size 128, where a CTA with 128-key tiles needs 192 KB of shared memory
+    // and has an SM to itself, while two CTAs with 64-key tiles (112 KB each) overlap one's softmax with the other's
+    // MMAs as at head size 64: 642 against 511 TFLOP/s at 8,192 tokens, 374 against 338 at 2,048 (24:8 heads).
+    // (64-key tiles at head size 64, three CTAs to an SM: slower, 531 against 558 TFLOP/s.)
+    if (hd == 64) return GI_ATC_LAUNCH(64, 128);
+    return GI_ATC_LAUNCH(128, 64);
+#undef GI_ATC_LAUNCH
 }
 
 // The exported names: each runs its implementation above and, while a launch program is recorded, leaves a copy of
