@@ -477,6 +477,36 @@ def test_gemm_persistent_many_tiles(M, N, K_, block_q):
     assert K().gemm_tc_status(torch.device(DEV)) == 0
 
 
+@pytest.mark.parametrize("paired", [True, False])
+@pytest.mark.parametrize("M,N,K_,splits", [(129, 256, 64, 1), (257, 528, 200, 1), (385, 272, 136, 1), (640, 1296, 328, 1),
+                                           (129, 256, 1032, 3), (513, 300, 2056, 4)])
+def test_gemm_on_pairs_of_ctas_and_on_single_ones(M, N, K_, splits, paired, monkeypatch):
+    """The many-token product on pairs of CTAs (cta_group::2: 256-row tiles of tokens, each CTA fetching half of the
+    weights' tile) and on single CTAs: token counts one past a multiple of 128 and of 256 (a pair whose second CTA has
+    a single row, or none), widths that are no multiple of the tile, K cut into ranges; store, add and SwiGLU epilogues."""
+    monkeypatch.setattr(K(), "PAIRED_PRODUCTS", paired)
+    g = torch.Generator().manual_seed(29)
+    a = torch.randn(M, K_, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(N, K_, generator=g).to(torch.bfloat16).to(DEV)
+    want = a.float().cpu().double() @ w.float().cpu().double().T
+    guard = torch.full((M + 2, N), -1024.0, device=DEV)
+    out = guard[1:M + 1]
+    out.fill_(float("nan"))
+    K().gemm_tc(a, w, out, plan=(False, 256, splits))
+    close(out, want, "float32", "store", f32_tol=2e-6 * max(1, K_ / 64))
+    assert float(guard[0].min()) == -1024.0 == float(guard[-1].max()), "wrote outside the output"
+    base = torch.randn(M, N, generator=g).to(DEV)
+    acc = base.clone()
+    K().gemm_tc(a, w, acc, accumulate=True, plan=(False, 256, splits))
+    close(acc, want + base.cpu().double(), "float32", "add", f32_tol=2e-6 * max(1, K_ / 64))
+    if splits == 1 and N % 16 == 0:
+        I = N // 2
+        h = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+        K().gemm_swiglu(a, w, h)
+        close(h, pm.plain_swiglu(want[:, :I].float(), want[:, I:].float()), "bfloat16", "swiglu", bf16_tol=1e-2)
+    assert K().gemm_tc_status(torch.device(DEV)) == 0
+
+
 @pytest.mark.parametrize("M,N,K_,block_q,splits", [(512, 2048, 2048, 256, 4), (300, 520, 1032, 256, 3), (130, 256, 520, 256, 2),
                                                    (256, 2048, 8192, 256, 8), (517, 384, 1600, 128, 5), (200, 260, 136, 256, 8)])
 def test_gemm_persistent_split_over_k(M, N, K_, block_q, splits):
