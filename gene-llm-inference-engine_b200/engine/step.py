@@ -109,6 +109,8 @@ class StepContext:
         if program is None:
             with kernels.record() as rec:
                 launch()
+            if len(eng._programs) >= eng.max_programs:          # a long-running server meets many shapes: the oldest goes
+                eng._programs.pop(next(iter(eng._programs)))
             eng._programs[full] = rec.program
         else:
             program.run()
@@ -233,6 +235,9 @@ class StepEngine:
         self.use_programs = True
         self._programs: Dict[Tuple, object] = {}
         self.program_runs = 0
+        # both caches are bounded: a server that runs for days meets ever new shapes (the oldest entry is dropped)
+        self.max_programs = 4096
+        self.max_graphs = 512
         # a listener for intermediate activations: tap(tag, layer, tensor, ctx); steps run outside graphs while it is set
         self.tap = None
         # the kernels' status word (a bounded wait that gave up) follows every step to pinned memory
@@ -482,6 +487,8 @@ class StepEngine:
                 captured = self.model.forward(ctx)
             n_kernels = kernels.launch_count() - before
             kernels.count_launches(-n_kernels)     # captured, not launched
+            if len(self._graphs) >= self.max_graphs:           # the oldest shape's graph goes
+                self._graphs.pop(next(iter(self._graphs)))
             self._graphs[key] = (graph, captured, n_kernels)
             return out
         graph, captured, n_kernels = entry

@@ -127,6 +127,24 @@ def test_live_set_grows_and_shrinks_under_graphs(dtype, grow_on_demand):
     tt.compare(got, _plain_rows(case, dtype, reqs, _wanted(steps)), gf.tolerance(dtype, case), f"grow and shrink {dtype}")
 
 
+def test_bounded_caches_of_graphs_and_launch_programs():
+    """With room for two graphs and three launch programs only, old entries are dropped and made again: the
+    logits stay what they are with room for all."""
+    case, dtype = "c", "bfloat16"
+    reqs = gf.requests(case)
+    steps = tt.trace_mixed(reqs, seed=7) + []
+    roomy = gf.make_engine(case, dtype, n_pages=tt.max_tokens_of(steps, reqs) // 16)
+    want = tt.run_in_process(roomy, steps)
+    tight = gf.make_engine(case, dtype, n_pages=tt.max_tokens_of(steps, reqs) // 16)
+    tight.max_graphs, tight.max_programs = 2, 3
+    got = tt.run_in_process(tight, steps)
+    assert len(tight._graphs) <= 2 and len(tight._programs) <= 3
+    assert len(roomy._programs) > 3, "the trace was meant to meet more shapes than the tight engine keeps"
+    for key, row in want.items():
+        assert np.array_equal(row, got[key]), f"{key}: dropping and re-making a graph or a program changed the logits"
+    _finish(tight, dtype)
+
+
 # ------------------------------------------------------------------ long portions on a cache that is not empty
 LONG_CUTS = {
     "c": [[1, 511], [17, 495], [300, 212]],
