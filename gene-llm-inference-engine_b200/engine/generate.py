@@ -80,6 +80,10 @@ class Engine:
     def result(self, request_id: int) -> RequestResult:
         return self.scheduler.result(request_id)
 
+    def forget(self, request_id: int) -> None:
+        """Drops the kept tokens and result of a finished request (``generate`` does so for its own)."""
+        self.scheduler.forget(request_id)
+
     @property
     def stats(self) -> SchedulerStats:
         return self.scheduler.stats
@@ -110,4 +114,5 @@ class Engine:
             if r.error:
                 raise RuntimeError(f"request {i}: {r.error}")
             out.append(list(r.generated_tokens))
+            self.forget(i)
         return out

@@ -156,7 +156,19 @@ class Scheduler:
         return job.id
 
     def result(self, jid: int) -> RequestResult:
+        if not (0 <= jid < len(self.jobs)) or self.jobs[jid] is None:
+            raise KeyError(f"request {jid} is unknown or was forgotten")
         return self.jobs[jid].result
+
+    def forget(self, jid: int) -> None:
+        """Drops what is kept of a finished request (its tokens and result), so that a long-running
+        engine does not grow with every request it has served; ids are not handed out again."""
+        job = self.jobs[jid] if 0 <= jid < len(self.jobs) else None
+        if job is None:
+            raise KeyError(f"request {jid} is unknown or was forgotten")
+        if not job.result.finished:
+            raise RuntimeError(f"request {jid} has not finished")
+        self.jobs[jid] = None
 
     def idle(self) -> bool:
         return not self.waiting and not self.running and self._ahead is None

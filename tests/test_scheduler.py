@@ -221,3 +221,22 @@ def test_sampled_ids_are_refused_when_a_kernel_reported_a_failed_wait():
     with pytest.raises(KernelError, match="0x21"):
         PendingSample(ids, 3, Done(), status, lambda: cleared.append(True)).result()
     assert cleared == [True] and int(status[0]) == 0
+
+
+def test_finished_requests_can_be_forgotten():
+    backend = fb.FakeBackend(16, 4, 64, 50)
+    s = Scheduler(backend, lambda l, p, u: [fb.pick_token(h, q, x, 50) for h, q, x in zip(l, p, u)], SchedulerConfig(2, 16, 0, False))
+    a = s.submit(GenerationRequest([1, 2, 3], 6, SamplingParams(0.0)))
+    with pytest.raises(RuntimeError):
+        s.forget(a)                                   # still waiting
+    s.run_until_idle()
+    assert len(s.result(a).generated_tokens) == 4
+    s.forget(a)
+    with pytest.raises(KeyError):
+        s.result(a)
+    with pytest.raises(KeyError):
+        s.forget(a)
+    b = s.submit(GenerationRequest([4], 3, SamplingParams(0.0)))
+    assert b == a + 1, "ids are not handed out again"
+    s.run_until_idle()
+    assert s.result(b).finished
