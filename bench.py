@@ -2,14 +2,25 @@
 """Decode and prefill throughput of the engine at the Llama-3.2-1B shape with random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 1b|3b|8b] [--layers L]
-    python bench.py --scenario mixed|prefix [--shape ...]      (continuous batching / shared prefixes, see run_scenario)
+    python bench.py --scenario mixed|prefix [--shape ...] [--dtype bfloat16|float32]
+                                        (continuous batching / shared prefixes through the scheduler, see run_scenario)
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 and context 8192, timed on
 the device over exactly K decode steps (one step = one token for every request of the batch);
 ``e2e`` is the same through the Python entry point (``Engine.step``: token ids from the host in,
-sampled ids back to the host, every step). ``prefill`` is one 2,048-token prompt in one step;
-``roofline`` relates the decode step's bytes (every weight once plus the cache of the live
-requests) to the measured copy bandwidth; ``points`` holds decode at batch 1 and 64.
+sampled ids back to the host, every step). ``prefill`` is one 2,048-token prompt in one step (its
+``frac`` is of the cuBLAS burst figure, ``frac_of_sustained`` of the sustained one); ``roofline``
+relates the decode step's bytes (every weight once plus the cache of the live requests) to the
+measured copy bandwidth, and ``rooflines`` gives the same fraction for every decode point;
+``points`` holds decode at batch 1 and 64, at context 128, the prefill in four portions, and
+``short_requests_b*``: requests of 16 prompt + 64 generated tokens through ``Engine.generate``.
+
+``--impl reference`` runs the unmodified reference: its own ``gi_serve_bench`` with its CUDA
+backend, built with its CMake files into baseline/_ref/build when it is not there yet, on the same
+random model folder, at 8 concurrent requests of 16 prompt + 64 generated tokens (the workload that
+finishes; the line says ``same_config: false`` and names ``points.short_requests_b8`` as the figure
+to compare with). When it cannot be built or gives no result, the line says ``unavailable`` and why.
+
 This engine runs on one GPU: for --gpus > 1 it prints one line saying so and exits with 2.
 """
 import argparse
