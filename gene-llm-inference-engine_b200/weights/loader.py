@@ -1,4 +1,5 @@
-"""Loading a model folder: config.json through the registry, model.safetensors by tensor name.
+"""Loading a model folder: config.json through the registry, model.safetensors (or the files that
+model.safetensors.index.json names) by tensor name.
 
 Tensors keep the precision they are stored in: bfloat16 stays bfloat16 and 32-bit floats stay
 32-bit; float16 is widened to 32-bit (exact); integer tables become int32. One ``WeightsError``
@@ -14,7 +15,7 @@ import torch
 
 from ..config import ConfigError, parse_config
 from .plan import WeightPlan
-from .safetensors_io import SafetensorsError, SafetensorsFile
+from .safetensors_io import SafetensorsError, SafetensorsFile, ShardedSafetensors
 
 _FLOATS = {"F32", "F16", "BF16"}
 _INTS = {"I64", "I32", "I16", "I8", "U8"}
@@ -51,7 +52,7 @@ def read_config(model_dir: str):
 
 def read_tensors(path: str, plan: WeightPlan) -> Dict[str, torch.Tensor]:
     """Reads every tensor the plan names; raises one WeightsError for all mismatches."""
-    st = SafetensorsFile(path)
+    st = ShardedSafetensors(path) if path.endswith(".index.json") else SafetensorsFile(path)
     try:
         missing, wrong = [], []
         wanted = {r.name for r in plan.rules}
@@ -87,9 +88,9 @@ def load_model_folder(model_dir: str) -> Tuple[object, object, Dict[str, torch.T
     arch, cfg, _ = read_config(model_dir)
     weights_path = os.path.join(model_dir, "model.safetensors")
     if not os.path.isfile(weights_path):
-        if os.path.isfile(os.path.join(model_dir, "model.safetensors.index.json")):
-            raise SafetensorsError("sharded checkpoints (model.safetensors.index.json) are not supported")
-        raise SafetensorsError(f"no model.safetensors in {model_dir}")
+        weights_path = os.path.join(model_dir, "model.safetensors.index.json")     # a checkpoint in several files
+        if not os.path.isfile(weights_path):
+            raise SafetensorsError(f"no model.safetensors (nor model.safetensors.index.json) in {model_dir}")
     plan = arch.weight_plan(cfg)
     tensors = read_tensors(weights_path, plan)
     return arch, cfg, plan.assemble(tensors)

@@ -128,6 +128,72 @@ class SafetensorsFile:
         self.close()
 
 
+class ShardedSafetensors:
+    """A checkpoint in several safetensors files named by ``model.safetensors.index.json``
+    (``{"weight_map": {tensor name: file name}}``): read by tensor name like a single file. The
+    reference refuses such folders (src/loader/hf_checkpoint.cpp:146-151); the larger published
+    checkpoints of this architecture come in this form, so they are read here. Every file the index
+    names must exist and hold the tensors the index says it holds; tensors that a file holds but the
+    index does not name are reported like any other unexpected tensor."""
+
+    def __init__(self, index_path: str):
+        self.path = index_path
+        folder = os.path.dirname(os.path.abspath(index_path))
+        try:
+            with open(index_path, "r", encoding="utf-8") as f:
+                index = json.load(f)
+        except OSError as e:
+            raise SafetensorsError(f"safetensors: cannot open {index_path}: {e}") from None
+        except (UnicodeDecodeError, json.JSONDecodeError) as e:
+            raise SafetensorsError(f"safetensors: {index_path}: invalid JSON: {e}") from None
+        weight_map = index.get("weight_map") if isinstance(index, dict) else None
+        if not isinstance(weight_map, dict) or not weight_map or not all(
+                isinstance(k, str) and isinstance(v, str) for k, v in weight_map.items()):
+            raise SafetensorsError(f"safetensors: {index_path}: no \"weight_map\" from tensor names to file names")
+        self._files: Dict[str, SafetensorsFile] = {}
+        self.entries: Dict[str, TensorEntry] = {}
+        self._owner: Dict[str, SafetensorsFile] = {}
+        try:
+            for file_name in sorted(set(weight_map.values())):
+                if os.path.basename(file_name) != file_name:
+                    raise SafetensorsError(f"safetensors: {index_path}: file name '{file_name}' leaves the model folder")
+                self._files[file_name] = SafetensorsFile(os.path.join(folder, file_name))
+            for name, file_name in weight_map.items():
+                shard = self._files[file_name]
+                if name not in shard.entries:
+                    raise SafetensorsError(f"safetensors: {index_path}: tensor '{name}' is not in {file_name}, where the index puts it")
+                self.entries[name] = shard.entries[name]
+                self._owner[name] = shard
+            for file_name, shard in self._files.items():      # tensors the index does not know: reported by the loader
+                for name, entry in shard.entries.items():
+                    if name not in self.entries:
+                        self.entries[name] = entry
+                        self._owner[name] = shard
+        except SafetensorsError:
+            self.close()
+            raise
+
+    def names(self) -> List[str]:
+        return list(self.entries)
+
+    def __contains__(self, name: str) -> bool:
+        return name in self.entries
+
+    def tensor(self, name: str) -> torch.Tensor:
+        return self._owner[name].tensor(name)
+
+    def close(self) -> None:
+        for shard in self._files.values():
+            shard.close()
+        self._files = {}
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
 def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]],
                       metadata: Optional[Dict[str, str]] = None) -> None:
     """Writes tensors in the given order (header padded with spaces to 8 bytes)."""

@@ -161,11 +161,56 @@ def test_broken_files_and_folders(tmp_path):
     with pytest.raises(SafetensorsError, match="no model.safetensors"):
         load_model_folder(d)
     open(os.path.join(d, "model.safetensors.index.json"), "w").write("{}")
-    with pytest.raises(SafetensorsError, match="sharded"):
+    with pytest.raises(SafetensorsError, match="weight_map"):
         load_model_folder(d)
+    os.remove(os.path.join(d, "model.safetensors.index.json"))
     os.remove(os.path.join(d, "config.json"))
     with pytest.raises(ConfigError, match="no config.json"):
         load_model_folder(d)
     open(os.path.join(d, "config.json"), "w").write("{not json")
     with pytest.raises(ConfigError, match="config.json"):
         load_model_folder(d)
+
+
+def test_checkpoint_in_several_files(tmp_path):
+    """model.safetensors.index.json names the file of every tensor: the folder loads like the single
+    file it was cut from; a file that is missing, a tensor that is not where the index puts it and
+    a tensor nobody asked for are reported."""
+    from geneinfer_b200.weights import write_safetensors
+    single = tc.make_model_dir(tc.TINY_B, tc.WEIGHTS_B, str(tmp_path / "single"))
+    want = load_model_folder(single)[2]
+    st = SafetensorsFile(os.path.join(single, "model.safetensors"))
+    names = st.names()
+    d = tmp_path / "sharded"
+    d.mkdir()
+    (d / "config.json").write_text(open(os.path.join(single, "config.json")).read())
+    files = ["model-00001-of-00003.safetensors", "model-00002-of-00003.safetensors", "model-00003-of-00003.safetensors"]
+    weight_map = {}
+    for k, f in enumerate(files):
+        mine = names[k::3]
+        write_safetensors(str(d / f), [(n, st.tensor(n)) for n in mine])
+        weight_map.update({n: f for n in mine})
+    index = d / "model.safetensors.index.json"
+    index.write_text(json.dumps({"metadata": {"total_size": 1}, "weight_map": weight_map}))
+    got = load_model_folder(str(d))[2]
+    assert set(got) == set(want) and all(torch.equal(got[k], want[k]) and got[k].dtype == want[k].dtype for k in want)
+    # a tensor that the index puts into the wrong file
+    moved = dict(weight_map)
+    moved[names[0]] = files[1]
+    index.write_text(json.dumps({"weight_map": moved}))
+    with pytest.raises(SafetensorsError, match="is not in model-00002"):
+        load_model_folder(str(d))
+    # a tensor that the index leaves out is missing for the configuration; one that a file holds beyond the plan is unexpected
+    index.write_text(json.dumps({"weight_map": {n: f for n, f in weight_map.items() if n != names[3]}}))
+    assert load_model_folder(str(d))[2].keys() == want.keys()        # still found: the file holds it
+    write_safetensors(str(d / files[2]), [(n, st.tensor(n)) for n in names[2::3] if n != names[2]] + [("stray.weight", torch.zeros(3))])
+    index.write_text(json.dumps({"weight_map": {n: f for n, f in weight_map.items() if n != names[2]}}))
+    with pytest.raises(WeightsError) as e:
+        load_model_folder(str(d))
+    assert e.value.missing == [names[2]] and e.value.unexpected == ["stray.weight"]
+    # a file of the index that is not there
+    os.remove(d / files[0])
+    index.write_text(json.dumps({"weight_map": weight_map}))
+    with pytest.raises(SafetensorsError, match="cannot open"):
+        load_model_folder(str(d))
+    st.close()
