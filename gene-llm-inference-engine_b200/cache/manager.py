@@ -252,6 +252,33 @@ class CacheManager:
                 rc.n_pages[g] -= 1
         rc.reserved = rc.length
 
+    def truncate(self, rc: RequestCache, length: int) -> None:
+        """Rewinds a request to its first ``length`` positions (the reference's Sequence::truncate,
+        src/model/kv_cache.cpp:96-104): pages wholly beyond them are given back, the rows of the last
+        kept page beyond ``length`` are simply written again later. A window group cannot be rewound
+        past positions whose pages it has already given back; per-request state cannot be rewound at
+        all (it would have to be recomputed)."""
+        if rc.closed or not (0 <= length <= rc.length):
+            raise ValueError(f"truncate: {length} is outside the {rc.length} cached positions of {rc.key!r}")
+        if length == rc.length:
+            return
+        if self.state_layers:
+            raise RuntimeError("truncate: a request with per-request state cannot be rewound")
+        ps = self.page_size
+        for g, group in enumerate(self.groups):
+            w = group.need.window
+            if w and max(0, length - w + 1) // ps < rc.first_live[g]:
+                raise RuntimeError(f"truncate: the window group has given back pages that position {length} would read")
+        keep = (length + ps - 1) // ps
+        for g, group in enumerate(self.groups):
+            while rc.n_pages[g] > keep:
+                i = rc.n_pages[g] - 1
+                if rc.tables[g][i] >= 0:
+                    group.pool.release(int(rc.tables[g][i]))
+                    rc.tables[g][i] = -1
+                rc.n_pages[g] -= 1
+        rc.length = rc.reserved = length
+
     def adopt(self, rc: RequestCache, group: int, pages: Sequence[int]) -> None:
         """Starts an empty request on full pages that already hold its first positions (a prefix
         cache hit). The caller has retained each page for this request."""

@@ -349,6 +349,10 @@ class StepEngine:
         their pages; the first step that writes into a shared page copies it on the device first."""
         return self.cache.fork(self.cache.requests[key], new_key, length)
 
+    def truncate(self, key: Hashable, length: int) -> None:
+        """Rewinds a request to its first ``length`` cached positions; later steps go on from there."""
+        self.cache.truncate(self.cache.requests[key], length)
+
     def length(self, key: Hashable) -> int:
         return self.cache.requests[key].length
 

@@ -210,3 +210,40 @@ def test_fork_shares_pages_until_one_side_writes():
         m.close(rc)
     assert pool.free_count == 8
     m.check_invariants()
+
+
+def test_truncate_gives_back_the_pages_beyond_the_kept_positions():
+    m = CacheManager({0: CacheNeed(1, 16)}, 4, 8, 64, 4)
+    a = m.open("a")
+    m.reserve(a, 14)
+    m.advance(a, 14)                                      # 4 pages
+    pool = m.groups[0].pool
+    b = m.fork(a, "b", 9)                                 # shares pages 0..2
+    m.truncate(a, 6)                                      # keeps pages 0, 1; page 2 stays with b, page 3 is free
+    assert a.length == 6 and a.n_pages[0] == 2 and pool.free_count == 5 and pool.ref_count(int(b.tables[0][2])) == 1
+    copies = m.reserve(a, 3)                              # positions 6..8: page 1 is shared with b and must be copied
+    assert len(copies) == 1 and copies[0].src == int(b.tables[0][1])
+    m.advance(a, 3)
+    m.truncate(a, 9)                                      # nothing to do
+    m.truncate(a, 0)
+    assert a.length == 0 and a.n_pages[0] == 0
+    with pytest.raises(ValueError):
+        m.truncate(a, 1)
+    m.check_invariants()
+    m.close(a)
+    m.close(b)
+    assert pool.free_count == 8
+    w = CacheManager({0: CacheNeed(1, 16, 5)}, 4, 8, 64, 4)            # a window of 5 positions
+    r = w.open("r")
+    w.reserve(r, 18)
+    w.advance(r, 18)                                      # the pages of positions below 12 were given back
+    w.truncate(r, 17)                                     # position 17 reads 13..17: still there
+    assert r.length == 17 and r.n_pages[0] == 5
+    with pytest.raises(RuntimeError, match="given back"):
+        w.truncate(r, 10)                                 # position 10 would read 6..10
+    s = CacheManager({0: CacheNeed(1, 16)}, 4, 8, 64, 4, state_layers=[0])
+    q = s.open("q")
+    s.reserve(q, 5)
+    s.advance(q, 5)
+    with pytest.raises(RuntimeError, match="state"):
+        s.truncate(q, 2)

@@ -247,6 +247,32 @@ def test_forked_request_copies_the_shared_page_before_writing(case, dtype):
     tt.compare(got, plain, gf.tolerance(dtype, case), f"copy-on-write {case} {dtype}")
 
 
+# ------------------------------------------------------------------ rewinding a request
+@pytest.mark.parametrize("case,dtype", [("b", "float32"), ("c", "bfloat16")])
+def test_a_rewound_request_goes_on_like_a_fresh_one(case, dtype):
+    """A request is fed 70 tokens, rewound to 37 (into the middle of a page; the rows beyond stay in the page as
+    they are) and fed other tokens: the logits are those of the new sequence as a whole."""
+    from geneinfer_b200.engine.step import StepEntry
+    vocab = gf.CASES[case][0]["vocab_size"]
+    first = tc.random_tokens(70, vocab, 951)
+    second = first[:37] + tc.random_tokens(40, vocab, 952)
+    engine = gf.make_engine(case, dtype, n_pages=8)
+    engine.open("r")
+    engine.step([StepEntry("r", first, [69])])
+    free = engine.cache.free_pages()
+    engine.truncate("r", 37)
+    assert engine.length("r") == 37 and engine.cache.free_pages() == free + 2      # 5 pages -> 3
+    got = {}
+    logits = engine.step([StepEntry("r", second[37:60], list(range(23)))]).float().cpu().numpy()
+    got.update({("r", 37 + k): logits[k].copy() for k in range(23)})
+    for p in range(60, 77):
+        got[("r", p)] = engine.step([StepEntry("r", [second[p]], [0])]).float().cpu().numpy()[0].copy()
+    engine.close("r")
+    _finish(engine, dtype)
+    plain = _plain_rows(case, dtype, {"r": second}, {"r": list(range(37, 77))})
+    tt.compare(got, plain, gf.tolerance(dtype, case), f"rewound request {case} {dtype}")
+
+
 # ------------------------------------------------------------------ preemption and eviction on the engine
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_engine_preempts_and_evicts_when_pages_run_out(dtype):
