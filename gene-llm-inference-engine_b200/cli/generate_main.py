@@ -159,8 +159,10 @@ def main(argv: Optional[List[str]] = None) -> int:
             first = times.get("first", t1)
             n_gen = len(res.generated_tokens)
             prefill_s, decode_s = first - t0, t1 - first
+            cache_bytes = sum(t.numel() * t.element_size() for t in engine.steps.group_pages)
             sys.stderr.write(
-                f"[stats] load {load_s:.2f} s | prompt {len(prompt)} tokens in {prefill_s * 1e3:.1f} ms "
+                f"[stats] load {load_s:.2f} s | weights {engine.model.weight_bytes() / 2 ** 20:.0f} MiB, "
+                f"cache {cache_bytes / 2 ** 20:.0f} MiB on the device | prompt {len(prompt)} tokens in {prefill_s * 1e3:.1f} ms "
                 f"({len(prompt) / max(prefill_s, 1e-9):.1f} tok/s) | generated {n_gen} tokens, "
                 f"{max(n_gen - 1, 0)} decode steps in {decode_s * 1e3:.1f} ms "
                 f"({max(n_gen - 1, 0) / max(decode_s, 1e-9):.1f} tok/s) | seed {o['seed']} | "
