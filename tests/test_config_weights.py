@@ -214,3 +214,12 @@ def test_checkpoint_in_several_files(tmp_path):
     with pytest.raises(SafetensorsError, match="cannot open"):
         load_model_folder(str(d))
     st.close()
+
+
+def test_bench_says_that_it_runs_on_one_gpu():
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--gpus", "2", "--steps", "2", "--warmup", "1"],
+                       capture_output=True, text=True, timeout=120)
+    assert p.returncode == 2 and len(p.stdout.strip().splitlines()) == 1 and "one GPU" in p.stdout

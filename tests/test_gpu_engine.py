@@ -112,7 +112,9 @@ def test_long_decoding_and_first_tokens(dtype):
 
 @pytest.mark.parametrize("case,dtype,page_size", [("a", "float32", 8), ("a", "float32", 64), ("c", "bfloat16", 8),
                                                   ("c", "bfloat16", 32), ("c", "bfloat16", 64), ("d", "bfloat16", 128),
-                                                  ("b", "bfloat16", 24)])
+                                                  ("b", "bfloat16", 24), ("a", "float32", 1), ("b", "float32", 3),
+                                                  ("b", "float32", 7), ("a", "float32", 1000), ("c", "bfloat16", 3),
+                                                  ("b", "bfloat16", 7), ("d", "bfloat16", 1), ("c", "bfloat16", 1000)])
 def test_other_page_sizes(case, dtype, page_size):
     """Pages smaller than, equal to and larger than the kernels' key tiles (the TMA boxes follow the
     page size), and a page size that TMA boxes cannot tile (24: the cp.async kernels)."""
@@ -122,6 +124,29 @@ def test_other_page_sizes(case, dtype, page_size):
     engine = gf.make_engine(case, dtype, n_pages=max_tokens // page_size, page_size=page_size)
     got = tt.run_in_process(engine, steps)
     tt.compare(got, gf.plain_logits(case, dtype), gf.tolerance(dtype, case), f"page size {page_size}")
+
+
+def test_portions_around_tile_edges_agree_bitwise_with_token_by_token_in_32bit():
+    """Portions of 1, 2, 7, 8, 9, 15, 16, 17, 63, 64, 65 and 149 tokens (the sizes around the kernels' tiles and the
+    pages' edges, tests/verify_device.py:140-153 of the reference) against the same request fed token by token:
+    the same bits in 32-bit."""
+    case = "c"
+    toks = gf.requests(case)["r2"]                          # 512 tokens
+    sizes = [1, 2, 7, 8, 9, 15, 16, 17, 63, 64, 65, 149]
+    assert sum(sizes) <= len(toks)
+    steps, p = [], 0
+    for n in sizes:
+        steps.append({"step": len(steps), "entries": [{"id": "r2", "tokens": toks[p:p + n], "want": list(range(n))}],
+                      "end": ["r2"] if n == sizes[-1] else []})
+        p += n
+    by_portions = _play(case, "float32", steps)
+    single = [{"step": i, "entries": [{"id": "r2", "tokens": [t], "want": [0]}], "end": ["r2"] if i == p - 1 else []}
+              for i, t in enumerate(toks[:p])]
+    one_by_one = _play(case, "float32", single)
+    assert set(by_portions) == set(one_by_one)
+    for key, row in by_portions.items():
+        assert np.array_equal(row, one_by_one[key]), f"{key}: a portion and single tokens differ in 32-bit"
+    tt.compare(by_portions, gf.plain_logits(case, "float32"), gf.tolerance("float32", case), "portions around tile edges")
 
 
 def test_step_refuses_bad_input_and_leaves_state_unchanged():
