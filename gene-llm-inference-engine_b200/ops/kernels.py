@@ -585,6 +585,17 @@ def gemm_rope_store(a: torch.Tensor, w_qkv: torch.Tensor, positions: torch.Tenso
                                                *rope_args, st.status.data_ptr(), _paired(M, 256), _stream()), "gemm_rope_store")
 
 
+def l2_streaming(weights: Optional[bool] = None, keys_values: Optional[bool] = None):
+    """In steps of few tokens the weights of the matrix products and the keys and values of decode attention, which
+    a step reads once, are loaded with the "evict first" L2 policy, so that they do not push out what the step's
+    kernels read again soon. Sets either switch (None leaves it) and returns the old (weights, keys_values)."""
+    old_w = bool(lib().gi_gemm_tc_set_stream_weights(1))
+    lib().gi_gemm_tc_set_stream_weights(int(old_w if weights is None else weights))
+    old_kv = bool(lib().gi_attention_set_stream_kv(1))
+    lib().gi_attention_set_stream_kv(int(old_kv if keys_values is None else keys_values))
+    return old_w, old_kv
+
+
 def status_word(device: torch.device) -> torch.Tensor:
     """The device word [1] (int32) in which a kernel records a bounded wait that gave up (0 = none)."""
     return _tc_state(device).status

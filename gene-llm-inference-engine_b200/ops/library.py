@@ -47,6 +47,8 @@ _SIGNATURES = {
                              c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p, c_void_p],
     "gi_attention_prefill_rows": [c_int, c_int],
     "gi_gemm_tc_set_cluster": [c_int],
+    "gi_gemm_tc_set_stream_weights": [c_int],
+    "gi_attention_set_stream_kv": [c_int],
     "gi_gemm_tc_cluster_capacity": [c_int, c_int, c_int],
     "gi_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                 c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p, c_void_p],

@@ -624,3 +624,30 @@ def test_gemm_rope_store_fused(T, H, Hkv, hd, ps, D, rotated, monkeypatch):
                         w_tiles=w_tiles)
     assert torch.isnan(kc3.float()).all() and torch.isnan(vc3.float()).all()
     assert not torch.isnan(q3.float()).any() and torch.equal(q3, q), "queries must not depend on write_kv"
+
+
+def test_l2_policy_of_streamed_loads_changes_no_result():
+    """Weights of few-token products and keys/values of decode attention are loaded with the evict-first L2 policy:
+    the same bits with the policy and without."""
+    g = torch.Generator().manual_seed(3)
+    a = (torch.randn(8, 1032, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(520, 1032, generator=g) / 32).to(torch.bfloat16).to(DEV)
+    outs, atts = [], []
+    old = K().l2_streaming()
+    try:
+        for on in (True, False):
+            K().l2_streaming(weights=on, keys_values=on)
+            for tiles in (None, K().tile_weight(w)):
+                out = torch.empty(8, 520, dtype=torch.float32, device=DEV)
+                K().gemm_tc(a, w, out, w_tiles=tiles)
+                outs.append(out)
+            got, want = _attention_case("bfloat16", 8, 2, 64, 16, ctx_lens=[100, 700, 1, 300], q_lens=[1, 1, 1, 1], window=None,
+                                        seed=5, fast=True)
+            close(got, want, "bfloat16", "decode attention", bf16_tol=1e-2)
+            atts.append(got)
+    finally:
+        K().l2_streaming(*old)
+    assert K().l2_streaming() == old
+    assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3]) and torch.equal(atts[0], atts[1])
+    exact = a.double().cpu() @ w.double().cpu().T
+    assert (outs[0].double().cpu() - exact).abs().max().item() <= 1e-4 * max(1.0, exact.abs().max().item())
