@@ -234,17 +234,17 @@ struct TcParams {
 };
 
 template <int BLOCK_Q>
-__device__ __forceinline__ void store_row_chunk(const TcParams& p, int row_p, int q0, const float* v) {
+__device__ __forceinline__ void store_row_chunk(const TcParams& p, bool c_bf16, bool accumulate, int row_p, int q0, const float* v) {
     // v[j] belongs to (row_p, q0 + j), j < 16
     if (row_p >= p.rows_p) return;
     const long long base = static_cast<long long>(row_p) * p.stride_p + static_cast<long long>(q0) * p.stride_q;
     const int n = min(16, p.rows_q - q0);
-    if (p.c_bf16) {
+    if (c_bf16) {
         __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.C) + base;
 #pragma unroll
         for (int j = 0; j < 16; ++j)
             if (j < n) c[j * p.stride_q] = __float2bfloat16_rn(v[j]);
-    } else if (p.accumulate) {
+    } else if (accumulate) {
         // all loads first, then all stores: the sixteen read-modify-writes overlap instead of
         // waiting for one another
         float* c = static_cast<float*>(p.C) + base;
@@ -272,10 +272,40 @@ __device__ __forceinline__ void store_row_chunk_old(const TcParams& p, int row_p
         if (j < n) c[j * p.stride_q] = old[j] + v[j];
 }
 
-template <int BLOCK_Q, bool TILED>
+// SPEC 0: every form of the product in one kernel, chosen by TcParams at run time (about 5,000 instructions). The
+// three forms that a decode step of up to 16 tokens runs have kernels of their own in which what TcParams says is
+// compiled in and everything else is left out: a short kernel pays for every instruction it has to fetch, and the
+// L2 cache that would serve the fetch is swept by the weights between two launches (measured on B200: the
+// RMSNorm kernel cut from 19 KB to 6 KB of code made each of its launches 0.5 us shorter inside a decode step).
+enum TcSpecKind : int {
+    kSpecAny = 0,
+    kSpecRopeCluster = 1,    // [q; k; v] with rotation and store, K split over a cluster with partial tiles in a place of their own
+    kSpecAddCluster = 2,     // added into a 32-bit C (O and down products), K split over such a cluster
+    kSpecStoreOne = 3,       // stored to a 32-bit C, K not split ([gate; up], the head)
+};
+template <int SPEC>
+struct TcSpec {
+    static constexpr bool fixed = SPEC != kSpecAny;
+    static constexpr bool rope = SPEC == kSpecRopeCluster;
+    static constexpr int cluster = (SPEC == kSpecRopeCluster || SPEC == kSpecAddCluster) ? 1 : 0;
+    static constexpr bool one_split = SPEC == kSpecStoreOne;
+    static constexpr bool accumulate = SPEC == kSpecAddCluster;
+};
+
+template <int BLOCK_Q, bool TILED, int SPEC = kSpecAny>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const TcParams p) {
     using Cfg = TcConfig<BLOCK_Q, TILED>;
+    using Spec = TcSpec<SPEC>;
+    // what the specialised kernels know at compile time
+    const bool rope_on = Spec::fixed ? Spec::rope : p.rope_on != 0;
+    const int cluster = Spec::fixed ? Spec::cluster : p.cluster;
+    const bool one_split = Spec::fixed ? Spec::one_split : p.splits == 1;
+    const bool accumulate = Spec::fixed ? Spec::accumulate : p.accumulate != 0;
+    const bool c_bf16 = Spec::fixed ? false : p.c_bf16 != 0;
+    const bool prefetch_p = Spec::fixed ? true : p.prefetch_p != 0;
+    const bool stream_p = Spec::fixed ? true : p.stream_p != 0;
+    const int n_splits = (Spec::fixed && Spec::one_split) ? 1 : p.splits;
     constexpr int kKb = Cfg::kKb;
     constexpr int kStages = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -285,7 +315,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     // [2kStages + 1] the other splits' partial tiles have arrived (cluster reduce, split 0),
     // [2kStages + 2] split 0's stages are free to receive them (cluster reduce, the other splits)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 3);
-    float* partials = reinterpret_cast<float*>((Cfg::kStagesReceive && p.cluster == 2) ? smem : smem + kStages * Cfg::kStageBytes + 256);
+    float* partials = reinterpret_cast<float*>((Cfg::kStagesReceive && cluster == 2) ? smem : smem + kStages * Cfg::kStageBytes + 256);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = const_cast<int*>(abort_flag) + 1;
     int* epi_abort = last_flag + 1;
@@ -304,7 +334,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             mbar_init(smem_u32(&bars[kStages + s]), 1);
         }
         mbar_init(smem_u32(&bars[2 * kStages]), 1);
-        mbar_init(smem_u32(&bars[2 * kStages + 1]), p.cluster ? static_cast<uint32_t>(p.splits - 1) * 128u : 1u);
+        mbar_init(smem_u32(&bars[2 * kStages + 1]), cluster ? static_cast<uint32_t>(n_splits - 1) * 128u : 1u);
         mbar_init(smem_u32(&bars[2 * kStages + 2]), 1);
         *abort_flag = 0;
         *last_flag = 0;
@@ -316,7 +346,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (p.cluster) cluster_sync_all();          // split 0's barrier exists before anyone arrives on it
+    if (cluster) cluster_sync_all();          // split 0's barrier exists before anyone arrives on it
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
@@ -325,15 +355,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             // The first stages are free: with prefetch_p their weight tiles are requested before
             // this kernel waits for its predecessors, so the weight stream never pauses between
             // the kernels of a decode step; the activation tiles follow after the wait.
-            const int early = p.prefetch_p ? min(n_kb, kStages) : 0;
+            const int early = prefetch_p ? min(n_kb, kStages) : 0;
             const uint64_t stream_policy = l2_evict_first_policy();
             auto load_p = [&](int i, uint32_t full) {          // stage i of this CTA: blocks kb_begin + i * kKb ..
                 const uint32_t dst = smem_u32(smem + (i % kStages) * Cfg::kStageBytes);
                 if (TILED) {
                     const uint8_t* src = p.p_tiles + (static_cast<size_t>(tile_p) * p.tiles_kb + kb_begin + i * kKb) * Cfg::kBlockBytesP;
-                    if (p.stream_p) bulk_load_hint(dst, src, Cfg::kStageBytesP, full, stream_policy);
+                    if (stream_p) bulk_load_hint(dst, src, Cfg::kStageBytesP, full, stream_policy);
                     else bulk_load(dst, src, Cfg::kStageBytesP, full);
-                } else if (p.stream_p) {
+                } else if (stream_p) {
                     tma_load_2d_hint(dst, &map_p, (kb_begin + i) * kBlockK, tile_p * kBlockP, full, stream_policy);
                 } else {
                     tma_load_2d(dst, &map_p, (kb_begin + i) * kBlockK, tile_p * kBlockP, full);
@@ -414,8 +444,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         const int row_p = tile_p * kBlockP + row_in_tile;
         // A tile of 16 columns that this CTA itself will add into C: the old values are requested
         // now, while the products run, instead of after them.
-        const bool early_old = BLOCK_Q == 16 && p.accumulate && !p.c_bf16 && row_p < p.rows_p &&
-                               (p.splits == 1 || (p.cluster && split == 0));
+        const bool early_old = BLOCK_Q == 16 && accumulate && !c_bf16 && row_p < p.rows_p &&
+                               (one_split || (cluster && split == 0));
         float old_c[16];
         if (early_old) {
             const float* c = static_cast<const float*>(p.C) + static_cast<long long>(row_p) * p.stride_p +
@@ -428,7 +458,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         // tile now, while the products run.
         int tok_pos = 0;
         long long tok_base = -1;
-        if (p.rope_on && row_in_tile < BLOCK_Q) {
+        if (rope_on && row_in_tile < BLOCK_Q) {
             const int tok = tile_q * BLOCK_Q + row_in_tile;
             if (tok < p.rows_q) {
                 tok_pos = p.rope.positions[tok];
@@ -443,12 +473,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         float* xch = reinterpret_cast<float*>(smem);
         bool emitted = false;
         auto emit = [&](int c, const float* v) {          // the final values of columns c * 16 .. of this thread's row
-            if (p.rope_on) {
+            if (rope_on) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) xch[(c * 16 + j) * kBlockP + row_in_tile] = v[j];
                 emitted = true;
             } else {
-                store_row_chunk<BLOCK_Q>(p, row_p, tile_q * BLOCK_Q + c * 16, v);
+                store_row_chunk<BLOCK_Q>(p, c_bf16, accumulate, row_p, tile_q * BLOCK_Q + c * 16, v);
             }
         };
         bool have = n_kb > 0;
@@ -463,7 +493,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const bool aborted = *epi_abort != 0;
         constexpr int kChunks = (BLOCK_Q + 15) / 16;
-        if (p.cluster) {
+        if (cluster) {
             // Splits 1.. hand their partial tile to split 0 (rank 0 of the cluster) and arrive on
             // its barrier, even after giving up, so that split 0 never waits for a CTA that is gone;
             // split 0 waits (bounded) before it leaves, so its memory outlives every write to it.
@@ -472,13 +502,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             // sent even after giving up), and the others wait for that (bounded) before they write and
             // before they leave, so that the arrival never finds their memory gone.
             if (split == 0) {
-                if (Cfg::kStagesReceive && p.cluster == 2 && warp == 2 && lane == 0) {
-                    for (int s = 1; s < p.splits; ++s)
+                if (Cfg::kStagesReceive && cluster == 2 && warp == 2 && lane == 0) {
+                    for (int s = 1; s < n_splits; ++s)
                         cluster_mbar_arrive(cluster_map(smem_u32(&bars[2 * kStages + 2]), static_cast<uint32_t>(s)));
                 }
             }
             if (split != 0) {
-                bool stages_free = !Cfg::kStagesReceive || p.cluster != 2 || mbar_try_wait_cluster(smem_u32(&bars[2 * kStages + 2]), 0);
+                bool stages_free = !Cfg::kStagesReceive || cluster != 2 || mbar_try_wait_cluster(smem_u32(&bars[2 * kStages + 2]), 0);
                 const unsigned long long t0 = clock64();
                 while (!stages_free) {
                     stages_free = mbar_try_wait_cluster(smem_u32(&bars[2 * kStages + 2]), 0);
@@ -518,7 +548,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                         }
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = have ? __uint_as_float(r[j]) : 0.f;
-                        for (int s = 1; s < p.splits; ++s) {
+                        for (int s = 1; s < n_splits; ++s) {
                             const float* part = partials + static_cast<size_t>(s - 1) * BLOCK_Q * kBlockP;
 #pragma unroll
                             for (int j = 0; j < 16; ++j) v[j] += part[(c * 16 + j) * kBlockP + row_in_tile];
@@ -529,7 +559,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 }
             }
         } else if (!aborted) {
-            if (p.splits == 1) {
+            if (one_split) {
 #pragma unroll 1
                 for (int c = 0; c < kChunks; ++c) {
                     uint32_t r[16];
@@ -549,7 +579,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             } else {
                 // partial tile -> workspace [tile][split][q][128 rows]; the last CTA of the tile sums all splits
                 const int tile_id = tile_q * gridDim.x + tile_p;
-                float* ws_tile = p.workspace + static_cast<size_t>(tile_id) * p.splits * BLOCK_Q * kBlockP;
+                float* ws_tile = p.workspace + static_cast<size_t>(tile_id) * n_splits * BLOCK_Q * kBlockP;
                 float* mine = ws_tile + static_cast<size_t>(split) * BLOCK_Q * kBlockP;
 #pragma unroll 1
                 for (int c = 0; c < kChunks; ++c) {
@@ -566,7 +596,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (warp == 2 && lane == 0) {
                     const unsigned arrived = atomicAdd(&p.counters[tile_id], 1u);
-                    *last_flag = (arrived == static_cast<unsigned>(p.splits - 1)) ? 1 : 0;
+                    *last_flag = (arrived == static_cast<unsigned>(n_splits - 1)) ? 1 : 0;
                     if (*last_flag) p.counters[tile_id] = 0;        // ready for the next launch
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -579,18 +609,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                         float v[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                        for (int s0 = 0; s0 < p.splits; s0 += 4) {
+                        for (int s0 = 0; s0 < n_splits; s0 += 4) {
                             float part[4][16];
 #pragma unroll
                             for (int ds = 0; ds < 4; ++ds) {
                                 const float* src = ws_tile + static_cast<size_t>(s0 + ds) * BLOCK_Q * kBlockP;
 #pragma unroll
                                 for (int j = 0; j < 16; ++j)
-                                    part[ds][j] = (s0 + ds < p.splits) ? __ldcg(&src[(c * 16 + j) * kBlockP + row_in_tile]) : 0.f;
+                                    part[ds][j] = (s0 + ds < n_splits) ? __ldcg(&src[(c * 16 + j) * kBlockP + row_in_tile]) : 0.f;
                             }
 #pragma unroll
                             for (int ds = 0; ds < 4; ++ds)
-                                if (s0 + ds < p.splits) {
+                                if (s0 + ds < n_splits) {
 #pragma unroll
                                     for (int j = 0; j < 16; ++j) v[j] += part[ds][j];
                                 }
@@ -600,10 +630,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 }
             }
         }
-        if (p.rope_on) {
+        if (rope_on) {
             const RopeStoreParams& rp = p.rope;
             // behind the finished tile and, in a cluster, behind the partial tiles that other threads may still be reading
-            int* tpos = reinterpret_cast<int*>(xch + ((Cfg::kStagesReceive && p.cluster == 2) ? max(1, p.splits - 1) : 1) * BLOCK_Q * kBlockP);
+            int* tpos = reinterpret_cast<int*>(xch + ((Cfg::kStagesReceive && cluster == 2) ? max(1, n_splits - 1) : 1) * BLOCK_Q * kBlockP);
             long long* tbase = reinterpret_cast<long long*>(tpos + BLOCK_Q);
             if (row_in_tile < BLOCK_Q) { tpos[row_in_tile] = tok_pos; tbase[row_in_tile] = tok_base; }
             asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -1238,22 +1268,18 @@ static int cluster_capacity(int splits) {
     return n;
 }
 
-template <int BLOCK_Q, bool TILED>
-static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, TcParams p, dim3 grid, cudaStream_t st) {
+// Launches the kernel of one form (p.cluster decided): plainly, or as clusters of the splits of a tile.
+template <int BLOCK_Q, bool TILED, int SPEC>
+static int launch_tc_form(const CUtensorMap& mp, const CUtensorMap& mq, const TcParams& p, dim3 grid, cudaStream_t st) {
     using Cfg = TcConfig<BLOCK_Q, TILED>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BLOCK_Q, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemPerBlock);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BLOCK_Q, TILED, SPEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemPerBlock);
         if (e != cudaSuccess) { set_error("gemm_tc: cannot reserve %d bytes of shared memory: %s", kMaxSmemPerBlock, cudaGetErrorString(e)); return 1; }
         configured = true;
     }
-    // all clusters of the launch resident at once, or the workspace path: a second wave of clusters
-    // would cost more than the reduce through global memory
-    const long long tiles = static_cast<long long>(grid.x) * grid.y;
-    p.cluster = (p.splits > 1 && g_cluster_reduce && tiles <= cluster_capacity<BLOCK_Q, TILED>(p.splits)) ? 1 : 0;
-    if (p.cluster && Cfg::smem_bytes(p.splits) > kMaxSmemPerBlock) p.cluster = 2;    // partial tiles in split 0's stages
     if (!p.cluster) {
-        launch_kernel((gemm_tc_kernel<BLOCK_Q, TILED>), dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, mp, mq, p);
+        launch_kernel((gemm_tc_kernel<BLOCK_Q, TILED, SPEC>), dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, mp, mq, p);
         return check_launch("gemm_tc");
     }
     cudaLaunchConfig_t cfg = {};
@@ -1270,9 +1296,30 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, TcParams p, d
     attr[1].val.clusterDim.z = p.splits;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BLOCK_Q, TILED>, mp, mq, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BLOCK_Q, TILED, SPEC>, mp, mq, p);
     if (e != cudaSuccess) { set_error("gemm_tc: cluster launch failed: %s", cudaGetErrorString(e)); return 1; }
     return check_launch("gemm_tc");
+}
+
+static int g_specialised = 1;
+
+template <int BLOCK_Q, bool TILED>
+static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, TcParams p, dim3 grid, cudaStream_t st) {
+    using Cfg = TcConfig<BLOCK_Q, TILED>;
+    // all clusters of the launch resident at once, or the workspace path: a second wave of clusters
+    // would cost more than the reduce through global memory
+    const long long tiles = static_cast<long long>(grid.x) * grid.y;
+    p.cluster = (p.splits > 1 && g_cluster_reduce && tiles <= cluster_capacity<BLOCK_Q, TILED>(p.splits)) ? 1 : 0;
+    if (p.cluster && Cfg::smem_bytes(p.splits) > kMaxSmemPerBlock) p.cluster = 2;    // partial tiles in split 0's stages
+    // the forms of a decode step of up to 16 tokens over tiled weights: kernels with nothing else in them
+    if constexpr (BLOCK_Q == 16 && TILED) {
+        if (g_specialised && p.prefetch_p && p.stream_p && !p.c_bf16) {
+            if (p.rope_on && p.cluster == 1 && !p.accumulate) return launch_tc_form<BLOCK_Q, TILED, kSpecRopeCluster>(mp, mq, p, grid, st);
+            if (!p.rope_on && p.cluster == 1 && p.accumulate) return launch_tc_form<BLOCK_Q, TILED, kSpecAddCluster>(mp, mq, p, grid, st);
+            if (!p.rope_on && p.splits == 1 && !p.accumulate) return launch_tc_form<BLOCK_Q, TILED, kSpecStoreOne>(mp, mq, p, grid, st);
+        }
+    }
+    return launch_tc_form<BLOCK_Q, TILED, kSpecAny>(mp, mq, p, grid, st);
 }
 
 
@@ -1300,6 +1347,14 @@ extern "C" int gi_gemm_tc_set_cluster(int on) {
 extern "C" int gi_gemm_tc_set_stream_weights(int on) {
     const int old = g_stream_weights;
     g_stream_weights = on ? 1 : 0;
+    return old;
+}
+
+// Switches the kernels of single forms (TcSpecKind) on or off (on by default; off: the kernel of every form runs
+// them); returns the old value.
+extern "C" int gi_gemm_tc_set_specialised(int on) {
+    const int old = g_specialised;
+    g_specialised = on ? 1 : 0;
     return old;
 }
 

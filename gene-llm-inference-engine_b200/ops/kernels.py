@@ -596,6 +596,15 @@ def l2_streaming(weights: Optional[bool] = None, keys_values: Optional[bool] = N
     return old_w, old_kv
 
 
+def specialised_products(on: Optional[bool] = None) -> bool:
+    """The forms of the few-token product that a decode step runs (rotating [q; k; v], added into the residual stream,
+    stored unsplit; up to 16 tokens over tiled weights) have kernels of their own with nothing else compiled in;
+    ``on`` False makes the kernel of every form run them too (same results). Returns the old setting."""
+    old = bool(lib().gi_gemm_tc_set_specialised(1))
+    lib().gi_gemm_tc_set_specialised(int(old if on is None else on))
+    return old
+
+
 def status_word(device: torch.device) -> torch.Tensor:
     """The device word [1] (int32) in which a kernel records a bounded wait that gave up (0 = none)."""
     return _tc_state(device).status

@@ -48,6 +48,7 @@ _SIGNATURES = {
     "gi_attention_prefill_rows": [c_int, c_int],
     "gi_gemm_tc_set_cluster": [c_int],
     "gi_gemm_tc_set_stream_weights": [c_int],
+    "gi_gemm_tc_set_specialised": [c_int],
     "gi_attention_set_stream_kv": [c_int],
     "gi_gemm_tc_cluster_capacity": [c_int, c_int, c_int],
     "gi_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,

@@ -651,3 +651,46 @@ def test_l2_policy_of_streamed_loads_changes_no_result():
     assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3]) and torch.equal(atts[0], atts[1])
     exact = a.double().cpu() @ w.double().cpu().T
     assert (outs[0].double().cpu() - exact).abs().max().item() <= 1e-4 * max(1.0, exact.abs().max().item())
+
+
+def test_specialised_forms_of_the_few_token_product_give_the_same_bits():
+    """The three forms a decode step runs (rotating [q; k; v] split over a cluster, added into the residual stream split
+    over a cluster, stored unsplit) in kernels of their own against the kernel that holds every form."""
+    g = torch.Generator().manual_seed(9)
+    T, D, H, Hkv, hd, ps = 8, 2048, 32, 8, 64, 16
+    a = (torch.randn(T, D, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    w_qkv = (torch.randn((H + 2 * Hkv) * hd, D, generator=g) / math.sqrt(D)).to(torch.bfloat16).to(DEV)
+    w_o = (torch.randn(D, D, generator=g) / math.sqrt(D)).to(torch.bfloat16).to(DEV)
+    w_up = (torch.randn(4096, D, generator=g) / math.sqrt(D)).to(torch.bfloat16).to(DEV)
+    tiles = [K().tile_weight(w) for w in (w_qkv, w_o, w_up)]
+    x0 = torch.randn(T, D, generator=g).to(DEV)
+    freq = 1.0 / (10000.0 ** (np.arange(hd // 2, dtype=np.float64) * 2 / hd))
+    ang = np.arange(64, dtype=np.float64)[:, None] * freq[None]
+    cos = torch.from_numpy(np.cos(ang).astype(np.float32)).to(DEV)
+    sin = torch.from_numpy(np.sin(ang).astype(np.float32)).to(DEV)
+    positions = torch.tensor([14, 15, 16, 17, 3, 40, 41, 0], dtype=torch.int32, device=DEV)
+    row_req = torch.tensor([0, 0, 0, 0, 1, 2, 2, 3], dtype=torch.int32, device=DEV)
+    tables = torch.tensor([[5, 2, -1], [7, -1, -1], [1, 0, 3], [8, -1, -1]], dtype=torch.int32, device=DEV)
+    results = []
+    old = K().specialised_products()
+    try:
+        for on in (True, False):
+            K().specialised_products(on)
+            kc, vc = _paged("bfloat16", 10, Hkv, ps, hd)
+            q = torch.full((T, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+            K().gemm_rope_store(a, w_qkv, positions, row_req, tables, cos, sin, False, q, kc, vc, H, Hkv, hd, ps, w_tiles=tiles[0])
+            x = x0.clone()
+            K().gemm_tc(a, w_o, x, accumulate=True, w_tiles=tiles[1])
+            up = torch.full((T, 4096), float("nan"), dtype=torch.float32, device=DEV)
+            K().gemm_tc(a, w_up, up, w_tiles=tiles[2])
+            results.append((q, kc, vc, x, up))
+    finally:
+        K().specialised_products(old)
+    assert K().gemm_tc_status(a.device) == 0
+    for got, want, what in zip(results[0], results[1], ("q", "k pages", "v pages", "residual stream", "stored product")):
+        assert torch.equal(torch.nan_to_num(got.float()), torch.nan_to_num(want.float())) and \
+            torch.equal(torch.isnan(got.float()), torch.isnan(want.float())), what
+    exact = x0.double().cpu() + a.double().cpu() @ w_o.double().cpu().T
+    assert (results[0][3].double().cpu() - exact).abs().max().item() <= 1e-4 * max(1.0, exact.abs().max().item())
+    exact = a.double().cpu() @ w_up.double().cpu().T
+    assert (results[0][4].double().cpu() - exact).abs().max().item() <= 1e-4 * max(1.0, exact.abs().max().item())
