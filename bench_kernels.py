@@ -9,6 +9,9 @@ Cases at the layer sizes of one of bench.py's shapes (random data, sizes larger 
   attention_prefill  one prompt of T tokens, with the mma.sync kernel and with the tcgen05 kernel
   decode_step        R whole decode steps of B requests at context C through the step function
   prefill_step       R whole prefills of T tokens through the step function
+  decode_timeline    one graph-replayed decode step of B requests at context C, seen from inside: the kernels of a library
+                     built with time stamps (it is compiled at the first call) record when their blocks enter, wait, compute
+                     and leave; prints one line per launch of the layers --from-launch .. --to-launch
 Each case prints the time per launch measured with CUDA events. Under a profiler, give --repeat a
 small value and select the kernel by name.
 """
@@ -152,18 +155,55 @@ def step_case(kind, shape_cfg, batch, context, tokens, layers, repeat):
         _time(f"prefill step T={tokens} layers={cfg['num_hidden_layers']}", run, repeat)
 
 
+def timeline_case(shape_cfg, batch, context, layers, first, last):
+    from geneinfer_b200.ops import library
+    library.use_timeline_build()
+    from geneinfer_b200 import Engine
+    from geneinfer_b200.engine.step import StepEntry
+    from geneinfer_b200.ops import kernels, timeline
+    cfg = dict(shape_cfg, num_hidden_layers=layers or shape_cfg["num_hidden_layers"])
+    folder = bench.model_folder(cfg)
+    llm = Engine(folder, dtype="bfloat16", max_seq_len=context, page_size=PAGE, kv_pages=batch * ((context + PAGE - 1) // PAGE),
+                 max_running=batch, step_tokens=max(batch, 16), prefix_cache=False)
+    eng = llm.steps
+    keys = [f"b{i}" for i in range(batch)]
+    bench.fill_cache(eng, keys, context - 12)
+    ids = torch.zeros(batch, dtype=torch.int32, device="cuda:0")
+
+    def run(i):
+        logits = eng.step([StepEntry(k, [17 + i], [0]) for k in keys])
+        kernels.argmax(logits, ids)
+    for i in range(6):                           # the step's graph is captured and replayed a few times
+        run(i)
+    rec = timeline.Recorder(eng.device)
+    run(6)
+    rec.start()
+    run(7)
+    records = rec.records()
+    found = timeline.launches(records)
+    span = records[:, 3].max() / 1000 if len(records) else 0.0
+    print(f"decode step B={batch} context={context} layers={cfg['num_hidden_layers']}: {len(records)} records of {len(found)} "
+          f"launches over {span:.1f} us (the time stamps themselves cost a few per cent)")
+    print(timeline.table(found, first, min(last, len(found))))
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     ap.add_argument("case", choices=["gemm_prefill", "gemm_decode", "attention_decode", "attention_prefill", "decode_step",
-                                     "prefill_step"])
+                                     "prefill_step", "decode_timeline"])
     ap.add_argument("--shape", choices=sorted(bench.SHAPES), default="1b")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="layers of the step cases (0 = all of the shape)")
     ap.add_argument("--repeat", type=int, default=10)
+    ap.add_argument("--from-launch", type=int, default=0, help="decode_timeline: the first launch to print")
+    ap.add_argument("--to-launch", type=int, default=40, help="decode_timeline: the launch after the last one to print")
     ap.add_argument("--no-pairs", action="store_true", help="many-token products on single CTAs instead of pairs (cta_group::2)")
     a = ap.parse_args()
+    if a.case == "decode_timeline":              # before anything loads the ordinary library
+        from geneinfer_b200.ops import library
+        library.use_timeline_build()
     from geneinfer_b200.ops import kernels
     shape_cfg = _set_shape(a.shape)
     if a.no_pairs:
@@ -177,6 +217,8 @@ def main() -> int:
         attention_decode_case(a.batch, a.context, a.repeat, dev, kernels)
     elif a.case == "attention_prefill":
         attention_prefill_case(a.tokens, a.repeat, dev, kernels)
+    elif a.case == "decode_timeline":
+        timeline_case(shape_cfg, a.batch, a.context, a.layers, a.from_launch, a.to_launch)
     else:
         step_case(a.case, shape_cfg, a.batch, a.context, a.tokens, a.layers, a.repeat)
     status = kernels.gemm_tc_status(dev)

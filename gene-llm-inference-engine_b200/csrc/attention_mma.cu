@@ -419,6 +419,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     int* meta = reinterpret_cast<int*>(smem + Cfg::kWarps * kStages * Cfg::kStageBytes + Cfg::kWarps * Cfg::kQBytes + Cfg::kBarBytes);
     const int G = H / Hkv;
 
+    if (threadIdx.x == 0) timeline_record(kTlAttentionDecode, 0);
     if (lane == 0) {
         for (int s = 0; s < kStages; ++s) att_mbar_init(smem_addr(&bars[s]));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -490,7 +491,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const int s = n_issued % kStages;
         const uint32_t k_tile = stages + s * Cfg::kStageBytes, v_tile = k_tile + Cfg::kTileBytes;
         const int key0 = pi.c0 + ptile * kTile;
-        if (!waited && key0 + kTile > pi.pos) { pdl_wait(); waited = true; }      // the key written in this step
+        if (!waited && key0 + kTile > pi.pos) { pdl_wait(); waited = true; if (lane == 0) timeline_record(kTlAttentionDecode, 1); }      // the key written in this step
         // lane b requests box b of this tile (keys and values): the copies of a tile are issued side by
         // side instead of one after the other by a single lane
         const int kb = key0 + (lane < boxes ? lane : 0) * box_rows;
@@ -523,7 +524,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
     p_seek();
     while (pw < total && n_issued < kStages) issue();
-    if (!waited) { pdl_wait(); waited = true; }
+    if (!waited) { pdl_wait(); waited = true; if (lane == 0 && first_item < total) timeline_record(kTlAttentionDecode, 1); }
 
     // ---- consumer
     DecodeItem ci;
@@ -560,6 +561,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             __syncwarp();
             load_q_frags<HD>(q_tile, 0, q_frag, lane);
         }
+        if (lane == 0) timeline_record(kTlAttentionDecode, 2);
 #pragma unroll
         for (int n = 0; n < HD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
         m[0] = m[1] = -INFINITY;
@@ -594,8 +596,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 else warp_tile_step<HD, kTile, true, false, true>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
             }
             __syncwarp();                                   // every lane is done reading the stage
+            if (lane == 0 && tile == ci.tile0) timeline_record(kTlAttentionDecode, 3);
             if (pw < total) issue();
         }
+        if (lane == 0) timeline_record(kTlAttentionDecode, 4);
         if (failed) break;
         if (ci.lo / kChunkKeys == ci.pos / kChunkKeys) {
             // all keys of this token lie in this one chunk: the result is final and is written as the
@@ -630,6 +634,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         // wait (bounded) for the copies this warp still has in flight before its memory is released
         for (int i = n_done; i < n_issued; ++i) att_wait(smem_addr(&bars[i % kStages]), (i / kStages) & 1);
     }
+    if (lane == 0) timeline_record(kTlAttentionDecode, 6);
 }
 
 // grid (H, decode requests), four warps. Warp w sums the chunks first + w, first + w + 4, ... in
@@ -1095,6 +1100,7 @@ static int launch_prefill_tma(const void* q, const void* kc, const void* vc, voi
 }  // namespace gi
 
 using namespace gi;
+GI_TIMELINE_SETTER(gi_timeline_set_attention)
 
 // Query rows per work item of the prefill kernels for this page size and head size: 128 where the
 // pages can be fetched by TMA boxes, 64 otherwise. A work item holds rows / group-size tokens.

@@ -55,6 +55,32 @@ extern int g_pdl_enabled;
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Timeline of a step (only in a library built with -DGI_TIMELINE; otherwise nothing is compiled in): kernels record
+// (kernel id, event, block, %globaltimer) into a buffer that the host hands to every translation unit
+// (gi_timeline_set_*), slot 0 of which counts the records. Events: 0 the block enters, 1 its wait for the
+// kernel ahead is over, 2..5 kernel-specific, 6 the block (for kernels whose warps work alone: a warp) leaves.
+#ifdef GI_TIMELINE
+static __device__ unsigned long long* g_timeline = nullptr;
+__device__ __forceinline__ void timeline_record(int kernel_id, int event) {
+    unsigned long long* tl = g_timeline;
+    if (!tl) return;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    const unsigned long long slot = atomicAdd(tl, 1ull);
+    if (slot < tl[1]) {
+        const unsigned block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        tl[2 + 2 * slot] = (static_cast<unsigned long long>(kernel_id) << 40) | (static_cast<unsigned long long>(event) << 32) | block;
+        tl[3 + 2 * slot] = t;
+    }
+}
+#define GI_TIMELINE_SETTER(name) \
+    extern "C" int name(void* p) { return cudaMemcpyToSymbol(gi::g_timeline, &p, sizeof(p)) == cudaSuccess ? 0 : 1; }
+#else
+__device__ __forceinline__ void timeline_record(int, int) {}
+#define GI_TIMELINE_SETTER(name) extern "C" int name(void*) { return 2; }
+#endif
+enum TimelineKernel : int { kTlRmsNorm = 1, kTlSwiGLU = 2, kTlAttentionDecode = 3, kTlProduct = 100 /* + the form (TcSpecKind) */ };
+
 __device__ __forceinline__ void pdl_prologue() { pdl_launch_dependents(); pdl_wait(); }
 
 template <typename... KArgs, typename... Args>

@@ -130,14 +130,24 @@ template <typename TOut>
 __global__ void __launch_bounds__(256)
 rmsnorm_rows_in_registers_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                  const float* __restrict__ weight, TOut* __restrict__ out, int D, float eps) {
-    pdl_prologue();
+    if (threadIdx.x == 0) timeline_record(kTlRmsNorm, 0);
     __shared__ float warp_part[8];
     __shared__ float s_scale;
     const int r = blockIdx.x;
-    const float4* x4 = reinterpret_cast<const float4*>(x + static_cast<size_t>(rows ? rows[r] : r) * D);
-    const float4* w4 = reinterpret_cast<const float4*>(weight);
-    TOut* o = out + static_cast<size_t>(r) * D;
     const int n4 = D / 4;
+    // the weights belong to no earlier kernel: they are requested before this kernel waits for the one ahead
+    pdl_launch_dependents();
+    const float4* w4 = reinterpret_cast<const float4*>(weight);
+    float4 w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = threadIdx.x + k * 256;
+        w[k] = (i < n4) ? __ldg(w4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
+    if (threadIdx.x == 0) timeline_record(kTlRmsNorm, 1);
+    const float4* x4 = reinterpret_cast<const float4*>(x + static_cast<size_t>(rows ? rows[r] : r) * D);
+    TOut* o = out + static_cast<size_t>(r) * D;
     float4 kept[4];
     float ss = 0.f;
 #pragma unroll
@@ -161,18 +171,19 @@ rmsnorm_rows_in_registers_kernel(const float* __restrict__ x, const int* __restr
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const int i = threadIdx.x + k * 256;
-        if (i < n4) {
-            const float4 w = w4[i];
-            store4<TOut>(o + 4 * i, w.x * (scale * kept[k].x), w.y * (scale * kept[k].y), w.z * (scale * kept[k].z),
-                         w.w * (scale * kept[k].w));
-        }
+        if (i < n4)
+            store4<TOut>(o + 4 * i, w[k].x * (scale * kept[k].x), w[k].y * (scale * kept[k].y), w[k].z * (scale * kept[k].z),
+                         w[k].w * (scale * kept[k].w));
     }
+    if (threadIdx.x == 0) timeline_record(kTlRmsNorm, 6);
 }
 
 // ---------------------------------------------------------------------------------- SwiGLU
 template <typename TOut>
 __global__ void swiglu_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int I, size_t total) {
+    if (threadIdx.x == 0) timeline_record(kTlSwiGLU, 0);
     pdl_prologue();
+    if (threadIdx.x == 0) timeline_record(kTlSwiGLU, 1);
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t t = i / I;
@@ -180,6 +191,7 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, TOut* __restrict__ o
     const float g = gu[t * 2 * I + c];
     const float u = gu[t * 2 * I + I + c];
     out[i] = from_float<TOut>(g * (1.0f / (1.0f + expf(-g))) * u);
+    if (threadIdx.x == 0) timeline_record(kTlSwiGLU, 6);
 }
 
 // ---------------------------------------------------------------------------------- RoPE + store
@@ -303,6 +315,7 @@ __global__ void copy_pages_kernel(char* base, size_t array_stride, size_t page_b
 }  // namespace gi
 
 using namespace gi;
+GI_TIMELINE_SETTER(gi_timeline_set_elementwise)
 
 extern "C" {
 

@@ -168,7 +168,8 @@ struct TcConfig {
     static constexpr int kStages = TILED ? ((BLOCK_Q >= 128) ? 3 : (BLOCK_Q >= 64) ? 4 : 5)
                                          : ((BLOCK_Q >= 256) ? 4 : (BLOCK_Q >= 128) ? 6 : 8);
     static constexpr int kTmemCols = BLOCK_Q < 32 ? 32 : BLOCK_Q;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
+    static constexpr int kSideBytes = 512;      // barriers and flags (the first 256), the tokens' positions and page rows of a rotating 16-token product
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment */ + kSideBytes;
     // A cluster's split 0 receives the partial tiles of the other splits, [split - 1][q][128 rows], in its
     // pipeline stages once its own products are done with them (it tells the others when); behind them
     // lie the per-token arrays of the rotating epilogue.
@@ -177,6 +178,7 @@ struct TcConfig {
     // (not for 16 tokens: their partial tiles always find a place of their own, and the kernel that every
     // small decode step runs stays free of the extra code)
     static constexpr bool kStagesReceive = BLOCK_Q >= 32;
+    static constexpr int kOwnPlaceLimit = 232448;
     static constexpr bool cluster_fits(int cluster_splits) {
         return kStagesReceive && (cluster_splits - 1) * kPartialBytes + kPartialBytes + kTokenInfoBytes <= kStages * kStageBytes;
     }
@@ -306,6 +308,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     const bool prefetch_p = Spec::fixed ? true : p.prefetch_p != 0;
     const bool stream_p = Spec::fixed ? true : p.stream_p != 0;
     const int n_splits = (Spec::fixed && Spec::one_split) ? 1 : p.splits;
+    if (threadIdx.x == 0) timeline_record(kTlProduct + SPEC, 0);
     constexpr int kKb = Cfg::kKb;
     constexpr int kStages = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -315,7 +318,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     // [2kStages + 1] the other splits' partial tiles have arrived (cluster reduce, split 0),
     // [2kStages + 2] split 0's stages are free to receive them (cluster reduce, the other splits)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 3);
-    float* partials = reinterpret_cast<float*>((Cfg::kStagesReceive && cluster == 2) ? smem : smem + kStages * Cfg::kStageBytes + 256);
+    float* partials = reinterpret_cast<float*>((Cfg::kStagesReceive && cluster == 2) ? smem : smem + kStages * Cfg::kStageBytes + Cfg::kSideBytes);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = const_cast<int*>(abort_flag) + 1;
     int* epi_abort = last_flag + 1;
@@ -381,6 +384,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 load_p(i, full);
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
+            timeline_record(kTlProduct + SPEC, 1);
             for (int i = 0; i < early; ++i) {
                 load_q(i, smem_u32(&bars[i]));
                 issued = i + 1;
@@ -421,6 +425,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     break;
                 }
                 tc_fence_after();
+                if (i == 0) timeline_record(kTlProduct + SPEC, 2);
                 const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes);
 #pragma unroll
                 for (int j = 0; j < kKb; ++j) {
@@ -435,6 +440,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 umma_commit(smem_u32(&bars[kStages + s]));      // frees the stage once the MMAs have read it
             }
             if (ok) umma_commit(smem_u32(&bars[2 * kStages]));  // accumulator complete
+            timeline_record(kTlProduct + SPEC, 3);
         }
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..5)
@@ -468,6 +474,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 }
             }
         }
+        // A 16-token product shares the tokens' positions and page rows among the epilogue threads now, and every thread
+        // fetches the cosines and sines its row will need: the table look-ups (two trips to memory) leave the tail
+        // that follows the last MMA, which is on every decode step's critical path.
+        constexpr bool kRopeEarly = BLOCK_Q == 16;
+        int* side_pos = reinterpret_cast<int*>(smem + kStages * Cfg::kStageBytes + 256);
+        long long* side_base = reinterpret_cast<long long*>(side_pos + 16);
+        float rope_c[16], rope_s[16];
+        int rope_partner = row_in_tile;
+        bool rope_rotate = false, rope_first = true;
+        if (kRopeEarly && rope_on) {
+            if (row_in_tile < 16) { side_pos[row_in_tile] = tok_pos; side_base[row_in_tile] = tok_base; }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const RopeStoreParams& rp = p.rope;
+            const int hd = rp.hd, head = row_p / hd, d = row_p - head * hd;
+            const int rh = rp.cos_t ? rp.rot_half : 0;
+            rope_rotate = row_p < p.rows_p && head < rp.H + rp.Hkv && d < 2 * rh;
+            int ci = 0;
+            if (rope_rotate) {
+                if (rp.interleaved) { rope_first = (d & 1) == 0; rope_partner = row_in_tile ^ 1; ci = d >> 1; }
+                else { rope_first = d < rh; rope_partner = rope_first ? row_in_tile + rh : row_in_tile - rh; ci = rope_first ? d : d - rh; }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const size_t at = static_cast<size_t>(side_pos[j]) * rh + ci;      // tokens beyond the last have position 0
+                    rope_c[j] = __ldg(rp.cos_t + at);
+                    rope_s[j] = __ldg(rp.sin_t + at);
+                }
+            }
+        }
         // The pipeline's stages are free once the accumulator is complete: the finished tile is laid
         // there as [token][128 rows] so that a thread can read its rotation partner's value.
         float* xch = reinterpret_cast<float*>(smem);
@@ -487,6 +521,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             have = false;
         }
         tc_fence_after();
+        if (warp == 2 && lane == 0) timeline_record(kTlProduct + SPEC, 4);
         // one decision for all 128 epilogue threads (they meet at named barriers below)
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) *epi_abort = *abort_flag;
@@ -632,40 +667,63 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         }
         if (rope_on) {
             const RopeStoreParams& rp = p.rope;
-            // behind the finished tile and, in a cluster, behind the partial tiles that other threads may still be reading
-            int* tpos = reinterpret_cast<int*>(xch + ((Cfg::kStagesReceive && cluster == 2) ? max(1, n_splits - 1) : 1) * BLOCK_Q * kBlockP);
-            long long* tbase = reinterpret_cast<long long*>(tpos + BLOCK_Q);
-            if (row_in_tile < BLOCK_Q) { tpos[row_in_tile] = tok_pos; tbase[row_in_tile] = tok_base; }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (emitted && row_p < p.rows_p) {
-                // this thread's row is feature d of one head; its partner in a rotated pair lies in the same tile
-                const int hd = rp.hd, head = row_p / hd, d = row_p - head * hd;
-                const bool is_q = head < rp.H, is_k = !is_q && head < rp.H + rp.Hkv;
-                const int rh = rp.cos_t ? rp.rot_half : 0;
-                const bool rotate = (is_q || is_k) && d < 2 * rh;
-                int partner = row_in_tile, ci = 0;
-                bool first = true;                       // first member of the pair: a c - b s; second: a s + b c
-                if (rotate) {
-                    if (rp.interleaved) { first = (d & 1) == 0; partner = row_in_tile ^ 1; ci = d >> 1; }
-                    else { first = d < rh; partner = first ? row_in_tile + rh : row_in_tile - rh; ci = first ? d : d - rh; }
-                }
-                const int n_tok = min(BLOCK_Q, p.rows_q - tile_q * BLOCK_Q);
-                const size_t kv_head = static_cast<size_t>(is_q ? 0 : (is_k ? head - rp.H : head - rp.H - rp.Hkv)) * rp.page_size * hd + d;
-                __nv_bfloat16* cache = is_k ? rp.k_cache : rp.v_cache;
-#pragma unroll 4
-                for (int j = 0; j < n_tok; ++j) {
-                    float out = xch[j * kBlockP + row_in_tile];
-                    if (rotate) {
-                        const float other = xch[j * kBlockP + partner];
-                        const size_t at = static_cast<size_t>(tpos[j]) * rh + ci;
-                        const float ck = __ldg(rp.cos_t + at), sk = __ldg(rp.sin_t + at);
-                        out = first ? out * ck - other * sk : other * sk + out * ck;
+            if constexpr (kRopeEarly) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");          // the finished tile is complete
+                if (emitted && row_p < p.rows_p) {
+                    const int hd = rp.hd, head = row_p / hd, d = row_p - head * hd;
+                    const bool is_q = head < rp.H, is_k = !is_q && head < rp.H + rp.Hkv;
+                    const int n_tok = min(BLOCK_Q, p.rows_q - tile_q * BLOCK_Q);
+                    const size_t kv_head = static_cast<size_t>(is_q ? 0 : (is_k ? head - rp.H : head - rp.H - rp.Hkv)) * rp.page_size * hd + d;
+                    __nv_bfloat16* cache = is_k ? rp.k_cache : rp.v_cache;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (j >= n_tok) break;
+                        float out = xch[j * kBlockP + row_in_tile];
+                        if (rope_rotate) {
+                            const float other = xch[j * kBlockP + rope_partner];
+                            out = rope_first ? out * rope_c[j] - other * rope_s[j] : other * rope_s[j] + out * rope_c[j];
+                        }
+                        if (is_q) rp.q_out[(static_cast<size_t>(tile_q * BLOCK_Q + j) * rp.H + head) * hd + d] = __float2bfloat16_rn(out);
+                        else if (side_base[j] >= 0) cache[side_base[j] + kv_head] = __float2bfloat16_rn(out);
                     }
-                    if (is_q) rp.q_out[(static_cast<size_t>(tile_q * BLOCK_Q + j) * rp.H + head) * hd + d] = __float2bfloat16_rn(out);
-                    else if (tbase[j] >= 0) cache[tbase[j] + kv_head] = __float2bfloat16_rn(out);
+                }
+            } else {
+                // behind the finished tile and, in a cluster, behind the partial tiles that other threads may still be reading
+                int* tpos = reinterpret_cast<int*>(xch + ((Cfg::kStagesReceive && cluster == 2) ? max(1, n_splits - 1) : 1) * BLOCK_Q * kBlockP);
+                long long* tbase = reinterpret_cast<long long*>(tpos + BLOCK_Q);
+                if (row_in_tile < BLOCK_Q) { tpos[row_in_tile] = tok_pos; tbase[row_in_tile] = tok_base; }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (emitted && row_p < p.rows_p) {
+                    // this thread's row is feature d of one head; its partner in a rotated pair lies in the same tile
+                    const int hd = rp.hd, head = row_p / hd, d = row_p - head * hd;
+                    const bool is_q = head < rp.H, is_k = !is_q && head < rp.H + rp.Hkv;
+                    const int rh = rp.cos_t ? rp.rot_half : 0;
+                    const bool rotate = (is_q || is_k) && d < 2 * rh;
+                    int partner = row_in_tile, ci = 0;
+                    bool first = true;                       // first member of the pair: a c - b s; second: a s + b c
+                    if (rotate) {
+                        if (rp.interleaved) { first = (d & 1) == 0; partner = row_in_tile ^ 1; ci = d >> 1; }
+                        else { first = d < rh; partner = first ? row_in_tile + rh : row_in_tile - rh; ci = first ? d : d - rh; }
+                    }
+                    const int n_tok = min(BLOCK_Q, p.rows_q - tile_q * BLOCK_Q);
+                    const size_t kv_head = static_cast<size_t>(is_q ? 0 : (is_k ? head - rp.H : head - rp.H - rp.Hkv)) * rp.page_size * hd + d;
+                    __nv_bfloat16* cache = is_k ? rp.k_cache : rp.v_cache;
+#pragma unroll 4
+                    for (int j = 0; j < n_tok; ++j) {
+                        float out = xch[j * kBlockP + row_in_tile];
+                        if (rotate) {
+                            const float other = xch[j * kBlockP + partner];
+                            const size_t at = static_cast<size_t>(tpos[j]) * rh + ci;
+                            const float ck = __ldg(rp.cos_t + at), sk = __ldg(rp.sin_t + at);
+                            out = first ? out * ck - other * sk : other * sk + out * ck;
+                        }
+                        if (is_q) rp.q_out[(static_cast<size_t>(tile_q * BLOCK_Q + j) * rp.H + head) * hd + d] = __float2bfloat16_rn(out);
+                        else if (tbase[j] >= 0) cache[tbase[j] + kv_head] = __float2bfloat16_rn(out);
+                    }
                 }
             }
         }
+        if (warp == 2 && lane == 0) timeline_record(kTlProduct + SPEC, 5);
         tc_fence_before();
     }
     __syncthreads();
@@ -673,6 +731,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         tc_fence_after();
         tmem_dealloc(tmem_base, Cfg::kTmemCols);
     }
+    if (threadIdx.x == 0) timeline_record(kTlProduct + SPEC, 6);
 }
 
 // ------------------------------------------------------------------------------------------ persistent kernel
@@ -1245,7 +1304,7 @@ template <int BLOCK_Q, bool TILED>
 static int cluster_capacity(int splits) {
     using Cfg = TcConfig<BLOCK_Q, TILED>;
     static int cached[kMaxClusterSplits + 1] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
-    const bool own_place = Cfg::smem_bytes(splits) <= kMaxSmemPerBlock;
+    const bool own_place = Cfg::smem_bytes(splits) <= Cfg::kOwnPlaceLimit;
     if (splits < 2 || splits > kMaxClusterSplits || !(own_place || Cfg::cluster_fits(splits))) return 0;
     if (cached[splits] >= 0) return cached[splits];
     int n = 0;
@@ -1310,12 +1369,12 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, TcParams p, d
     // would cost more than the reduce through global memory
     const long long tiles = static_cast<long long>(grid.x) * grid.y;
     p.cluster = (p.splits > 1 && g_cluster_reduce && tiles <= cluster_capacity<BLOCK_Q, TILED>(p.splits)) ? 1 : 0;
-    if (p.cluster && Cfg::smem_bytes(p.splits) > kMaxSmemPerBlock) p.cluster = 2;    // partial tiles in split 0's stages
+    if (p.cluster && Cfg::smem_bytes(p.splits) > Cfg::kOwnPlaceLimit) p.cluster = 2;    // partial tiles in split 0's stages
     // the forms of a decode step of up to 16 tokens over tiled weights: kernels with nothing else in them
     if constexpr (BLOCK_Q == 16 && TILED) {
         if (g_specialised && p.prefetch_p && p.stream_p && !p.c_bf16) {
-            if (p.rope_on && p.cluster == 1 && !p.accumulate) return launch_tc_form<BLOCK_Q, TILED, kSpecRopeCluster>(mp, mq, p, grid, st);
-            if (!p.rope_on && p.cluster == 1 && p.accumulate) return launch_tc_form<BLOCK_Q, TILED, kSpecAddCluster>(mp, mq, p, grid, st);
+            if (p.rope_on && p.cluster == TcSpec<kSpecRopeCluster>::cluster && !p.accumulate) return launch_tc_form<BLOCK_Q, TILED, kSpecRopeCluster>(mp, mq, p, grid, st);
+            if (!p.rope_on && p.cluster == TcSpec<kSpecAddCluster>::cluster && p.accumulate) return launch_tc_form<BLOCK_Q, TILED, kSpecAddCluster>(mp, mq, p, grid, st);
             if (!p.rope_on && p.splits == 1 && !p.accumulate) return launch_tc_form<BLOCK_Q, TILED, kSpecStoreOne>(mp, mq, p, grid, st);
         }
     }
@@ -1326,6 +1385,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, TcParams p, d
 }  // namespace gi
 
 using namespace gi;
+GI_TIMELINE_SETTER(gi_timeline_set_gemm)
 
 // C[M,N] (+)= A[M,K] * W[N,K]^T, A and W bfloat16 row-major with row strides lda, ldw (elements),
 // C float (optionally accumulated into) or bfloat16 with row stride ldc.
@@ -1366,10 +1426,10 @@ extern "C" int gi_gemm_tc_cluster_capacity(int block_q, int splits, int tiled) {
         splits = -splits;
         bool own = false;
         switch (block_q) {
-            case 16: own = (tiled ? TcConfig<16, true>::smem_bytes(splits) : TcConfig<16, false>::smem_bytes(splits)) <= kMaxSmemPerBlock; break;
-            case 32: own = (tiled ? TcConfig<32, true>::smem_bytes(splits) : TcConfig<32, false>::smem_bytes(splits)) <= kMaxSmemPerBlock; break;
-            case 64: own = (tiled ? TcConfig<64, true>::smem_bytes(splits) : TcConfig<64, false>::smem_bytes(splits)) <= kMaxSmemPerBlock; break;
-            case 128: own = (tiled ? TcConfig<128, true>::smem_bytes(splits) : TcConfig<128, false>::smem_bytes(splits)) <= kMaxSmemPerBlock; break;
+            case 16: own = tiled ? TcConfig<16, true>::smem_bytes(splits) <= TcConfig<16, true>::kOwnPlaceLimit : TcConfig<16, false>::smem_bytes(splits) <= TcConfig<16, false>::kOwnPlaceLimit; break;
+            case 32: own = tiled ? TcConfig<32, true>::smem_bytes(splits) <= TcConfig<32, true>::kOwnPlaceLimit : TcConfig<32, false>::smem_bytes(splits) <= TcConfig<32, false>::kOwnPlaceLimit; break;
+            case 64: own = tiled ? TcConfig<64, true>::smem_bytes(splits) <= TcConfig<64, true>::kOwnPlaceLimit : TcConfig<64, false>::smem_bytes(splits) <= TcConfig<64, false>::kOwnPlaceLimit; break;
+            case 128: own = tiled ? TcConfig<128, true>::smem_bytes(splits) <= TcConfig<128, true>::kOwnPlaceLimit : TcConfig<128, false>::smem_bytes(splits) <= TcConfig<128, false>::kOwnPlaceLimit; break;
             default: break;
         }
         if (!own) return 0;

@@ -39,9 +39,14 @@ def _nvcc() -> str:
                      "the CUDA kernels of this engine cannot be built")
 
 
-def _digest() -> str:
+def _flags(timeline: bool) -> List[str]:
+    """nvcc flags; ``timeline``: the kernels also record time stamps of their phases (csrc/common.cuh: GI_TIMELINE)."""
+    return NVCC_FLAGS + (["-DGI_TIMELINE"] if timeline else [])
+
+
+def _digest(timeline: bool = False) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(_flags(timeline)).encode())
     for name in sorted(os.listdir(CSRC)):
         if name.endswith((".cu", ".cuh", ".h")):
             h.update(name.encode())
@@ -50,8 +55,8 @@ def _digest() -> str:
     return h.hexdigest()
 
 
-def _build_dir() -> str:
-    in_tree = os.path.join(CSRC, "_build")
+def _build_dir(timeline: bool = False) -> str:
+    in_tree = os.path.join(CSRC, "_build", "timeline") if timeline else os.path.join(CSRC, "_build")
     try:
         os.makedirs(in_tree, exist_ok=True)
         probe = os.path.join(in_tree, f".write_probe_{os.getpid()}")
@@ -60,16 +65,17 @@ def _build_dir() -> str:
         os.remove(probe)
         return in_tree
     except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"geneinfer_b200_build_{os.getuid()}")
+        d = os.path.join(tempfile.gettempdir(), f"geneinfer_b200_build_{os.getuid()}" + ("_timeline" if timeline else ""))
         os.makedirs(d, exist_ok=True)
         return d
 
 
-def library_path(build_if_needed: bool = True, verbose: bool = True) -> str:
-    """Path of the built library, compiling it first when missing or stale."""
-    digest = _digest()
-    in_tree = os.path.join(CSRC, "_build")
-    for d in (in_tree, os.path.join(tempfile.gettempdir(), f"geneinfer_b200_build_{os.getuid()}")):
+def library_path(build_if_needed: bool = True, verbose: bool = True, timeline: bool = False) -> str:
+    """Path of the built library, compiling it first when missing or stale. ``timeline``: the variant whose
+    kernels record time stamps (a library of its own beside the ordinary one)."""
+    digest = _digest(timeline)
+    in_tree = os.path.join(CSRC, "_build", "timeline") if timeline else os.path.join(CSRC, "_build")
+    for d in (in_tree, os.path.join(tempfile.gettempdir(), f"geneinfer_b200_build_{os.getuid()}" + ("_timeline" if timeline else ""))):
         lib, stamp = os.path.join(d, LIB_NAME), os.path.join(d, "stamp.txt")
         if os.path.isfile(lib) and os.path.isfile(stamp):
             with open(stamp) as f:
@@ -77,13 +83,13 @@ def library_path(build_if_needed: bool = True, verbose: bool = True) -> str:
                     return lib
     if not build_if_needed:
         raise BuildError("the kernel library is not built")
-    return build(verbose=verbose)
+    return build(verbose=verbose, timeline=timeline)
 
 
-def build(verbose: bool = True) -> str:
+def build(verbose: bool = True, timeline: bool = False) -> str:
     nvcc = _nvcc()
-    out_dir = _build_dir()
-    digest = _digest()
+    out_dir = _build_dir(timeline)
+    digest = _digest(timeline)
     srcs = sources()
     log = (lambda m: print(f"[geneinfer_b200 build] {m}", file=sys.stderr, flush=True)) if verbose else (lambda m: None)
     log(f"compiling {len(srcs)} CUDA files for sm_100a into {out_dir}")
@@ -91,7 +97,7 @@ def build(verbose: bool = True) -> str:
 
     def compile_one(name: str) -> None:
         obj = os.path.join(out_dir, name[:-3] + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-I", CSRC, "-c", os.path.join(CSRC, name), "-o", obj]
+        cmd = [nvcc, *_flags(timeline), "-I", CSRC, "-c", os.path.join(CSRC, name), "-o", obj]
         p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         results[name] = (p.returncode, p.stdout, obj)
 
@@ -99,12 +105,14 @@ def build(verbose: bool = True) -> str:
     t0 = time.time()
     for t in threads:
         t.start()
+    last = t0
     while any(t.is_alive() for t in threads):
         for t in threads:
-            t.join(timeout=5.0 / max(1, len(threads)))
-        if any(t.is_alive() for t in threads):
+            t.join(timeout=0.2)
+        if any(t.is_alive() for t in threads) and time.time() - last >= 5.0:
+            last = time.time()
             done = sum(1 for s in srcs if s in results)
-            log(f"nvcc is running: {done}/{len(srcs)} files done after {time.time() - t0:.0f} s")
+            log(f"nvcc is running: {done}/{len(srcs)} files done after {last - t0:.0f} s")
     with open(os.path.join(out_dir, "ptxas.log"), "w") as f:
         for name in srcs:
             f.write(f"==== {name}\n{results[name][1]}\n")

@@ -49,6 +49,7 @@ _SIGNATURES = {
     "gi_gemm_tc_set_cluster": [c_int],
     "gi_gemm_tc_set_stream_weights": [c_int],
     "gi_gemm_tc_set_specialised": [c_int],
+    "gi_timeline_set_gemm": [c_void_p], "gi_timeline_set_elementwise": [c_void_p], "gi_timeline_set_attention": [c_void_p],
     "gi_attention_set_stream_kv": [c_int],
     "gi_gemm_tc_cluster_capacity": [c_int, c_int, c_int],
     "gi_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
@@ -66,10 +67,22 @@ _SIGNATURES = {
 }
 
 
+_timeline_build = False
+
+
+def use_timeline_build() -> None:
+    """Makes this process load the library variant whose kernels record time stamps of their phases
+    (``ops/timeline.py``); to be called before the first kernel call."""
+    global _timeline_build
+    if _lib is not None and not _timeline_build:
+        raise RuntimeError("the kernel library is loaded already: ask for the timeline build before the first kernel call")
+    _timeline_build = True
+
+
 def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
-        path = library_path()
+        path = library_path(timeline=_timeline_build)
         loaded = ctypes.CDLL(path)
         loaded.gi_last_error.restype = c_char_p
         loaded.gi_last_error.argtypes = []
