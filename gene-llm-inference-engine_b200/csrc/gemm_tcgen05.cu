@@ -225,6 +225,8 @@ struct TcParams {
     int* status;
     int prefetch_p;          // P is a weight matrix no earlier kernel writes: its first tiles may be
                              // fetched before the kernel waits for the kernels it depends on
+    const uint8_t* ahead;    // weights that a later product of the step will read, asked into L2 by this product's CTAs
+    unsigned long long ahead_bytes;   //   once their own loads are on their way (null: none); a multiple of 32 KB
     int stream_p;            // P is a weight matrix that the step reads once (few tokens): its loads carry the
                              // evict-first L2 policy
     int cluster;             // the splits of a tile are one cluster (dims 1 x 1 x splits): reduce in shared memory
@@ -401,6 +403,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 load_p(i, full);
                 load_q(i, full);
                 issued = i + 1;
+            }
+            if (p.ahead != nullptr && !*abort_flag) {
+                // This CTA's share of the weights to ask into L2, in pieces of 32 KB. The product that reads them keeps
+                // only five stages per CTA in flight of its own before it may start; what lies in L2 by then is fetched
+                // in a fraction of the time, so the stream from memory pauses less between the kernels of a step.
+                const unsigned long long ctas = static_cast<unsigned long long>(gridDim.x) * gridDim.y * gridDim.z;
+                const unsigned long long me = blockIdx.x + gridDim.x * (blockIdx.y + static_cast<unsigned long long>(gridDim.y) * blockIdx.z);
+                for (unsigned long long i = me; i < p.ahead_bytes / 32768ull; i += ctas)
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.ahead + i * 32768ull), "r"(32768u) : "memory");
             }
             if (*abort_flag) {
                 // drain: every copy this lane issued must have landed before the CTA may exit
@@ -1395,6 +1406,8 @@ GI_TIMELINE_SETTER(gi_timeline_set_gemm)
 //   tiles * splits * 128 * block_q floats and counters one zeroed word per tile.
 //   w_tiles (swap only, may be null): W once more in the tile-by-tile layout of TcParams::p_tiles;
 //   the weights are then fetched with bulk copies, two 64-wide blocks of K to a stage.
+//   ahead, ahead_bytes (products of at most 32 tokens, may be null): memory that a later kernel of the step will
+//   stream (the start of the next large weight matrix), asked into L2 by this product's CTAs.
 // Switches the cluster reduce of split products on or off (on by default); returns the old value.
 extern "C" int gi_gemm_tc_set_cluster(int on) {
     const int old = g_cluster_reduce;
@@ -1446,7 +1459,7 @@ extern "C" int gi_gemm_tc_cluster_capacity(int block_q, int splits, int tiled) {
 static int run_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int accumulate, int M, int N, int K,
                        long long lda, long long ldw, long long ldc, int swap, int block_q, int splits,
                        void* workspace, long long workspace_floats, void* counters, int n_counters, void* status,
-                       const void* w_tiles, const RopeStoreParams* rope, void* stream) {
+                       const void* w_tiles, const RopeStoreParams* rope, const void* ahead, long long ahead_bytes, void* stream) {
     if (M == 0 || N == 0) return 0;
     GI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: sizes must be positive (M=%d, N=%d, K=%d)", M, N, K);
     GI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
@@ -1485,6 +1498,11 @@ static int run_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int a
     }
 
     CUtensorMap mp, mq;
+    if (ahead != nullptr && ahead_bytes >= 32768 && swap && block_q <= 32) {
+        GI_REQUIRE(reinterpret_cast<uintptr_t>(ahead) % 16 == 0, "gemm_tc: the weights to ask into L2 must be 16-byte aligned");
+        p.ahead = static_cast<const uint8_t*>(ahead);
+        p.ahead_bytes = static_cast<unsigned long long>(ahead_bytes) / 32768ull * 32768ull;
+    }
     p.prefetch_p = swap ? 1 : 0;
     // measured on B200 (Llama-3.2-1B shape, a decode step): 3.5 % faster at 1 and 8 tokens, 0.8 % slower at 64
     p.stream_p = (swap && block_q <= 32 && g_stream_weights) ? 1 : 0;
@@ -1517,9 +1535,9 @@ static int run_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int a
 static int gi_gemm_tc_impl(const void* A, const void* W, void* C, int c_dtype, int accumulate, int M, int N, int K,
                           long long lda, long long ldw, long long ldc, int swap, int block_q, int splits,
                           void* workspace, long long workspace_floats, void* counters, int n_counters, void* status,
-                          const void* w_tiles, void* stream) {
+                          const void* w_tiles, const void* ahead, long long ahead_bytes, void* stream) {
     return run_gemm_tc(A, W, C, c_dtype, accumulate, M, N, K, lda, ldw, ldc, swap, block_q, splits, workspace,
-                       workspace_floats, counters, n_counters, status, w_tiles, nullptr, stream);
+                       workspace_floats, counters, n_counters, status, w_tiles, nullptr, ahead, ahead_bytes, stream);
 }
 
 // The [q; k; v] product of few tokens (at most block_q <= 128, weights on the 128-row side) with rotation
@@ -1541,7 +1559,7 @@ static int gi_gemm_tc_rope_impl(const void* A, const void* W, int M, int K, long
                          static_cast<__nv_bfloat16*>(v_cache), H, Hkv, hd, page_size, write_kv};
     const int N = (H + 2 * Hkv) * hd;
     return run_gemm_tc(A, W, nullptr, kF32, 0, M, N, K, lda, ldw, N, 1, block_q, splits, workspace, workspace_floats,
-                       counters, n_counters, status, w_tiles, &rope, stream);
+                       counters, n_counters, status, w_tiles, &rope, nullptr, 0, stream);
 }
 
 // Reads the status word (synchronises the stream): 0 = no bounded wait ever gave up.
@@ -1703,8 +1721,8 @@ static int gi_gemm_tc_persistent_rope_impl(const void* A, const void* W, int M, 
 
 // The exported names: each runs its implementation above and, while a launch program is recorded, leaves a copy of
 // its arguments in the program (common.cuh).
-extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int accumulate, int M, int N, int K, long long lda, long long ldw, long long ldc, int swap, int block_q, int splits, void* workspace, long long workspace_floats, void* counters, int n_counters, void* status, const void* w_tiles, void* stream) {
-    return gi::dispatch(gi_gemm_tc_impl, A, W, C, c_dtype, accumulate, M, N, K, lda, ldw, ldc, swap, block_q, splits, workspace, workspace_floats, counters, n_counters, status, w_tiles, stream);
+extern "C" int gi_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int accumulate, int M, int N, int K, long long lda, long long ldw, long long ldc, int swap, int block_q, int splits, void* workspace, long long workspace_floats, void* counters, int n_counters, void* status, const void* w_tiles, const void* ahead, long long ahead_bytes, void* stream) {
+    return gi::dispatch(gi_gemm_tc_impl, A, W, C, c_dtype, accumulate, M, N, K, lda, ldw, ldc, swap, block_q, splits, workspace, workspace_floats, counters, n_counters, status, w_tiles, ahead, ahead_bytes, stream);
 }
 
 extern "C" int gi_gemm_tc_rope(const void* A, const void* W, int M, int K, long long lda, long long ldw, int block_q, int splits, void* workspace, long long workspace_floats, void* counters, int n_counters, void* status, const void* w_tiles, const int* positions, const int* row_req, const int* block_tables, int table_stride, const float* cos_t, const float* sin_t, int rot_half, int interleaved, void* q_out, void* k_cache, void* v_cache, int H, int Hkv, int hd, int page_size, int write_kv, void* stream) {

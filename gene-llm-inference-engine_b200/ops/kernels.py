@@ -462,11 +462,18 @@ def tile_weight(w: torch.Tensor) -> torch.Tensor:
 _gemm_choice = {}      # (M, N, K, output dtype, tiled weights) -> (swap, block_q, splits, persistent): the sizes decide, once
 
 
+# How much of the weights that a later product will stream a few-token product asks into L2 (measured on B200 at the
+# Llama-3.2-1B widths: 16 to 24 MiB ahead of the [gate; up] product make a decode step 1 to 3 % faster, 48 MiB slower)
+AHEAD_BYTES = 24 << 20
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, plan=None,
-            w_tiles: Optional[torch.Tensor] = None) -> None:
+            w_tiles: Optional[torch.Tensor] = None, ahead: Optional[torch.Tensor] = None) -> None:
     """out[M,N] (+)= a[M,K] @ w[N,K]^T on the tensor cores: bfloat16 operands, 32-bit accumulation,
     output 32-bit (optionally accumulated into) or bfloat16. K must be a multiple of 8. ``w_tiles``
-    (tile_weight(w)) lets products of few tokens fetch the weights with bulk copies."""
+    (tile_weight(w)) lets products of few tokens fetch the weights with bulk copies. ``ahead``: a tensor
+    that a later kernel of the step streams (the tile-by-tile weights of the next large product); a product of few
+    tokens asks its first AHEAD_BYTES into L2 while it runs, so that memory keeps streaming between the kernels."""
     M, K = a.shape
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (M, N):
@@ -503,7 +510,10 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     check(lib().gi_gemm_tc(_dev(a, "a", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"),
                            dtype_code(out.dtype), int(accumulate), M, N, K, K, K, N, int(swap), block_q, splits,
                            st.workspace.data_ptr(), st.workspace.numel(), st.counters.data_ptr(), st.counters.numel(),
-                           st.status.data_ptr(), _opt(w_tiles, "w_tiles", torch.bfloat16), _stream()), "gemm_tc")
+                           st.status.data_ptr(), _opt(w_tiles, "w_tiles", torch.bfloat16),
+                           ahead.data_ptr() if ahead is not None and swap and M <= 32 else 0,
+                           min(AHEAD_BYTES, ahead.numel() * ahead.element_size()) if ahead is not None else 0,
+                           _stream()), "gemm_tc")
 
 
 def gemm_swiglu_supported(M: int, I: int, K: int) -> bool:

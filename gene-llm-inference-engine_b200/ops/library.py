@@ -30,7 +30,8 @@ _SIGNATURES = {
     "gi_gemm_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                      c_int, c_void_p],
     "gi_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
-                   c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
+                   c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong,
+                   c_void_p],
     "gi_gemm_tc_persistent": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                               c_int, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p],
     "gi_gemm_tc_persistent_rope": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,

@@ -52,11 +52,14 @@ class Linear:
             new.weight_tiles = kernels.tile_weight(weight)
         return new
 
-    def forward(self, a: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
+    def forward(self, a: torch.Tensor, out: torch.Tensor, accumulate: bool = False, then: "Linear" = None) -> torch.Tensor:
+        """``then``: the Linear whose product runs next but one (after a small kernel); a product of few tokens
+        asks the start of its weights into L2 meanwhile (``kernels.gemm_tc``: ``ahead``)."""
         if a.dtype != self.compute_dtype:
             raise kernels.KernelError(f"Linear: activations are {a.dtype}, the weight is {self.compute_dtype}")
         if self.compute_dtype is torch.bfloat16 and self.in_features % 8 == 0:
-            kernels.gemm_tc(a, self.weight, out, accumulate, w_tiles=self.weight_tiles)   # tensor cores (TMA needs 16-byte rows)
+            kernels.gemm_tc(a, self.weight, out, accumulate, w_tiles=self.weight_tiles,   # tensor cores (TMA needs 16-byte rows)
+                            ahead=then.weight_tiles if then is not None else None)
         else:
             kernels.gemm_simt(a, self.weight, out, accumulate)
         return out

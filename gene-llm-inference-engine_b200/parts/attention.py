@@ -85,9 +85,13 @@ class AttentionMixer:
         return (run.cache_layer, run.writes_cache, rows.numel(), work.shape[0],
                 (longest + self.chunk_keys - 1) // self.chunk_keys)
 
-    def forward(self, ctx, run, xn: torch.Tensor, x: torch.Tensor) -> None:
+    takes_then = True      # forward accepts ``then``
+
+    def forward(self, ctx, run, xn: torch.Tensor, x: torch.Tensor, then=None) -> None:
         """``xn``: normalised input [T, hidden] in the compute dtype; ``x``: the 32-bit residual
-        stream, to which the mixer's output is added. ``run`` names whose cache to use."""
+        stream, to which the mixer's output is added. ``run`` names whose cache to use. ``then``: the Linear
+        of the large product that follows this mixer (the feed-forward's first), for the last product here to
+        ask the start of its weights into L2."""
         T = xn.shape[0]
         H, Hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         k_cache, v_cache = ctx.pages(run.cache_layer)
@@ -124,4 +128,4 @@ class AttentionMixer:
         else:
             kernels.attention_generic(q, k_cache, v_cache, att, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
                                       ctx.page_size, self.scale, self.window)
-        self.w_o.forward(att, x, accumulate=True)
+        self.w_o.forward(att, x, accumulate=True, then=then)

@@ -40,7 +40,11 @@ class PreNormBlock:
 
     def _mixer_half(self, ctx, run, xn, x) -> None:
         self.mixer_norm.forward(x, xn)
-        self.mixer.forward(ctx, run, xn, x)
+        then = getattr(self.feed_forward, "first_product", None)
+        if then is not None and getattr(self.mixer, "takes_then", False):
+            self.mixer.forward(ctx, run, xn, x, then=then)      # the mixer's last product asks for the weights that follow
+        else:
+            self.mixer.forward(ctx, run, xn, x)
 
     def _feed_forward_half(self, ctx, xn, x) -> None:
         self.feed_forward_norm.forward(x, xn)

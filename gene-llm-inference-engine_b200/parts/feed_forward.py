@@ -30,6 +30,11 @@ class SwiGLUFeedForward:
         self.w_down = Linear(weights["w_down"], build.compute_dtype, build.device, tiles=build.weight_tiles)
         self.dtype = build.compute_dtype
 
+    @property
+    def first_product(self):
+        """The Linear of the first product (a block hands it to the mixer that runs before, see AttentionMixer.forward)."""
+        return self.w_gate_up
+
     def launch_key(self, ctx):
         """Its launches depend on the token count only (which the caller's key holds)."""
         return ()

@@ -649,6 +649,14 @@ def test_l2_policy_of_streamed_loads_changes_no_result():
         K().l2_streaming(*old)
     assert K().l2_streaming() == old
     assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3]) and torch.equal(atts[0], atts[1])
+    # a product that asks other memory into L2 while it runs (the weights of a product to come): the same bits,
+    # whatever the size of that memory (less than a piece of 32 KB, pieces and a rest)
+    for n in (1000, 32768 // 2 * 3 + 8):
+        ahead = torch.zeros(n, dtype=torch.bfloat16, device=DEV)
+        out = torch.empty(8, 520, dtype=torch.float32, device=DEV)
+        K().gemm_tc(a, w, out, w_tiles=K().tile_weight(w), ahead=ahead)
+        assert torch.equal(out, outs[1])
+    assert K().gemm_tc_status(a.device) == 0
     exact = a.double().cpu() @ w.double().cpu().T
     assert (outs[0].double().cpu() - exact).abs().max().item() <= 1e-4 * max(1.0, exact.abs().max().item())
 
