@@ -397,7 +397,9 @@ struct DecodeItem {
     bool visible;
 };
 
-template <int HD>
+// WIDE: a group has more than 8 query heads (both row halves of the 16-row tile are worked on); a kernel of its own,
+// so that the usual one carries half as much code (short kernels pay for the instructions they fetch).
+template <int HD, bool WIDE>
 __global__ void __launch_bounds__(DecodeTma<HD>::kThreads, 1)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const __nv_bfloat16* __restrict__ q, const int* __restrict__ rows, int n_rows,
@@ -589,11 +591,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                         asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(kv_addr<HD, kTile, true>(v_tile, row, c)), "r"(0) : "memory");
                 }
                 __syncwarp();
-                if (G <= 8) warp_tile_step<HD, kTile, true, true, false>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
-                else warp_tile_step<HD, kTile, true, true, true>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
+                warp_tile_step<HD, kTile, true, true, WIDE>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
             } else {
-                if (G <= 8) warp_tile_step<HD, kTile, true, false, false>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
-                else warp_tile_step<HD, kTile, true, false, true>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
+                warp_tile_step<HD, kTile, true, false, WIDE>(q_frag, k_tile, v_tile, key0, row_lo, row_pos, scale_log2, o, m, l, lane, off);
             }
             __syncwarp();                                   // every lane is done reading the stage
             if (lane == 0 && tile == ci.tile0) timeline_record(kTlAttentionDecode, 3);
@@ -1026,7 +1026,8 @@ static int launch_decode_tma(const void* q, const void* kc, const void* vc, void
     using Cfg = DecodeTma<HD>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
         if (e != cudaSuccess) { set_error("attention_decode: %s", cudaGetErrorString(e)); return 1; }
         configured = true;
     }
@@ -1042,7 +1043,13 @@ static int launch_decode_tma(const void* q, const void* kc, const void* vc, void
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int items = n_rows * Hkv * n_chunks;
     int grid = items < sms ? items : sms;           // few items: fewer per CTA rather than fewer CTAs
-    launch_kernel((attention_decode_tma_kernel<HD>), dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, mk, mv,
+    if (H / Hkv > 8)
+        launch_kernel((attention_decode_tma_kernel<HD, true>), dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, mk, mv,
+                  static_cast<const __nv_bfloat16*>(q), rows, n_rows, row_req, positions, tables, table_stride, H, Hkv,
+                  page_size, scale * kLog2e, window, part_o, part_ml, max_chunks, n_chunks, static_cast<__nv_bfloat16*>(out), status,
+                  (g_stream_kv && n_rows <= 32) ? 1 : 0);     // measured: 2 % faster at 8 requests, no gain at 64
+    else
+        launch_kernel((attention_decode_tma_kernel<HD, false>), dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, mk, mv,
                   static_cast<const __nv_bfloat16*>(q), rows, n_rows, row_req, positions, tables, table_stride, H, Hkv,
                   page_size, scale * kLog2e, window, part_o, part_ml, max_chunks, n_chunks, static_cast<__nv_bfloat16*>(out), status,
                   (g_stream_kv && n_rows <= 32) ? 1 : 0);     // measured: 2 % faster at 8 requests, no gain at 64
