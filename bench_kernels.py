@@ -9,6 +9,7 @@ Cases at the layer sizes of one of bench.py's shapes (random data, sizes larger 
   attention_prefill  one prompt of T tokens, with the mma.sync kernel and with the tcgen05 kernel
   decode_step        R whole decode steps of B requests at context C through the step function
   prefill_step       R whole prefills of T tokens through the step function
+  prefill_timeline   the same for a prompt portion of T tokens on top of C cached positions
   decode_timeline    one graph-replayed decode step of B requests at context C, seen from inside: the kernels of a library
                      built with time stamps (it is compiled at the first call) record when their blocks enter, wait, compute
                      and leave; prints one line per launch of the layers --from-launch .. --to-launch
@@ -155,7 +156,7 @@ def step_case(kind, shape_cfg, batch, context, tokens, layers, repeat):
         _time(f"prefill step T={tokens} layers={cfg['num_hidden_layers']}", run, repeat)
 
 
-def timeline_case(shape_cfg, batch, context, layers, first, last):
+def timeline_case(shape_cfg, batch, context, layers, first, last, tokens=0):
     from geneinfer_b200.ops import library
     library.use_timeline_build()
     from geneinfer_b200 import Engine
@@ -163,17 +164,24 @@ def timeline_case(shape_cfg, batch, context, layers, first, last):
     from geneinfer_b200.ops import kernels, timeline
     cfg = dict(shape_cfg, num_hidden_layers=layers or shape_cfg["num_hidden_layers"])
     folder = bench.model_folder(cfg)
+    if tokens:
+        batch = 1
+        context = context + 10 * tokens
     llm = Engine(folder, dtype="bfloat16", max_seq_len=context, page_size=PAGE, kv_pages=batch * ((context + PAGE - 1) // PAGE),
-                 max_running=batch, step_tokens=max(batch, 16), prefix_cache=False)
+                 max_running=batch, step_tokens=max(batch, 16, tokens), prefix_cache=False)
     eng = llm.steps
     keys = [f"b{i}" for i in range(batch)]
-    bench.fill_cache(eng, keys, context - 12)
+    bench.fill_cache(eng, keys, context - (10 * tokens if tokens else 12))
     ids = torch.zeros(batch, dtype=torch.int32, device="cuda:0")
+    portion = torch.randint(0, V, (max(tokens, 1),)).tolist()
 
     def run(i):
-        logits = eng.step([StepEntry(k, [17 + i], [0]) for k in keys])
+        if tokens:                               # a portion of a prompt on top of the cached positions
+            logits = eng.step([StepEntry(keys[0], portion, [tokens - 1])])
+        else:
+            logits = eng.step([StepEntry(k, [17 + i], [0]) for k in keys])
         kernels.argmax(logits, ids)
-    for i in range(6):                           # the step's graph is captured and replayed a few times
+    for i in range(6):                           # the step's graph (or launch programs) are made and repeated a few times
         run(i)
     rec = timeline.Recorder(eng.device)
     run(6)
@@ -182,7 +190,8 @@ def timeline_case(shape_cfg, batch, context, layers, first, last):
     records = rec.records()
     found = timeline.launches(records)
     span = records[:, 3].max() / 1000 if len(records) else 0.0
-    print(f"decode step B={batch} context={context} layers={cfg['num_hidden_layers']}: {len(records)} records of {len(found)} "
+    what = f"portion of {tokens} tokens after {context - 10 * tokens + 7 * tokens} cached ones" if tokens else f"decode step B={batch} context={context}"
+    print(f"{what}, layers={cfg['num_hidden_layers']}: {len(records)} records of {len(found)} "
           f"launches over {span:.1f} us (the time stamps themselves cost a few per cent)")
     print(timeline.table(found, first, min(last, len(found))))
 
@@ -190,7 +199,7 @@ def timeline_case(shape_cfg, batch, context, layers, first, last):
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     ap.add_argument("case", choices=["gemm_prefill", "gemm_decode", "attention_decode", "attention_prefill", "decode_step",
-                                     "prefill_step", "decode_timeline"])
+                                     "prefill_step", "decode_timeline", "prefill_timeline"])
     ap.add_argument("--shape", choices=sorted(bench.SHAPES), default="1b")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -201,7 +210,7 @@ def main() -> int:
     ap.add_argument("--to-launch", type=int, default=40, help="decode_timeline: the launch after the last one to print")
     ap.add_argument("--no-pairs", action="store_true", help="many-token products on single CTAs instead of pairs (cta_group::2)")
     a = ap.parse_args()
-    if a.case == "decode_timeline":              # before anything loads the ordinary library
+    if a.case in ("decode_timeline", "prefill_timeline"):              # before anything loads the ordinary library
         from geneinfer_b200.ops import library
         library.use_timeline_build()
     from geneinfer_b200.ops import kernels
@@ -219,6 +228,8 @@ def main() -> int:
         attention_prefill_case(a.tokens, a.repeat, dev, kernels)
     elif a.case == "decode_timeline":
         timeline_case(shape_cfg, a.batch, a.context, a.layers, a.from_launch, a.to_launch)
+    elif a.case == "prefill_timeline":
+        timeline_case(shape_cfg, 1, a.context, a.layers, a.from_launch, a.to_launch, tokens=a.tokens)
     else:
         step_case(a.case, shape_cfg, a.batch, a.context, a.tokens, a.layers, a.repeat)
     status = kernels.gemm_tc_status(dev)

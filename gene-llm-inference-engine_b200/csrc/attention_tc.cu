@@ -200,7 +200,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + KEYS;
+    if (threadIdx.x == 0) timeline_record(kTlAttentionPrefill, 0);
     pdl_prologue();
+    if (threadIdx.x == 0) timeline_record(kTlAttentionPrefill, 1);
 
     const int t0 = work[blockIdx.y * 3], n_tok = work[blockIdx.y * 3 + 1], req = work[blockIdx.y * 3 + 2];
     const int n_rows = n_tok * G;
@@ -490,6 +492,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::kTmemCols);
+        if (lane == 0) timeline_record(kTlAttentionPrefill, 6);
     }
 }
 
@@ -522,6 +525,7 @@ static int launch(const void* q, const void* kc, const void* vc, void* out, cons
 }  // namespace gi
 
 using namespace gi;
+GI_TIMELINE_SETTER(gi_timeline_set_attention_tc)
 
 // Whether the tcgen05 prefill kernel serves this shape: head size 64 or 128, at most 128 query
 // heads per key/value head, pages that TMA boxes can tile.

@@ -79,7 +79,11 @@ __device__ __forceinline__ void timeline_record(int kernel_id, int event) {
 __device__ __forceinline__ void timeline_record(int, int) {}
 #define GI_TIMELINE_SETTER(name) extern "C" int name(void*) { return 2; }
 #endif
-enum TimelineKernel : int { kTlRmsNorm = 1, kTlSwiGLU = 2, kTlAttentionDecode = 3, kTlProduct = 100 /* + the form (TcSpecKind) */ };
+enum TimelineKernel : int {
+    kTlRmsNorm = 1, kTlSwiGLU = 2, kTlAttentionDecode = 3, kTlAddRanges = 4, kTlRopeStore = 5, kTlAttentionPrefill = 6,
+    kTlProduct = 100,            // + the form (TcSpecKind) of the few-token product
+    kTlProductManyTokens = 200,  // + 2 * epilogue (TcEpilogue) + (1 on pairs of CTAs)
+};
 
 __device__ __forceinline__ void pdl_prologue() { pdl_launch_dependents(); pdl_wait(); }
 

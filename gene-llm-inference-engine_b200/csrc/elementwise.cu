@@ -217,7 +217,9 @@ rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positio
                   const float* __restrict__ sin_t, int rot_half, int interleaved,
                   TQ* __restrict__ q_out, TKV* __restrict__ k_cache, TKV* __restrict__ v_cache,
                   int H, int Hkv, int hd, int page_size, int write_kv) {
+    if (threadIdx.x == 0) timeline_record(kTlRopeStore, 0);
     pdl_prologue();
+    if (threadIdx.x == 0) timeline_record(kTlRopeStore, 1);
     const int t = blockIdx.x;
     const int pos = positions[t];
     const float* row = qkv + static_cast<size_t>(t) * (H + 2 * Hkv) * hd;

@@ -865,6 +865,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_kb = (p.K + kBlockK - 1) / kBlockK;
+    constexpr int kTl = kTlProductManyTokens + 2 * EPI + (PAIR ? 1 : 0);
+    if (threadIdx.x == 0) timeline_record(kTl, 0);
     // PAIR: the two CTAs of a cluster walk over the same work items; rank r takes rows 128 r .. 128 r + 127 of a
     // 256-row tile of tokens and fetches rows r BLOCK_Q/2 .. of the weights' tile; p.tiles_p counts 256-row tiles.
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
@@ -899,6 +901,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
     grid_launch_dependents();
     if (PAIR) cluster_sync_all();    // both CTAs' barriers exist before either signals the other's
     grid_dependency_wait();          // everything below reads what earlier kernels wrote
+    if (threadIdx.x == 0) timeline_record(kTl, 1);
     // the first CTA's barriers as the other CTA addresses them: "stage full" counts both CTAs' bytes there, and
     // "accumulator empty" both CTAs' epilogue threads
     auto leader_bar = [&](int i) { return PAIR ? cluster_map(smem_u32(&bars[i]), 0u) : smem_u32(&bars[i]); };
@@ -979,6 +982,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                         break;
                     }
                     tc_fence_after();
+                    if (it == 0) timeline_record(kTl, 2);
                     const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes);
                     const uint64_t desc_p = umma_desc(a_addr);
                     const uint64_t desc_q = umma_desc(a_addr + Cfg::kStageBytesP);
@@ -995,6 +999,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                     else umma_commit(smem_u32(&bars[2 * kStages + buf]));
                 }
             }
+            timeline_record(kTl, 3);
         }
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..9)
@@ -1050,6 +1055,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
             group_sync();
             if (!ok) break;
             tc_fence_after();
+            if (j == 0 && warp == 2 && lane == 0) timeline_record(kTl, 4);
             const uint32_t tmem_d = tmem_base + buf * Cfg::kAccStride + lane_addr;
             if constexpr (EPI == kEpiRopeStore) {
                 // A thread holds one token's row of the tile: whole heads (BLOCK_Q is a multiple of the head
@@ -1178,9 +1184,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
             }
         }
         if (leader) bulk_wait_all();
+        if (warp == 2 && lane == 0) timeline_record(kTl, 5);
         tc_fence_before();
     }
     __syncthreads();
+    if (threadIdx.x == 0) timeline_record(kTl, 6);
     if (PAIR) cluster_sync_all();    // neither CTA leaves (or frees tensor memory) while the other may still signal it
     if (warp == 1) {
         tc_fence_after();
@@ -1573,7 +1581,9 @@ extern "C" int gi_gemm_tc_status(const void* status, void* stream, int* out) {
 // C[m, n] (+)= ws[0][m][n] + ws[1][m][n] + ... in this order: the ranges of K of a split product.
 __global__ void reduce_splits_kernel(const float* __restrict__ ws, float* __restrict__ C, int M, int N4, long long ldc,
                                      long long split_stride, int splits, int accumulate) {
+    if (threadIdx.x == 0) timeline_record(kTlAddRanges, 0);
     pdl_prologue();
+    if (threadIdx.x == 0) timeline_record(kTlAddRanges, 1);
     const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= static_cast<long long>(M) * N4) return;
     const int m = static_cast<int>(i / N4), n4 = static_cast<int>(i % N4);
@@ -1588,6 +1598,7 @@ __global__ void reduce_splits_kernel(const float* __restrict__ ws, float* __rest
     for (int s = 0; s < 8; ++s)
         if (s < splits) { v.x += part[s].x; v.y += part[s].y; v.z += part[s].z; v.w += part[s].w; }
     *c = v;
+    if (threadIdx.x == 0) timeline_record(kTlAddRanges, 6);
 }
 
 // Many tokens, one persistent CTA per SM. epilogue 0: C[M,N] = A W^T (32-bit); 1: C += A W^T (32-bit);

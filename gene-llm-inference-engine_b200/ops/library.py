@@ -51,6 +51,7 @@ _SIGNATURES = {
     "gi_gemm_tc_set_stream_weights": [c_int],
     "gi_gemm_tc_set_specialised": [c_int],
     "gi_timeline_set_gemm": [c_void_p], "gi_timeline_set_elementwise": [c_void_p], "gi_timeline_set_attention": [c_void_p],
+    "gi_timeline_set_attention_tc": [c_void_p],
     "gi_attention_set_stream_kv": [c_int],
     "gi_gemm_tc_cluster_capacity": [c_int, c_int, c_int],
     "gi_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,

@@ -1,7 +1,7 @@
 """A step's timeline from time stamps that the kernels take themselves.
 
 Built with ``-DGI_TIMELINE`` (``library.use_timeline_build()``, a library of its own beside the ordinary one), the
-kernels of a decode step record (kernel, event, block, %globaltimer) at a few places: a block enters, its wait for the
+kernels of a step record (kernel, event, block, %globaltimer) at a few places: a block enters, its wait for the
 kernel ahead is over, its first operands have arrived, its last MMA is issued, the accumulator is complete, its results
 are stored, it leaves. This shows what no per-kernel profile shows: how the kernels of a step overlap (programmatic
 dependent launch lets a block enter, and fetch weights, long before it may read what the kernel ahead writes), what
@@ -16,12 +16,18 @@ import torch
 
 from .library import lib
 
-KERNELS = {1: "rmsnorm", 2: "swiglu", 3: "attention_decode", 100: "product (any form)", 101: "product qkv+rope",
-           102: "product add", 103: "product store"}
+KERNELS = {1: "rmsnorm", 2: "swiglu", 3: "attention_decode", 4: "add ranges", 5: "rope_store", 6: "attention_prefill",
+           100: "product (any form)", 101: "product qkv+rope", 102: "product add", 103: "product store",
+           200: "products store", 201: "products store (pairs)", 202: "products add", 203: "products add (pairs)",
+           204: "products swiglu", 205: "products swiglu (pairs)", 206: "products rope", 207: "products rope (pairs)"}
 EVENTS = {"rmsnorm": {0: "enter", 1: "waited", 6: "leave"}, "swiglu": {0: "enter", 1: "waited", 6: "leave"},
           "attention_decode": {0: "enter", 1: "waited", 2: "queries loaded", 3: "first tile done", 4: "last tile done", 6: "leave"},
+          "add ranges": {0: "enter", 1: "waited", 6: "leave"}, "rope_store": {0: "enter", 1: "waited"},
+          "attention_prefill": {0: "enter", 1: "waited", 6: "leave"},
           "product": {0: "enter", 1: "waited", 2: "first operands", 3: "last MMA issued", 4: "accumulator ready",
-                      5: "results stored", 6: "leave"}}
+                      5: "results stored", 6: "leave"},
+          "products": {0: "enter", 1: "waited", 2: "first operands", 3: "last MMA issued", 4: "first accumulator ready",
+                       5: "results stored", 6: "leave"}}
 
 
 class Recorder:
@@ -30,7 +36,8 @@ class Recorder:
     def __init__(self, device: torch.device, capacity: int = 1 << 19):
         self.buffer = torch.zeros(2 + 2 * capacity, dtype=torch.int64, device=device)
         self.buffer[1] = capacity
-        for setter in ("gi_timeline_set_gemm", "gi_timeline_set_elementwise", "gi_timeline_set_attention"):
+        for setter in ("gi_timeline_set_gemm", "gi_timeline_set_elementwise", "gi_timeline_set_attention",
+                       "gi_timeline_set_attention_tc"):
             code = getattr(lib(), setter)(self.buffer.data_ptr())
             if code == 2:
                 raise RuntimeError("this library was built without time stamps: call library.use_timeline_build() first")
@@ -76,11 +83,11 @@ def table(all_launches: List[Dict], first: int, last: int) -> str:
     lines = []
     for n, launch in enumerate(all_launches[first:last], first):
         name = KERNELS.get(launch["kernel"], str(launch["kernel"]))
-        events = EVENTS["product" if name.startswith("product") else name]
+        events = EVENTS["products" if name.startswith("products") else "product" if name.startswith("product") else name]
         cells = []
         for event, label in events.items():
             stamps = [b[event] / 1000 for b in launch["blocks"].values() if event in b]
             if stamps:
                 cells.append(f"{label} {min(stamps):.2f}..{max(stamps):.2f}")
-        lines.append(f"{n:4d} {name:18s} {len(launch['blocks']):4d} blocks | " + " | ".join(cells))
+        lines.append(f"{n:4d} {name:24s} {len(launch['blocks']):4d} blocks | " + " | ".join(cells))
     return "\n".join(lines)
