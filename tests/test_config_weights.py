@@ -223,3 +223,23 @@ def test_bench_says_that_it_runs_on_one_gpu():
     p = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--gpus", "2", "--steps", "2", "--warmup", "1"],
                        capture_output=True, text=True, timeout=120)
     assert p.returncode == 2 and len(p.stdout.strip().splitlines()) == 1 and "one GPU" in p.stdout
+
+
+def test_timeline_records_are_grouped_into_launches():
+    """ops/timeline.py: time-ordered records of (kernel, event, block, ns) become launches (a kernel's launch ends where one
+    of its blocks enters again), per block the first stamp of an event and, for leaving, the last warp's."""
+    import numpy as np
+    from geneinfer_b200.ops import timeline
+    rec = np.array([
+        [1, 0, 0, 0], [1, 0, 1, 10], [101, 0, 0, 20], [1, 1, 0, 100], [1, 1, 1, 110], [1, 6, 0, 200], [1, 6, 1, 210],
+        [101, 1, 0, 300], [101, 2, 0, 350], [101, 6, 0, 400], [101, 6, 0, 450],      # two warps leave: the later one counts
+        [1, 0, 0, 500], [1, 1, 0, 600], [1, 1, 0, 650], [1, 6, 0, 700],              # block 0 enters again: a new launch
+    ], dtype=np.int64)
+    found = timeline.launches(rec)
+    assert [(l["kernel"], sorted(l["blocks"])) for l in found] == [(1, [0, 1]), (101, [0]), (1, [0])]
+    assert found[0]["blocks"][1] == {0: 10, 1: 110, 6: 210}
+    assert found[1]["blocks"][0] == {0: 20, 1: 300, 2: 350, 6: 450}
+    assert found[2]["blocks"][0] == {0: 500, 1: 600, 6: 700}
+    text = timeline.table(found, 0, 3).splitlines()
+    assert len(text) == 3 and "rmsnorm" in text[0] and "2 blocks" in text[0] and "waited 0.10..0.11" in text[0]
+    assert "product qkv+rope" in text[1] and "first operands 0.35..0.35" in text[1]

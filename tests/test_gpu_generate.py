@@ -158,3 +158,20 @@ def test_command_line(tmp_path):
     assert bad.returncode == 2 and "tokenizer" in bad.stderr
     missing = subprocess.run(cmd[:2] + ["--model", str(tmp_path / "nothing"), "--prompt-ids", "1"], capture_output=True, text=True)
     assert missing.returncode == 1 and "config.json" in missing.stderr
+
+
+def test_decode_timeline_from_inside_the_kernels():
+    """bench_kernels.py decode_timeline: the library variant with time stamps is built, a decode step is recorded,
+    and every kernel of a layer shows up with its events in order."""
+    cmd = [sys.executable, os.path.join(ROOT, "bench_kernels.py"), "decode_timeline", "--batch", "2", "--context", "64",
+           "--layers", "2", "--from-launch", "0", "--to-launch", "20"]
+    run = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-2000:]
+    lines = [l for l in run.stdout.splitlines() if " blocks | " in l]
+    kinds = {l.split(" blocks | ")[0].split(None, 1)[1].rsplit(None, 1)[0].strip() for l in lines}
+    assert {"rmsnorm", "product qkv+rope", "attention_decode", "product add", "product store", "swiglu"} <= kinds, run.stdout
+    for l in lines:
+        if "product add" in l:
+            stamps = [float(cell.split()[-1].split("..")[0]) for cell in l.split(" | ")[1:]]
+            assert stamps == sorted(stamps), f"events out of order: {l}"
+    assert "status word: 0" in run.stdout
