@@ -194,6 +194,24 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, TOut* __restrict__ o
     if (threadIdx.x == 0) timeline_record(kTlSwiGLU, 6);
 }
 
+// The same, four channels to a thread with 16-byte accesses (I a multiple of 4, pointers aligned): a quarter of the
+// blocks (64 tokens of the Llama-3.2-1B shape: 512 blocks in one round instead of 2,048 in two).
+template <typename TOut>
+__global__ void swiglu4_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int I4, size_t total4) {
+    if (threadIdx.x == 0) timeline_record(kTlSwiGLU, 0);
+    pdl_prologue();
+    if (threadIdx.x == 0) timeline_record(kTlSwiGLU, 1);
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total4) return;
+    const size_t t = i / I4;
+    const int c = static_cast<int>(i % I4);
+    const float4* row = reinterpret_cast<const float4*>(gu) + t * 2 * I4;
+    const float4 g = row[c], u = row[I4 + c];
+    store4<TOut>(out + 4 * i, g.x * (1.0f / (1.0f + expf(-g.x))) * u.x, g.y * (1.0f / (1.0f + expf(-g.y))) * u.y,
+                 g.z * (1.0f / (1.0f + expf(-g.z))) * u.z, g.w * (1.0f / (1.0f + expf(-g.w))) * u.w);
+    if (threadIdx.x == 0) timeline_record(kTlSwiGLU, 6);
+}
+
 // ---------------------------------------------------------------------------------- RoPE + store
 __device__ __forceinline__ void store4(float* dst, const float4 v) { *reinterpret_cast<float4*>(dst) = v; }
 __device__ __forceinline__ void store4(__nv_bfloat16* dst, const float4 v) {
@@ -373,10 +391,14 @@ static int gi_swiglu_impl(const float* gate_up, void* out, int out_dtype, int T,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t total = static_cast<size_t>(T) * I;
     const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+    const bool by4 = I % 4 == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+    const unsigned blocks4 = static_cast<unsigned>((total / 4 + 255) / 256);
     if (out_dtype == kF32) {
-        launch_kernel((swiglu_kernel<float>), dim3(blocks), dim3(256), 0, st, gate_up, static_cast<float*>(out), I, total);
+        if (by4) launch_kernel((swiglu4_kernel<float>), dim3(blocks4), dim3(256), 0, st, gate_up, static_cast<float*>(out), I / 4, total / 4);
+        else launch_kernel((swiglu_kernel<float>), dim3(blocks), dim3(256), 0, st, gate_up, static_cast<float*>(out), I, total);
     } else if (out_dtype == kBF16) {
-        launch_kernel((swiglu_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, st, gate_up, static_cast<__nv_bfloat16*>(out), I, total);
+        if (by4) launch_kernel((swiglu4_kernel<__nv_bfloat16>), dim3(blocks4), dim3(256), 0, st, gate_up, static_cast<__nv_bfloat16*>(out), I / 4, total / 4);
+        else launch_kernel((swiglu_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, st, gate_up, static_cast<__nv_bfloat16*>(out), I, total);
     } else {
         GI_REQUIRE(false, "swiglu: unsupported output dtype code %d", out_dtype);
     }

@@ -59,7 +59,7 @@ def test_rmsnorm(out_dtype, T, D, eps):
 
 
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("T,I", [(1, 16), (9, 160), (64, 1000)])
+@pytest.mark.parametrize("T,I", [(1, 16), (9, 160), (64, 1000), (5, 30), (3, 8192 + 2)])
 def test_swiglu(out_dtype, T, I):
     g = torch.Generator().manual_seed(3)
     gu = (torch.randn(T, 2 * I, generator=g) * 4).to(DEV)
