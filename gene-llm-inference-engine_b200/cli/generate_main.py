@@ -14,11 +14,13 @@ from typing import List, Optional
 
 USAGE = (
     "usage: gi_generate --model DIR (--prompt-ids \"1 2 3\" | --prompt-ids-file FILE) [--steps N] [--max-seq-len N]\n"
-    "                   [--weights native|f32] [--device cuda] [--profile] [--temperature F] [--top-k N] [--top-p F]\n"
-    "                   [--seed N] [--stop-ids \"2 7\"] [--page-size N] [--kv-pages N] [--no-echo] [--quiet]\n"
-    "                   [--dump-tokens FILE]\n"
+    "                   [--weights native|f32 | --dtype bf16|fp32] [--device cuda] [--profile] [--temperature F]\n"
+    "                   [--top-k N] [--top-p F] [--seed N] [--stop-ids \"2 7\"] [--page-size N] [--kv-pages N]\n"
+    "                   [--no-echo] [--quiet] [--dump-tokens FILE] [--random-weights SEED --config FILE]\n"
     "  DIR holds config.json and model.safetensors. --steps is the maximum number of positions including the\n"
-    "  prompt (default: the context length). --weights f32 runs the whole model in true 32-bit.\n")
+    "  prompt (default: the context length). --weights f32 (= --dtype fp32) runs the whole model in true 32-bit.\n"
+    "  --random-weights SEED --config FILE first writes such a folder (random bfloat16 weights from the seed, for the\n"
+    "  configuration in FILE, a config.json) to DIR, or to a temporary folder when no --model is given.\n")
 
 
 class UsageError(Exception):
@@ -49,7 +51,8 @@ def _ids(flag: str, text: str) -> List[int]:
 def parse(argv: List[str]) -> dict:
     o = {"model": "", "prompt_ids": None, "steps": 0, "max_seq_len": 0, "weights": "native", "device": "cuda",
          "profile": False, "temperature": 0.8, "top_k": 0, "top_p": 0.9, "seed": None, "stop_ids": [],
-         "page_size": 16, "kv_pages": None, "echo": True, "quiet": False, "dump_tokens": ""}
+         "page_size": 16, "kv_pages": None, "echo": True, "quiet": False, "dump_tokens": "", "random_weights": None,
+         "config": "", "help": False}
     i = 0
     while i < len(argv):
         flag = argv[i]
@@ -79,6 +82,14 @@ def parse(argv: List[str]) -> dict:
         elif flag == "--steps": o["steps"] = _int(flag, value())
         elif flag == "--max-seq-len": o["max_seq_len"] = _int(flag, value())
         elif flag == "--weights": o["weights"] = value()
+        elif flag == "--dtype":
+            name = value().lower()
+            if name not in ("bf16", "bfloat16", "fp32", "f32", "float32"):
+                raise UsageError("--dtype must be bf16 or fp32")
+            o["weights"] = "native" if name in ("bf16", "bfloat16") else "f32"
+        elif flag == "--random-weights": o["random_weights"] = _int(flag, value())
+        elif flag == "--config": o["config"] = value()
+        elif flag in ("--help", "-h"): o["help"] = True
         elif flag == "--device": o["device"] = value()
         elif flag == "--profile": o["profile"] = True
         elif flag == "--temperature": o["temperature"] = _float(flag, value())
@@ -94,7 +105,11 @@ def parse(argv: List[str]) -> dict:
         else:
             raise UsageError(f"unknown option {flag}")
         i += 1
-    if not o["model"]:
+    if o["help"]:
+        return o
+    if (o["random_weights"] is None) != (not o["config"]):
+        raise UsageError("--random-weights SEED and --config FILE go together")
+    if not o["model"] and o["random_weights"] is None:
         raise UsageError("--model is required")
     if not o["prompt_ids"]:
         raise UsageError("--prompt-ids or --prompt-ids-file is required (at least one token id)")
@@ -113,10 +128,31 @@ def main(argv: Optional[List[str]] = None) -> int:
     except UsageError as e:
         sys.stderr.write(f"error: {e}\n{USAGE}")
         return 2
+    if o["help"]:
+        sys.stdout.write(USAGE)
+        return 0
+    scratch_folder = None
     try:
         import torch
         from ..engine.generate import Engine
         from ..sampling.params import SamplingParams
+        if o["random_weights"] is not None:
+            # the random-weights mode: a model folder from a configuration and a seed, then everything as usual
+            import json
+            import tempfile
+            from ..weights import write_random_model
+            try:
+                with open(o["config"]) as f:
+                    config_json = json.load(f)
+            except (OSError, ValueError) as e:
+                sys.stderr.write(f"error: cannot read the configuration {o['config']}: {e}\n")
+                return 2
+            if not o["model"]:
+                scratch_folder = tempfile.TemporaryDirectory(prefix="gi_generate_random_")
+                o["model"] = scratch_folder.name
+            write_random_model(config_json, o["random_weights"], o["model"], "bfloat16")
+            if not o["quiet"]:
+                sys.stderr.write(f"[random weights] seed {o['random_weights']}, folder {o['model']}\n")
         try:
             params = SamplingParams(o["temperature"], o["top_k"], o["top_p"], o["seed"])
         except ValueError as e:
@@ -174,6 +210,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     except Exception as e:   # runtime errors: bad model folder, kernels cannot be built, no GPU ...
         sys.stderr.write(f"error: {e}\n")
         return 1
+    finally:
+        if scratch_folder is not None:
+            scratch_folder.cleanup()
 
 
 if __name__ == "__main__":

@@ -158,6 +158,24 @@ def test_command_line(tmp_path):
     assert bad.returncode == 2 and "tokenizer" in bad.stderr
     missing = subprocess.run(cmd[:2] + ["--model", str(tmp_path / "nothing"), "--prompt-ids", "1"], capture_output=True, text=True)
     assert missing.returncode == 1 and "config.json" in missing.stderr
+    # the random-weights mode: a folder from a configuration and a seed, the same tokens from the same seed,
+    # the folder kept when --model names it
+    import json
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(tc.TINY_B))
+    made = tmp_path / "made"
+    runs = []
+    for extra in (["--model", str(made)], [], ["--dtype", "fp32"]):
+        r = subprocess.run(cmd[:2] + ["--random-weights", "11", "--config", str(cfg_file), "--prompt-ids", "5 9 2", "--steps", "9",
+                                      "--temperature", "0", "--no-echo"] + extra, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr
+        runs.append([int(t) for t in r.stdout.split()])
+    assert len(runs[0]) == 7 and runs[0] == runs[1]        # positions 3..8 fed, the token after the last one also sampled
+    assert (made / "config.json").is_file() and (made / "model.safetensors").is_file()
+    assert sum(a != b for a, b in zip(runs[0], runs[2])) <= 2          # 32-bit on the same weights: near-ties at most
+    alone = subprocess.run(cmd[:2] + ["--random-weights", "11", "--prompt-ids", "1"], capture_output=True, text=True)
+    assert alone.returncode == 2 and "go together" in alone.stderr
+    assert subprocess.run(cmd[:2] + ["--help"], capture_output=True, text=True).returncode == 0
 
 
 def test_decode_timeline_from_inside_the_kernels():
