@@ -390,7 +390,7 @@ def test_gemm_tensor_cores_refuses_what_tma_cannot_address():
 
 
 @pytest.mark.parametrize("H,Hkv,hd,ps", [(4, 2, 16, 16), (3, 1, 32, 8), (8, 2, 64, 16), (32, 8, 64, 16), (8, 2, 128, 32), (5, 5, 64, 4),
-                                          (16, 1, 32, 16)])
+                                          (16, 1, 32, 16), (12, 1, 64, 16), (18, 2, 128, 16)])
 def test_attention_tensor_cores_mixed_rows(H, Hkv, hd, ps):
     """The mma kernels on a whole prompt, single tokens deep in long contexts (several chunks, a
     chunk edge, a tile edge), a portion over page edges, and position 0 alone."""
