@@ -4,6 +4,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 1b|3b|8b] [--layers L]
     python bench.py --scenario mixed|prefix [--shape ...] [--dtype bfloat16|float32]
                                         (continuous batching / shared prefixes through the scheduler, see run_scenario)
+    python bench.py --scenario sizes [--shape ...]   (decode steps at a grid of batch sizes and contexts, see run_sizes)
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 and context 8192, timed on
 the device over exactly K decode steps (one step = one token for every request of the batch);
@@ -350,6 +351,40 @@ def run_ours(args):
     return 0
 
 
+def run_sizes(args):
+    """Decode steps of the step function at a grid of batch sizes and context lengths (device time per step with CUDA
+    events, the same timing as the default run's), each with its fraction of the HBM roofline. Prints one JSON line."""
+    import torch
+    from geneinfer_b200 import Engine
+    shape_name, shape = SHAPES[args.shape]
+    cfg = dict(shape)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    pk = peaks()
+    folder = model_folder(cfg)
+    vocab = cfg["vocab_size"]
+    contexts = (128, 2048, CONTEXT, 4 * CONTEXT)
+    points = []
+    for batch in (1, 4, 8, 16, 32, 64):
+        longest = max(c for c in contexts if batch * c <= 8 * 4 * CONTEXT)          # at most 256 Ki cached positions
+        llm = Engine(folder, dtype="bfloat16", max_seq_len=longest, page_size=PAGE, kv_pages=batch * ((longest + PAGE - 1) // PAGE),
+                     max_running=batch, step_tokens=max(batch, 16), prefix_cache=False)
+        for context in contexts:
+            if context > longest:
+                continue
+            ms, _ = time_decode_device(llm.steps, batch, context, args.steps, args.warmup, vocab)
+            achieved = step_bytes(llm.model, cfg, batch, context) / (ms * 1e-3) / 1e9
+            points.append({"batch": batch, "context": context, "ms_per_step": round(ms, 4), "tok_s": round(batch / ms * 1e3, 1),
+                           "gb_s": round(achieved, 1), "frac": round(achieved / pk["hbm_gbs"], 4)})
+        llm.steps.check_status()
+        del llm
+        torch.cuda.empty_cache()
+    print(json.dumps({"metric": f"decode steps at a grid of sizes ({shape_name} shape, random bf16 weights)", "impl": "ours", "n_gpus": 1,
+                      "dtype": "bf16", "steps": args.steps, "warmup": args.warmup, "peak_gb_s": pk["hbm_gbs"],
+                      "peaks": pk["source"], "points": points}))
+    return 0
+
+
 def run_scenario(args):
     """Two workloads through the entry point, beside the default run: ``mixed`` (32 requests with
     prompts of 128 to 4096 random ids and 256 generated tokens each, admitted together, prompts cut
@@ -560,7 +595,8 @@ def main():
     ap.add_argument("--shape", choices=sorted(SHAPES), default="1b", help="layer sizes (the default is the baseline's third configuration)")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="precision of a --scenario run (float32: the requests run alone must give identical tokens)")
-    ap.add_argument("--scenario", choices=["mixed", "prefix"], default="", help="a workload through the scheduler instead of the default run")
+    ap.add_argument("--scenario", choices=["mixed", "prefix", "sizes"], default="",
+                    help="a workload through the scheduler (mixed, prefix) or decode steps at a grid of sizes, instead of the default run")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -568,6 +604,8 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.scenario == "sizes":
+        return run_sizes(args)
     if args.scenario:
         return run_scenario(args)
     return run_ours(args)

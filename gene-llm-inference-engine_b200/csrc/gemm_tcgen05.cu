@@ -165,10 +165,10 @@ struct TcConfig {
     static constexpr int kStageBytesP = kBlockBytesP * kKb;
     static constexpr int kStageBytesQ = kBlockBytesQ * kKb;
     static constexpr int kStageBytes = kStageBytesP + kStageBytesQ;
-    static constexpr int kStages = TILED ? ((BLOCK_Q >= 128) ? 3 : (BLOCK_Q >= 64) ? 4 : 5)
+    static constexpr int kStages = TILED ? ((BLOCK_Q >= 128) ? 3 : (BLOCK_Q >= 32) ? 4 : 5)
                                          : ((BLOCK_Q >= 256) ? 4 : (BLOCK_Q >= 128) ? 6 : 8);
     static constexpr int kTmemCols = BLOCK_Q < 32 ? 32 : BLOCK_Q;
-    static constexpr int kSideBytes = 512;      // barriers and flags (the first 256), the tokens' positions and page rows of a rotating 16-token product
+    static constexpr int kSideBytes = 768;      // barriers and flags (the first 256), the tokens' positions (128) and page rows (256) of a rotating product of up to 32 tokens
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment */ + kSideBytes;
     // A cluster's split 0 receives the partial tiles of the other splits, [split - 1][q][128 rows], in its
     // pipeline stages once its own products are done with them (it tells the others when); behind them
@@ -310,7 +310,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     const bool prefetch_p = Spec::fixed ? true : p.prefetch_p != 0;
     const bool stream_p = Spec::fixed ? true : p.stream_p != 0;
     const int n_splits = (Spec::fixed && Spec::one_split) ? 1 : p.splits;
-    if (threadIdx.x == 0) timeline_record(kTlProduct + SPEC, 0);
+    // the kernel of every form names the form it runs: 11 rotating, 12 adding, 13 storing
+    const int tl_id = kTlProduct + (Spec::fixed ? SPEC : 10 + (rope_on ? 1 : accumulate ? 2 : 3));
+    if (threadIdx.x == 0) timeline_record(tl_id, 0);
     constexpr int kKb = Cfg::kKb;
     constexpr int kStages = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -386,7 +388,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 load_p(i, full);
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
-            timeline_record(kTlProduct + SPEC, 1);
+            timeline_record(tl_id, 1);
             for (int i = 0; i < early; ++i) {
                 load_q(i, smem_u32(&bars[i]));
                 issued = i + 1;
@@ -436,7 +438,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     break;
                 }
                 tc_fence_after();
-                if (i == 0) timeline_record(kTlProduct + SPEC, 2);
+                if (i == 0) timeline_record(tl_id, 2);
                 const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes);
 #pragma unroll
                 for (int j = 0; j < kKb; ++j) {
@@ -451,7 +453,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 umma_commit(smem_u32(&bars[kStages + s]));      // frees the stage once the MMAs have read it
             }
             if (ok) umma_commit(smem_u32(&bars[2 * kStages]));  // accumulator complete
-            timeline_record(kTlProduct + SPEC, 3);
+            timeline_record(tl_id, 3);
         }
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..5)
@@ -459,17 +461,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         const int lane_group = warp & 3;                        // the TMEM lanes this warp may read
         const int row_in_tile = lane_group * 32 + lane;
         const int row_p = tile_p * kBlockP + row_in_tile;
-        // A tile of 16 columns that this CTA itself will add into C: the old values are requested
-        // now, while the products run, instead of after them.
-        const bool early_old = BLOCK_Q == 16 && accumulate && !c_bf16 && row_p < p.rows_p &&
+        // A tile of up to 32 columns that this CTA itself will add into C: the old values are requested
+        // now, while the products run, instead of after them (at 32 tokens the tail after the last MMA was 6 us with
+        // the loads in it).
+        constexpr int kEarlyOld = BLOCK_Q <= 32 ? BLOCK_Q : 1;
+        const bool early_old = BLOCK_Q <= 32 && accumulate && !c_bf16 && row_p < p.rows_p &&
                                (one_split || (cluster && split == 0));
-        float old_c[16];
+        float old_c[kEarlyOld];
         if (early_old) {
             const float* c = static_cast<const float*>(p.C) + static_cast<long long>(row_p) * p.stride_p +
                              static_cast<long long>(tile_q * BLOCK_Q) * p.stride_q;
-            const int n = min(16, p.rows_q - tile_q * BLOCK_Q);
+            const int n = min(kEarlyOld, p.rows_q - tile_q * BLOCK_Q);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) old_c[j] = (j < n) ? __ldcg(c + j * p.stride_q) : 0.f;
+            for (int j = 0; j < kEarlyOld; ++j) old_c[j] = (j < n) ? __ldcg(c + j * p.stride_q) : 0.f;
         }
         // Rotation and store: thread j < BLOCK_Q looks up the position and the page row of token j of the
         // tile now, while the products run.
@@ -485,17 +489,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 }
             }
         }
-        // A 16-token product shares the tokens' positions and page rows among the epilogue threads now, and every thread
-        // fetches the cosines and sines its row will need: the table look-ups (two trips to memory) leave the tail
-        // that follows the last MMA, which is on every decode step's critical path.
-        constexpr bool kRopeEarly = BLOCK_Q == 16;
+        // A product of up to 32 tokens shares the tokens' positions and page rows among the epilogue threads now, and every
+        // thread fetches the cosines and sines its row will need: the table look-ups (two trips to memory per four tokens)
+        // leave the tail that follows the last MMA, which is on every decode step's critical path. (Asking L1 for them
+        // with prefetch instructions instead, and reading them in a rolled loop later, was far slower.)
+        constexpr bool kRopeEarly = BLOCK_Q <= 32;
+        constexpr int kRopeN = kRopeEarly ? BLOCK_Q : 1;
         int* side_pos = reinterpret_cast<int*>(smem + kStages * Cfg::kStageBytes + 256);
-        long long* side_base = reinterpret_cast<long long*>(side_pos + 16);
-        float rope_c[16], rope_s[16];
+        long long* side_base = reinterpret_cast<long long*>(smem + kStages * Cfg::kStageBytes + 256 + 128);
+        float rope_c[kRopeN], rope_s[kRopeN];
         int rope_partner = row_in_tile;
         bool rope_rotate = false, rope_first = true;
         if (kRopeEarly && rope_on) {
-            if (row_in_tile < 16) { side_pos[row_in_tile] = tok_pos; side_base[row_in_tile] = tok_base; }
+            if (row_in_tile < kRopeN) { side_pos[row_in_tile] = tok_pos; side_base[row_in_tile] = tok_base; }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             const RopeStoreParams& rp = p.rope;
             const int hd = rp.hd, head = row_p / hd, d = row_p - head * hd;
@@ -506,7 +512,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 if (rp.interleaved) { rope_first = (d & 1) == 0; rope_partner = row_in_tile ^ 1; ci = d >> 1; }
                 else { rope_first = d < rh; rope_partner = rope_first ? row_in_tile + rh : row_in_tile - rh; ci = rope_first ? d : d - rh; }
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
+                for (int j = 0; j < kRopeN; ++j) {
                     const size_t at = static_cast<size_t>(side_pos[j]) * rh + ci;      // tokens beyond the last have position 0
                     rope_c[j] = __ldg(rp.cos_t + at);
                     rope_s[j] = __ldg(rp.sin_t + at);
@@ -532,7 +538,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             have = false;
         }
         tc_fence_after();
-        if (warp == 2 && lane == 0) timeline_record(kTlProduct + SPEC, 4);
+        if (warp == 2 && lane == 0) timeline_record(tl_id, 4);
         // one decision for all 128 epilogue threads (they meet at named barriers below)
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) *epi_abort = *abort_flag;
@@ -583,6 +589,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     all_here = mbar_try_wait_cluster(smem_u32(&bars[2 * kStages + 1]), 0);
                     if (!all_here && clock64() - t0 > kWaitCycles) { atomicCAS(p.status, 0, kErrClusterWait); break; }
                 }
+                if (warp == 2 && lane == 0) timeline_record(tl_id, 7);
                 if (all_here && !aborted) {
 #pragma unroll 1
                     for (int c = 0; c < kChunks; ++c) {
@@ -599,7 +606,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
                             for (int j = 0; j < 16; ++j) v[j] += part[(c * 16 + j) * kBlockP + row_in_tile];
                         }
-                        if (early_old) store_row_chunk_old(p, row_p, tile_q * BLOCK_Q, v, old_c);
+                        if (early_old) {
+                            float oc[16];                         // this chunk's old values, picked with constant indices
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) oc[j] = (kEarlyOld > 16 && c == 1) ? old_c[(kEarlyOld > 16 ? 16 : 0) + j] : old_c[j];
+                            store_row_chunk_old(p, row_p, tile_q * BLOCK_Q + c * 16, v, oc);
+                        }
                         else emit(c, v);
                     }
                 }
@@ -619,7 +631,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = 0.f;
                     }
-                    if (early_old) store_row_chunk_old(p, row_p, tile_q * BLOCK_Q, v, old_c);
+                    if (early_old) {
+                            float oc[16];                         // this chunk's old values, picked with constant indices
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) oc[j] = (kEarlyOld > 16 && c == 1) ? old_c[(kEarlyOld > 16 ? 16 : 0) + j] : old_c[j];
+                            store_row_chunk_old(p, row_p, tile_q * BLOCK_Q + c * 16, v, oc);
+                        }
                     else emit(c, v);
                 }
             } else {
@@ -676,6 +693,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 }
             }
         }
+        if (warp == 2 && lane == 0) timeline_record(tl_id, 8);
         if (rope_on) {
             const RopeStoreParams& rp = p.rope;
             if constexpr (kRopeEarly) {
@@ -687,7 +705,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     const size_t kv_head = static_cast<size_t>(is_q ? 0 : (is_k ? head - rp.H : head - rp.H - rp.Hkv)) * rp.page_size * hd + d;
                     __nv_bfloat16* cache = is_k ? rp.k_cache : rp.v_cache;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
+                    for (int j = 0; j < kRopeN; ++j) {
                         if (j >= n_tok) break;
                         float out = xch[j * kBlockP + row_in_tile];
                         if (rope_rotate) {
@@ -734,7 +752,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 }
             }
         }
-        if (warp == 2 && lane == 0) timeline_record(kTlProduct + SPEC, 5);
+        if (warp == 2 && lane == 0) timeline_record(tl_id, 5);
         tc_fence_before();
     }
     __syncthreads();
@@ -742,7 +760,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         tc_fence_after();
         tmem_dealloc(tmem_base, Cfg::kTmemCols);
     }
-    if (threadIdx.x == 0) timeline_record(kTlProduct + SPEC, 6);
+    if (threadIdx.x == 0) timeline_record(tl_id, 6);
 }
 
 // ------------------------------------------------------------------------------------------ persistent kernel

@@ -2,8 +2,8 @@
 
 Built with ``-DGI_TIMELINE`` (``library.use_timeline_build()``, a library of its own beside the ordinary one), the
 kernels of a step record (kernel, event, block, %globaltimer) at a few places: a block enters, its wait for the
-kernel ahead is over, its first operands have arrived, its last MMA is issued, the accumulator is complete, its results
-are stored, it leaves. This shows what no per-kernel profile shows: how the kernels of a step overlap (programmatic
+kernel ahead is over, its first operands have arrived, its last MMA is issued, the accumulator is complete, (the first block of a cluster:) the
+other blocks' partial tiles have arrived, the sums are complete, its results are stored, it leaves. This shows what no per-kernel profile shows: how the kernels of a step overlap (programmatic
 dependent launch lets a block enter, and fetch weights, long before it may read what the kernel ahead writes), what
 the hand-over from one kernel to the next costs, and which blocks of a kernel are late. 32 ns resolution on a B200.
 """
@@ -17,7 +17,8 @@ import torch
 from .library import lib
 
 KERNELS = {1: "rmsnorm", 2: "swiglu", 3: "attention_decode", 4: "add ranges", 5: "rope_store", 6: "attention_prefill",
-           100: "product (any form)", 101: "product qkv+rope", 102: "product add", 103: "product store",
+           101: "product qkv+rope", 102: "product add", 103: "product store",
+           111: "product qkv+rope (general)", 112: "product add (general)", 113: "product store (general)",
            200: "products store", 201: "products store (pairs)", 202: "products add", 203: "products add (pairs)",
            204: "products swiglu", 205: "products swiglu (pairs)", 206: "products rope", 207: "products rope (pairs)"}
 EVENTS = {"rmsnorm": {0: "enter", 1: "waited", 6: "leave"}, "swiglu": {0: "enter", 1: "waited", 6: "leave"},
@@ -25,7 +26,7 @@ EVENTS = {"rmsnorm": {0: "enter", 1: "waited", 6: "leave"}, "swiglu": {0: "enter
           "add ranges": {0: "enter", 1: "waited", 6: "leave"}, "rope_store": {0: "enter", 1: "waited"},
           "attention_prefill": {0: "enter", 1: "waited", 6: "leave"},
           "product": {0: "enter", 1: "waited", 2: "first operands", 3: "last MMA issued", 4: "accumulator ready",
-                      5: "results stored", 6: "leave"},
+                      7: "partial tiles arrived", 8: "sums complete", 5: "results stored", 6: "leave"},
           "products": {0: "enter", 1: "waited", 2: "first operands", 3: "last MMA issued", 4: "first accumulator ready",
                        5: "results stored", 6: "leave"}}
 
