@@ -366,7 +366,7 @@ def run_sizes(args):
     contexts = (128, 2048, CONTEXT, 4 * CONTEXT)
     points = []
     for batch in (1, 4, 8, 16, 32, 64):
-        longest = max(c for c in contexts if batch * c <= 8 * 4 * CONTEXT)          # at most 256 Ki cached positions
+        longest = max(c for c in contexts if batch * c <= 64 * CONTEXT)             # at most 512 Ki cached positions
         llm = Engine(folder, dtype="bfloat16", max_seq_len=longest, page_size=PAGE, kv_pages=batch * ((longest + PAGE - 1) // PAGE),
                      max_running=batch, step_tokens=max(batch, 16), prefix_cache=False)
         for context in contexts:
