@@ -1598,7 +1598,7 @@ static int gi_gemm_tc_rope_impl(const void* A, const void* W, int M, int K, long
                                int hd, int page_size, int write_kv, void* stream) {
     GI_REQUIRE(H > 0 && Hkv > 0 && hd > 0 && page_size > 0, "gemm_tc rope: sizes must be positive");
     GI_REQUIRE(kBlockP % hd == 0, "gemm_tc rope: the head size %d does not divide %d", hd, kBlockP);
-    GI_REQUIRE(M <= block_q || block_q == 128, "gemm_tc rope: block_q=%d is too small for %d tokens", block_q, M);
+    GI_REQUIRE(block_q <= 128, "gemm_tc rope: block_q=%d (at most 128 tokens to a tile)", block_q);
     GI_REQUIRE(cos_t == nullptr || (sin_t != nullptr && rot_half > 0 && 2 * rot_half <= hd),
                "gemm_tc rope: rotary size %d does not fit the head size %d", 2 * rot_half, hd);
     RopeStoreParams rope{positions, row_req, block_tables, table_stride, cos_t, sin_t, rot_half, interleaved,

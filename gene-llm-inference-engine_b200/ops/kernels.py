@@ -408,6 +408,15 @@ def _swap_plan(M: int, N: int, K: int):
     block_q = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
     tiles = (N + 127) // 128
     k_blocks = (K + 63) // 64
+    if 32 < M <= 64 and 2 * tiles * 2 <= sm_count():
+        # 33 to 64 tokens over a matrix of few row tiles: two tiles of 32 tokens, each with its own CTAs (the second reads the
+        # weights from L2), so that what the 32-token form has applies: ranges of K added up in a cluster, residual values
+        # and rotation tables requested early, rotation in the epilogue. Measured at the Llama-3.2-1B widths, 64 tokens:
+        # the O product 11.1 -> 7.3 us, down 16.1 -> 12.3, [q; k; v] 10.1 -> 8.6 (and no rotation kernel after it).
+        splits = 1
+        while 2 * tiles * (splits + 1) <= sm_count() and k_blocks // (splits + 1) >= 4 and splits < 5:
+            splits += 1
+        return True, 32, splits
     # split K until about three quarters of the SMs stream weights (112 CTAs on a B200), keeping at least
     # 4 steps of 64 per CTA (measured on B200 at the Llama-3.2-1B widths: 4 splits for 24 tiles, 6..8 for 16, 1 for 128)
     streaming = int(sm_count() * _STREAMING_SHARE) + 1
@@ -492,7 +501,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
             else:
                 splits = 1
         if plan is None and swap and splits > 1:
-            splits = gemm_tc_cluster_splits(block_q, (N + 127) // 128, splits, w_tiles is not None and block_q <= 128)
+            splits = gemm_tc_cluster_splits(block_q, (N + 127) // 128 * ((M + block_q - 1) // block_q), splits,
+                                            w_tiles is not None and block_q <= 128)
         chosen = (swap, block_q, splits, persistent)
         if key is not None:
             _gemm_choice[key] = chosen
@@ -538,8 +548,9 @@ def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> 
                                       st.status.data_ptr(), 1, 0, 0, _paired(M, 256), _stream()), "gemm_swiglu")
 
 
-_ROPE_FEW_TOKENS = 32      # up to here the few-token product (weights on the 128-row side) does the rotation: measured
-                           # in whole decode steps, 2.4 % faster at 16 tokens, even at 32, 1.7 % slower at 64
+_ROPE_FEW_TOKENS = 64      # up to here the few-token product (weights on the 128-row side, token tiles of at most 32) does
+                           # the rotation: measured in whole decode steps, 2.4 % faster at 16 tokens (with 64-token tiles
+                           # it was 1.7 % slower at 64 tokens)
 
 
 def gemm_rope_store_supported(M: int, K: int, num_heads: int, num_kv_heads: int, head_dim: int,
@@ -551,11 +562,11 @@ def gemm_rope_store_supported(M: int, K: int, num_heads: int, num_kv_heads: int,
     the rope+store kernel run one after the other."""
     if K % 8:
         return False
-    if M <= _ROPE_FEW_TOKENS:
+    N = (num_heads + 2 * num_kv_heads) * head_dim
+    if M <= 32 or (M <= _ROPE_FEW_TOKENS and _swap_plan(M, N, K)[1] == 32):      # token tiles of at most 32
         return 128 % head_dim == 0
     if head_dim not in (32, 64, 128) or not (cos is None or (not interleaved and 2 * cos.shape[1] == head_dim)):
         return False
-    N = (num_heads + 2 * num_kv_heads) * head_dim
     return M > 128 and _persistent_plan(M, N, K)[2] == 1
 
 
@@ -588,7 +599,7 @@ def gemm_rope_store(a: torch.Tensor, w_qkv: torch.Tensor, positions: torch.Tenso
     if M <= _ROPE_FEW_TOKENS:
         _, block_q, splits = _swap_plan(M, N, K)
         if splits > 1:
-            splits = gemm_tc_cluster_splits(block_q, (N + 127) // 128, splits, w_tiles is not None)
+            splits = gemm_tc_cluster_splits(block_q, (N + 127) // 128 * ((M + block_q - 1) // block_q), splits, w_tiles is not None)
         check(lib().gi_gemm_tc_rope(_dev(a, "a", torch.bfloat16), _dev(w_qkv, "w_qkv", torch.bfloat16), M, K, K, K, block_q,
                                     splits, st.workspace.data_ptr(), st.workspace.numel(), st.counters.data_ptr(),
                                     st.counters.numel(), st.status.data_ptr(), _opt(w_tiles, "w_tiles", torch.bfloat16),
