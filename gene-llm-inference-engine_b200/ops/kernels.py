@@ -385,15 +385,24 @@ def _persistent_plan(M: int, N: int, K: int):
     return False, block_q, splits
 
 
-def gemm_tc_plan(M: int, N: int, K: int):
-    """(swap, block_q, splits) for a product of these sizes; the choice depends on the sizes only.
+def gemm_tc_plan(M: int, N: int, K: int, accumulate: bool = False):
+    """(swap, block_q, splits) for a product of these sizes; the choice depends on the sizes (and on whether the
+    product is added into its output) only.
     Few tokens put the weights on the 128-row side (the tokens are the N of the MMA) and split K until
     the grid fills the GPU. Many tokens put the tokens on the 128-row side, one persistent CTA per SM,
-    K cut into ranges when the output has few tiles. Between 33 and 128 tokens a narrow matrix (one
+    K cut into ranges when the output has few tiles. Between 65 and 128 tokens a narrow matrix with a long K (one
     that the first form would split) is faster in the second form, whose ranges are added up by a
-    kernel of their own instead of by one CTA per tile (measured at the Llama-3.2-1B widths: the O
-    product of 128 tokens 25 -> 10.5 us, the down product 30 -> 17 us)."""
+    kernel of their own instead of by one CTA per tile (measured at the Llama-3.2-1B widths: the down product of
+    128 tokens 30 -> 17 us); with a short K, token tiles of 32 (or, for a product that is stored, of 64) in the first
+    form are faster still (the O product of 128 tokens 11.5 -> 8.6 us, [q; k; v] 12.3 -> 9.6 us; at the Llama-3.1-8B
+    widths [q; k; v] 30.5 -> 17.6 us)."""
     if M <= 128:
+        tiles, k_blocks = (N + 127) // 128, (K + 63) // 64
+        if M > 64 and k_blocks <= 64:
+            if tiles * ((M + 31) // 32) * 2 <= sm_count():
+                return True, 32, 2 if k_blocks >= 8 else 1
+            if not accumulate and tiles * ((M + 63) // 64) <= sm_count():
+                return True, 64, 1
         swap, block_q, splits = _swap_plan(M, N, K)
         if M > 32 and N >= 256 and N % 4 == 0 and (splits >= 6 or (M > 64 and splits > 1)):
             return _persistent_plan(M, N, K)
@@ -490,10 +499,10 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (M, N):
         raise KernelError(f"gemm: shapes do not agree (a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)})")
-    key = (M, N, K, out.dtype, w_tiles is not None) if plan is None else None
+    key = (M, N, K, out.dtype, w_tiles is not None, bool(accumulate)) if plan is None else None
     chosen = _gemm_choice.get(key) if key is not None else None
     if chosen is None:
-        swap, block_q, splits = plan or gemm_tc_plan(M, N, K)
+        swap, block_q, splits = plan or gemm_tc_plan(M, N, K, bool(accumulate))
         persistent = not swap and out.dtype is torch.float32 and N % 4 == 0 and block_q >= 128
         if not swap and not persistent:
             if plan is None and M <= 128:
