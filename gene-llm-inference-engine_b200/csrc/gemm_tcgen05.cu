@@ -61,8 +61,14 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t local_addr, uint32_t ra
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
     return remote;
 }
-__device__ __forceinline__ void cluster_store_f32(uint32_t remote_addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_addr), "f"(v) : "memory");
+// A 32-bit store into another CTA's shared memory that counts 4 bytes on a barrier of that CTA when it lands: the
+// receiver's wait ends with the last store's arrival, with no acknowledgement to the sender and no arrival after it.
+__device__ __forceinline__ void cluster_store_f32_counted(uint32_t remote_addr, float v, uint32_t remote_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+                 ::"r"(remote_addr), "r"(__float_as_uint(v)), "r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_local(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cluster_mbar_arrive(uint32_t remote_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
@@ -281,6 +287,14 @@ __device__ __forceinline__ void store_row_chunk_old(const TcParams& p, int row_p
 // compiled in and everything else is left out: a short kernel pays for every instruction it has to fetch, and the
 // L2 cache that would serve the fetch is swept by the weights between two launches (measured on B200: the
 // RMSNorm kernel cut from 19 KB to 6 KB of code made each of its launches 0.5 us shorter inside a decode step).
+// A 16-byte read-only load that stays where it is written: the compiler moves an ordinary load down to its first
+// use, which for values fetched "while the products run" is behind the wait for the products.
+__device__ __forceinline__ float4 load_now_f32x4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+
 enum TcSpecKind : int {
     kSpecAny = 0,
     kSpecRopeCluster = 1,    // [q; k; v] with rotation and store, K split over a cluster with partial tiles in a place of their own
@@ -341,7 +355,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             mbar_init(smem_u32(&bars[kStages + s]), 1);
         }
         mbar_init(smem_u32(&bars[2 * kStages]), 1);
-        mbar_init(smem_u32(&bars[2 * kStages + 1]), cluster ? static_cast<uint32_t>(n_splits - 1) * 128u : 1u);
+        mbar_init(smem_u32(&bars[2 * kStages + 1]), 1u);     // one arrival (split 0's own) and the bytes of the partial tiles
         mbar_init(smem_u32(&bars[2 * kStages + 2]), 1);
         *abort_flag = 0;
         *last_flag = 0;
@@ -489,55 +503,63 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 }
             }
         }
-        // A product of up to 16 tokens shares the tokens' positions and page rows among the epilogue threads now, and every
-        // thread fetches the cosines and sines its row will need: the table look-ups (two trips to memory per four tokens)
-        // leave the tail that follows the last MMA, which is on every decode step's critical path. (Asking L1 for them
-        // with prefetch instructions instead, and reading them in a rolled loop later, was far slower.)
-        constexpr bool kRopeEarly = BLOCK_Q <= 16;
-        constexpr bool kRopeWarm = BLOCK_Q == 32;
-        constexpr int kRopeN = kRopeEarly ? BLOCK_Q : 1;
-        int* side_pos = reinterpret_cast<int*>(smem + kStages * Cfg::kStageBytes + 256);
-        long long* side_base = reinterpret_cast<long long*>(smem + kStages * Cfg::kStageBytes + 256 + 128);
-        float rope_c[kRopeN], rope_s[kRopeN];
-        int rope_partner = row_in_tile;
-        bool rope_rotate = false, rope_first = true;
-        if (kRopeEarly && rope_on) {
-            if (row_in_tile < kRopeN) { side_pos[row_in_tile] = tok_pos; side_base[row_in_tile] = tok_base; }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+        // Token tiles of 16 and 32: rotation and store are done four features at a time. The finished tile lies in shared
+        // memory as [token][128 rows]; thread t takes token t / kTpt and kFeat neighbouring rows of it, reads them and their
+        // rotation partners 16 bytes at a time and writes 8 bytes of bfloat16 at a time. Everything that does not need the
+        // sums is worked out now, while the products run: the cosines and sines (16 bytes at a time), where each group of
+        // four goes and how it is rotated. What follows the last MMA is one warp's instructions one after the other, about
+        // 4 ns each: one thread per row walking over 32 tokens (two table look-ups, index arithmetic and a 2-byte store
+        // per token) took 5 to 7 us there, this takes 1 to 2. The loads and the addresses are pinned with volatile asm,
+        // since the compiler moves both down to their first use, behind the wait. Needs the half-split pairing with a
+        // rotary half that is a multiple of 4; else the loop below.
+        constexpr bool kRopeVec = BLOCK_Q <= 32;
+        constexpr int kTpt = kRopeVec ? 128 / BLOCK_Q : 1;          // threads per token
+        constexpr int kFeat = kRopeVec ? BLOCK_Q : 4;               // rows (features) per thread
+        constexpr int kGroups = kFeat / 4;
+        bool rope_vec = false;
+        float4 rope_c4[kGroups], rope_s4[kGroups];
+        __nv_bfloat16* v_dst[kGroups];              // where each group of 4 features goes (nullptr: nowhere)
+        unsigned v_mode = 0;                        // 2 bits a group: 1 first members of rotated pairs, 2 second members
+        int v_partner = 0;                          // distance to the rotation partners, in groups
+        if (kRopeVec && rope_on) {
             const RopeStoreParams& rp = p.rope;
-            const int hd = rp.hd, head = row_p / hd, d = row_p - head * hd;
             const int rh = rp.cos_t ? rp.rot_half : 0;
-            rope_rotate = row_p < p.rows_p && head < rp.H + rp.Hkv && d < 2 * rh;
-            int ci = 0;
-            if (rope_rotate) {
-                if (rp.interleaved) { rope_first = (d & 1) == 0; rope_partner = row_in_tile ^ 1; ci = d >> 1; }
-                else { rope_first = d < rh; rope_partner = rope_first ? row_in_tile + rh : row_in_tile - rh; ci = rope_first ? d : d - rh; }
+            rope_vec = !rp.interleaved && rh % 4 == 0 && (reinterpret_cast<uintptr_t>(rp.cos_t) % 16 == 0) &&
+                       (reinterpret_cast<uintptr_t>(rp.sin_t) % 16 == 0);
+            if (rope_vec) {
+                const int v_tok = tile_q * BLOCK_Q + row_in_tile / kTpt;
+                int pos = 0;
+                long long v_base = -1;
+                if (v_tok < p.rows_q) {
+                    pos = rp.positions[v_tok];
+                    if (rp.write_kv) {
+                        const int page = rp.block_tables[static_cast<size_t>(rp.row_req[v_tok]) * rp.table_stride + pos / rp.page_size];
+                        v_base = (static_cast<long long>(page) * rp.Hkv * rp.page_size + (pos % rp.page_size)) * rp.hd;
+                    }
+                }
+                v_partner = rh / 4;
 #pragma unroll
-                for (int j = 0; j < kRopeN; ++j) {
-                    const size_t at = static_cast<size_t>(side_pos[j]) * rh + ci;      // tokens beyond the last have position 0
-                    rope_c[j] = __ldg(rp.cos_t + at);
-                    rope_s[j] = __ldg(rp.sin_t + at);
+                for (int g = 0; g < kGroups; ++g) {
+                    const int row = tile_p * kBlockP + (row_in_tile % kTpt) * kFeat + 4 * g;
+                    const int head = row / rp.hd, d = row - head * rp.hd;
+                    const bool is_q = head < rp.H, is_k = !is_q && head < rp.H + rp.Hkv;
+                    rope_c4[g] = rope_s4[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    v_dst[g] = nullptr;
+                    if (row < p.rows_p && v_tok < p.rows_q) {
+                        if ((is_q || is_k) && d < 2 * rh) {
+                            const size_t at = static_cast<size_t>(pos) * rh + (d < rh ? d : d - rh);
+                            rope_c4[g] = load_now_f32x4(rp.cos_t + at);
+                            rope_s4[g] = load_now_f32x4(rp.sin_t + at);
+                            v_mode |= (d < rh ? 1u : 2u) << (2 * g);
+                        }
+                        if (is_q) v_dst[g] = rp.q_out + (static_cast<size_t>(v_tok) * rp.H + head) * rp.hd + d;
+                        else if (v_base >= 0)
+                            v_dst[g] = (is_k ? rp.k_cache : rp.v_cache) + v_base +
+                                       static_cast<size_t>(is_k ? head - rp.H : head - rp.H - rp.Hkv) * rp.page_size * rp.hd + d;
+                    }
+                    asm volatile("" : "+l"(v_dst[g]));      // worked out here, not behind the wait
                 }
-            }
-        }
-        if (kRopeWarm && rope_on) {
-            // 32 tokens: the values would need 64 registers and a loop unrolled 32 times, 13 KB of code that runs once and
-            // has to be fetched; instead the loads are done now for their side effect: the lines are in L1 when the loop
-            // after the last MMA asks for them again (a decode step of 24 tokens 1.7 % faster than with registers; at
-            // 16 tokens the registers are 0.6 % faster)
-            const RopeStoreParams& rp = p.rope;
-            const int hd = rp.hd, head = row_p / hd, d = row_p - head * hd;
-            const int rh = rp.cos_t ? rp.rot_half : 0;
-            if (row_p < p.rows_p && head < rp.H + rp.Hkv && d < 2 * rh) {
-                const int ci = rp.interleaved ? d >> 1 : (d < rh ? d : d - rh);
-                const int n_tok = min(BLOCK_Q, p.rows_q - tile_q * BLOCK_Q);
-                float warm = 0.f;
-#pragma unroll 4
-                for (int j = 0; j < n_tok; ++j) {
-                    const size_t at = static_cast<size_t>(__ldg(p.rope.positions + tile_q * BLOCK_Q + j)) * rh + ci;
-                    warm += __ldg(rp.cos_t + at) + __ldg(rp.sin_t + at);
-                }
-                if (warm == 1.2345e30f) tok_pos += 1;        // keeps the loads alive
+                asm volatile("" : "+r"(v_mode), "+r"(v_partner));
             }
         }
         // The pipeline's stages are free once the accumulator is complete: the finished tile is laid
@@ -587,23 +609,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     stages_free = mbar_try_wait_cluster(smem_u32(&bars[2 * kStages + 2]), 0);
                     if (!stages_free && clock64() - t0 > kWaitCycles) { atomicCAS(p.status, 0, kErrClusterWait); break; }
                 }
-                if (!aborted && stages_free) {
+                // The stores count their bytes on split 0's barrier as they land. A CTA that has given up sends zeros, so
+                // that the count is reached; only one that never heard from split 0 sends nothing (split 0 has then
+                // given up too, or will when its wait runs out).
+                if (stages_free) {
                     const uint32_t remote = cluster_map(smem_u32(partials), 0) +
                                             static_cast<uint32_t>((split - 1) * BLOCK_Q * kBlockP + row_in_tile) * 4u;
+                    const uint32_t remote_bar = cluster_map(smem_u32(&bars[2 * kStages + 1]), 0);
+                    const bool send = have && !aborted;
 #pragma unroll 1
                     for (int c = 0; c < kChunks; ++c) {
                         uint32_t r[16];
-                        if (have) {
+                        if (send) {
                             tmem_ld_x16(tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + c * 16, r);
                             tmem_ld_wait();
                         }
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
-                            cluster_store_f32(remote + static_cast<uint32_t>((c * 16 + j) * kBlockP) * 4u, have ? __uint_as_float(r[j]) : 0.f);
+                            cluster_store_f32_counted(remote + static_cast<uint32_t>((c * 16 + j) * kBlockP) * 4u,
+                                                      send ? __uint_as_float(r[j]) : 0.f, remote_bar);
                     }
                 }
-                cluster_mbar_arrive(cluster_map(smem_u32(&bars[2 * kStages + 1]), 0));
             } else {
+                if (warp == 2 && lane == 0)
+                    mbar_arrive_expect_tx_local(smem_u32(&bars[2 * kStages + 1]),
+                                                static_cast<uint32_t>(n_splits - 1) * 128u * kChunks * 16u * 4u);
+                // up to 32 tokens: this CTA's own sums leave tensor memory while the others' are on their way
+                constexpr int kOwnEarly = kChunks <= 2 ? kChunks : 0;
+                uint32_t own[kOwnEarly > 0 ? kOwnEarly : 1][16];
+                if (kOwnEarly > 0 && have && !aborted) {
+#pragma unroll
+                    for (int c = 0; c < kOwnEarly; ++c)
+                        tmem_ld_x16(tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + c * 16, own[c]);
+                    tmem_ld_wait();
+                }
                 bool all_here = mbar_try_wait_cluster(smem_u32(&bars[2 * kStages + 1]), 0);
                 const unsigned long long t0 = clock64();
                 while (!all_here) {
@@ -612,11 +651,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 }
                 if (warp == 2 && lane == 0) timeline_record(tl_id, 7);
                 if (all_here && !aborted) {
-#pragma unroll 1
+#pragma unroll (kOwnEarly > 0 ? kOwnEarly : 1)
                     for (int c = 0; c < kChunks; ++c) {
                         uint32_t r[16];
                         float v[16];
-                        if (have) {
+                        if (kOwnEarly > 0) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) r[j] = own[kOwnEarly > 0 ? c : 0][j];
+                        } else if (have) {
                             tmem_ld_x16(tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + c * 16, r);
                             tmem_ld_wait();
                         }
@@ -717,24 +759,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         if (warp == 2 && lane == 0) timeline_record(tl_id, 8);
         if (rope_on) {
             const RopeStoreParams& rp = p.rope;
-            if constexpr (kRopeEarly) {
+            if (kRopeVec && rope_vec) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");          // the finished tile is complete
-                if (emitted && row_p < p.rows_p) {
-                    const int hd = rp.hd, head = row_p / hd, d = row_p - head * hd;
-                    const bool is_q = head < rp.H, is_k = !is_q && head < rp.H + rp.Hkv;
-                    const int n_tok = min(BLOCK_Q, p.rows_q - tile_q * BLOCK_Q);
-                    const size_t kv_head = static_cast<size_t>(is_q ? 0 : (is_k ? head - rp.H : head - rp.H - rp.Hkv)) * rp.page_size * hd + d;
-                    __nv_bfloat16* cache = is_k ? rp.k_cache : rp.v_cache;
+                if (emitted) {
+                    const float4* x4 = reinterpret_cast<const float4*>(xch) + (row_in_tile / kTpt) * (kBlockP / 4) +
+                                       (row_in_tile % kTpt) * kGroups;
 #pragma unroll
-                    for (int j = 0; j < kRopeN; ++j) {
-                        if (j >= n_tok) break;
-                        float out = xch[j * kBlockP + row_in_tile];
-                        if (rope_rotate) {
-                            const float other = xch[j * kBlockP + rope_partner];
-                            out = rope_first ? out * rope_c[j] - other * rope_s[j] : other * rope_s[j] + out * rope_c[j];
+                    for (int g = 0; g < kGroups; ++g) {
+                        if (!v_dst[g]) continue;
+                        const unsigned mode = (v_mode >> (2 * g)) & 3u;
+                        float4 o = x4[g];
+                        if (mode) {
+                            // first member of a pair: a c - b s; second: a s + b c (b: the partner, rot_half rows away)
+                            const bool first = mode == 1u;
+                            const float4 b4 = x4[first ? g + v_partner : g - v_partner], c4 = rope_c4[g], s4 = rope_s4[g];
+                            o.x = first ? o.x * c4.x - b4.x * s4.x : b4.x * s4.x + o.x * c4.x;
+                            o.y = first ? o.y * c4.y - b4.y * s4.y : b4.y * s4.y + o.y * c4.y;
+                            o.z = first ? o.z * c4.z - b4.z * s4.z : b4.z * s4.z + o.z * c4.z;
+                            o.w = first ? o.w * c4.w - b4.w * s4.w : b4.w * s4.w + o.w * c4.w;
                         }
-                        if (is_q) rp.q_out[(static_cast<size_t>(tile_q * BLOCK_Q + j) * rp.H + head) * hd + d] = __float2bfloat16_rn(out);
-                        else if (side_base[j] >= 0) cache[side_base[j] + kv_head] = __float2bfloat16_rn(out);
+                        const __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+                        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+                        *reinterpret_cast<uint2*>(v_dst[g]) = packed;
                     }
                 }
             } else {
