@@ -15,7 +15,7 @@
 // become the narrow side (C[q, p]), so that a decode step streams every weight once at full tile
 // efficiency. The split over K (few tokens, narrow weight matrices) runs the splits of a tile as
 // one thread-block cluster where they fit: splits 1.. write their partial tiles into the shared
-// memory of split 0 (st.shared::cluster) and arrive on its mbarrier, and split 0 adds them in split
+// memory of split 0 with stores that count their bytes on its mbarrier (st.async), and split 0 adds them in split
 // order. The tiles have a place of their own behind the pipeline stages where there is room (few
 // tokens); otherwise they land in split 0's stages once it has told the others that its products are
 // done with them. Where a cluster does not fit, partial tiles go to a workspace in global memory and the CTA
@@ -589,9 +589,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         const bool aborted = *epi_abort != 0;
         constexpr int kChunks = (BLOCK_Q + 15) / 16;
         if (cluster) {
-            // Splits 1.. hand their partial tile to split 0 (rank 0 of the cluster) and arrive on
-            // its barrier, even after giving up, so that split 0 never waits for a CTA that is gone;
-            // split 0 waits (bounded) before it leaves, so its memory outlives every write to it.
+            // Splits 1.. hand their partial tile to split 0 (rank 0 of the cluster) with stores that count
+            // their bytes on its barrier, zeros after giving up, so that split 0 never waits for a CTA that is gone;
+            // split 0 waits (bounded) for all bytes before it leaves, so its memory outlives every write to it.
             // Where the tiles land in split 0's pipeline stages (cluster == 2): split 0 says when its
             // products are done with them (an arrival on every other split's "stages free" barrier,
             // sent even after giving up), and the others wait for that (bounded) before they write and
