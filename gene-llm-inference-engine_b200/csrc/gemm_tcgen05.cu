@@ -1475,6 +1475,8 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, TcParams p, d
     // would cost more than the reduce through global memory
     const long long tiles = static_cast<long long>(grid.x) * grid.y;
     p.cluster = (p.splits > 1 && g_cluster_reduce && tiles <= cluster_capacity<BLOCK_Q, TILED>(p.splits)) ? 1 : 0;
+    // the partial tiles count their bytes on one mbarrier, whose byte count ends at 2^20 - 1
+    if (p.cluster && static_cast<long long>(p.splits - 1) * kBlockP * ((BLOCK_Q + 15) / 16 * 16) * 4 > 1048575ll) p.cluster = 0;
     if (p.cluster && Cfg::smem_bytes(p.splits) > Cfg::kOwnPlaceLimit) p.cluster = 2;    // partial tiles in split 0's stages
     // the forms of a decode step of up to 16 tokens over tiled weights: kernels with nothing else in them
     if constexpr (BLOCK_Q == 16 && TILED) {
